@@ -1,0 +1,339 @@
+/*
+ * CPU oracle for the quantized u8 x s8 -> s32 and fp16 -> fp32 contractions.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are
+ * compared against and the timed host-CPU baseline; nothing in the shipped
+ * library links or calls it.
+ *
+ * It restates, in plain C, the arithmetic the reference (were/UNIT) produces
+ * on its tensorized paths.  The reference's own computes live in a forked TVM
+ * that is not part of the reference tree, so every function below follows the
+ * reference's call sites and layouts:
+ *
+ *   - micro-op  c[x] += sum_{r<4} u8 a[4x+r] * s8 b[4x+r], 16 lanes, wrapping
+ *     s32 add: python/tensorizer/intrinsics/pattern.py:3-16 (x86_vnni),
+ *     python/tensorizer/intrinsics/cpu.py:42-49 (vpdpbusd), checked by
+ *     poc/vnni/poc.cc:22-38.
+ *   - int8 conv, data [N][C/cb][H][W][cb] (cb = 16, or 4 for the stem) and
+ *     weights [O/16][C/cb][KH][KW][cb/4][16][4]:
+ *     apps/cpu/kernel/conv2d.py:18-30,50-51; the index expression is written
+ *     out for the 3-D sibling at apps/cpu/kernel/conv3d.py:60-64.
+ *   - int8 dense, A [M][K] u8 and B [N/T][K/4][T][4] s8:
+ *     apps/cpu/kernel/int8-gemm.py:9-16, poc/vnni/vnni_dense.py:10-20,58-67.
+ *   - fp16 conv, data [N][C/16][H][W][16], weights [O/16][C/16][KH][KW][16i][16o],
+ *     fp32 accumulate: python/tensorizer/ops/gpu.py:8-53.
+ *   - fp16 GEMM A [M][K] * B [K][N] -> fp32: apps/gpu/gemm.py:6-19.
+ *
+ * Parity pin: the int8 definitions are exact integer sums and are pinned by
+ * the reference's known-answer vector (poc/vnni/poc.cc, a[i]=i+1, b[i]=64-i)
+ * and by equality with an integer matmul (poc/vnni/vnni_dense.py:58-67), both
+ * reproduced in tests/.  The bias + requantise epilogue has no test in the
+ * reference: PARITY UNPINNED for that epilogue; its definition here is
+ * q = clamp((acc + bias[oc] + 128) >> 8, 0, 255) (round-half-up of /256).
+ *
+ * All convolutions take explicit zero padding (pad_h, pad_w) and equal
+ * "zero-pad the input, then valid convolution", which is how the reference
+ * feeds pre-padded inputs (cpu-shapes.log rows carry the padded H, W).
+ */
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+#if defined(__AVX512VNNI__) && defined(__AVX512F__)
+#include <immintrin.h>
+#define UNIT_HAVE_VNNI 1
+#else
+#define UNIT_HAVE_VNNI 0
+#endif
+
+typedef _Float16 f16;
+
+int oracle_has_vnni(void) { return UNIT_HAVE_VNNI; }
+
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* The 16-lane, 4-way dot-product micro-op (pattern.py:3-16).  Scalar form. */
+void oracle_vnni_dot(const uint8_t *a, const int8_t *b, int32_t *c) {
+  for (int x = 0; x < 16; ++x) {
+    uint32_t acc = (uint32_t)c[x];
+    for (int r = 0; r < 4; ++r)
+      acc += (uint32_t)((int32_t)a[4 * x + r] * (int32_t)b[4 * x + r]);
+    c[x] = (int32_t)acc;
+  }
+}
+
+/* Same micro-op through the hardware instruction, when the host has it.
+ * Returns 0 if it ran, -1 if the host has no AVX-512 VNNI. */
+int oracle_vnni_dot_hw(const uint8_t *a, const int8_t *b, int32_t *c) {
+#if UNIT_HAVE_VNNI
+  __m512i va = _mm512_loadu_si512((const void *)a);
+  __m512i vb = _mm512_loadu_si512((const void *)b);
+  __m512i vc = _mm512_loadu_si512((const void *)c);
+  vc = _mm512_dpbusd_epi32(vc, va, vb);
+  _mm512_storeu_si512((void *)c, vc);
+  return 0;
+#else
+  (void)a; (void)b; (void)c;
+  return -1;
+#endif
+}
+
+static inline uint8_t requant_u8(int64_t acc, int32_t bias, int shift) {
+  int64_t v = acc + (int64_t)bias + ((int64_t)1 << (shift - 1));
+  v >>= shift; /* arithmetic shift: gcc implements >> on negative signed as such */
+  if (v < 0) v = 0;
+  if (v > 255) v = 255;
+  return (uint8_t)v;
+}
+
+/*
+ * Scalar int8 convolution in the reference's blocked layouts.
+ *   x   [N][Cc][H][W][cb]            u8, cb in {4, 16}
+ *   w   [Oc][Cc][KH][KW][cb/4][16][4] s8
+ *   out [N][Oc][OH][OW][16]          s32 (out_u8 == NULL) or u8 (requantised)
+ * Accumulates in int64 and reports (return value 1) if any sum left the s32
+ * range, in which case the wrapped value is stored like the hardware would.
+ */
+int oracle_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
+                       int32_t *out_s32, uint8_t *out_u8, int shift,
+                       int N, int Cc, int H, int W, int cb, int Oc,
+                       int KH, int KW, int sh, int sw, int ph, int pw) {
+  const int OH = (H + 2 * ph - KH) / sh + 1;
+  const int OW = (W + 2 * pw - KW) / sw + 1;
+  const int c4 = cb / 4;
+  int overflow = 0;
+#pragma omp parallel for collapse(2) reduction(| : overflow) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oc = 0; oc < Oc; ++oc)
+      for (int oh = 0; oh < OH; ++oh)
+        for (int ow = 0; ow < OW; ++ow) {
+          int64_t acc[16];
+          for (int l = 0; l < 16; ++l) acc[l] = 0;
+          for (int ic = 0; ic < Cc; ++ic)
+            for (int kh = 0; kh < KH; ++kh) {
+              const int ih = oh * sh + kh - ph;
+              if (ih < 0 || ih >= H) continue;
+              for (int kw = 0; kw < KW; ++kw) {
+                const int iw = ow * sw + kw - pw;
+                if (iw < 0 || iw >= W) continue;
+                const uint8_t *xp = x + ((((size_t)n * Cc + ic) * H + ih) * W + iw) * cb;
+                const int8_t *wp = w + ((((size_t)oc * Cc + ic) * KH + kh) * KW + kw) * (size_t)(c4 * 64);
+                for (int m = 0; m < c4; ++m)
+                  for (int l = 0; l < 16; ++l)
+                    for (int r = 0; r < 4; ++r)
+                      acc[l] += (int32_t)xp[m * 4 + r] * (int32_t)wp[(m * 16 + l) * 4 + r];
+              }
+            }
+          const size_t o = ((((size_t)n * Oc + oc) * OH + oh) * OW + ow) * 16;
+          for (int l = 0; l < 16; ++l) {
+            if (acc[l] > INT32_MAX || acc[l] < INT32_MIN) overflow |= 1;
+            if (out_u8)
+              out_u8[o + l] = requant_u8((int64_t)(int32_t)(uint32_t)(uint64_t)acc[l],
+                                         bias ? bias[oc * 16 + l] : 0, shift);
+            else
+              out_s32[o + l] = (int32_t)(uint32_t)(uint64_t)acc[l] + (bias ? bias[oc * 16 + l] : 0);
+          }
+        }
+  return overflow;
+}
+
+/* Scalar int8 dense: C[i][j] = sum_k A[i][k] * Bp[j/T][k/4][j%T][k%4]. */
+int oracle_dense_u8s8s32(const uint8_t *A, const int8_t *Bp, int32_t *C,
+                         int M, int N, int K, int T) {
+  int overflow = 0;
+#pragma omp parallel for reduction(| : overflow) schedule(static)
+  for (int i = 0; i < M; ++i)
+    for (int j = 0; j < N; ++j) {
+      int64_t acc = 0;
+      const int8_t *bp = Bp + ((size_t)(j / T) * (K / 4)) * T * 4 + (size_t)(j % T) * 4;
+      for (int k = 0; k < K; ++k)
+        acc += (int32_t)A[(size_t)i * K + k] * (int32_t)bp[(size_t)(k / 4) * T * 4 + (k % 4)];
+      if (acc > INT32_MAX || acc < INT32_MIN) overflow |= 1;
+      C[(size_t)i * N + j] = (int32_t)(uint32_t)(uint64_t)acc;
+    }
+  return overflow;
+}
+
+/* fp16 conv, fp32 accumulate in plain (ic, kh, kw) order: ops/gpu.py:39-45. */
+void oracle_conv2d_f16f32(const f16 *x, const f16 *w, float *out,
+                          int N, int Cc, int H, int W, int Oc,
+                          int KH, int KW, int sh, int sw, int ph, int pw) {
+  const int OH = (H + 2 * ph - KH) / sh + 1;
+  const int OW = (W + 2 * pw - KW) / sw + 1;
+#pragma omp parallel for collapse(3) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oc = 0; oc < Oc; ++oc)
+      for (int oh = 0; oh < OH; ++oh)
+        for (int ow = 0; ow < OW; ++ow) {
+          float acc[16];
+          for (int l = 0; l < 16; ++l) acc[l] = 0.f;
+          for (int ic = 0; ic < Cc; ++ic)
+            for (int kh = 0; kh < KH; ++kh) {
+              const int ih = oh * sh + kh - ph;
+              if (ih < 0 || ih >= H) continue;
+              for (int kw = 0; kw < KW; ++kw) {
+                const int iw = ow * sw + kw - pw;
+                if (iw < 0 || iw >= W) continue;
+                const f16 *xp = x + ((((size_t)n * Cc + ic) * H + ih) * W + iw) * 16;
+                const f16 *wp = w + ((((size_t)oc * Cc + ic) * KH + kh) * KW + kw) * (size_t)256;
+                for (int i = 0; i < 16; ++i) {
+                  const float a = (float)xp[i];
+                  for (int l = 0; l < 16; ++l) acc[l] += a * (float)wp[i * 16 + l];
+                }
+              }
+            }
+          float *op = out + ((((size_t)n * Oc + oc) * OH + oh) * OW + ow) * 16;
+          for (int l = 0; l < 16; ++l) op[l] = acc[l];
+        }
+}
+
+/* fp16 GEMM C[M][N] = A[M][K] * B[K][N], fp32 accumulate: apps/gpu/gemm.py:14-19. */
+void oracle_gemm_f16f32(const f16 *A, const f16 *B, float *C, int M, int N, int K) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    float *c = C + (size_t)i * N;
+    for (int j = 0; j < N; ++j) c[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float a = (float)A[(size_t)i * K + k];
+      const f16 *b = B + (size_t)k * N;
+      for (int j = 0; j < N; ++j) c[j] += a * (float)b[j];
+    }
+  }
+}
+
+/* ------------------------------------------------------------------------
+ * AVX-512 VNNI + OpenMP restatement of the reference's generated loop nest
+ * (python/tensorizer/intrinsics/cpu.py:51-187: parallel fused outer axes,
+ * reduction over (ic chunk, kh, kw), unrolled output positions, one
+ * vpdpbusd per 4 input channels x 16 output channels).  This is the timed
+ * CPU baseline; tests check it bit-exact against the scalar functions above.
+ * Returns -1 when the host has no AVX-512 VNNI.
+ * ---------------------------------------------------------------------- */
+#define OWB 14 /* output positions kept in registers per inner block */
+
+int vnni_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
+                     int32_t *out_s32, uint8_t *out_u8, int shift,
+                     int N, int Cc, int H, int W, int cb, int Oc,
+                     int KH, int KW, int sh, int sw, int ph, int pw) {
+#if UNIT_HAVE_VNNI
+  const int OH = (H + 2 * ph - KH) / sh + 1;
+  const int OW = (W + 2 * pw - KW) / sw + 1;
+  const int c4 = cb / 4;
+  const int nblk = (OW + OWB - 1) / OWB;
+#pragma omp parallel for collapse(3) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oc = 0; oc < Oc; ++oc)
+      for (int oh = 0; oh < OH; ++oh)
+        for (int blk = 0; blk < nblk; ++blk) {
+          const int ow0 = blk * OWB;
+          const int nw = (OW - ow0 < OWB) ? (OW - ow0) : OWB;
+          __m512i acc[OWB];
+          const __m512i vb = bias ? _mm512_loadu_si512((const void *)(bias + oc * 16))
+                                  : _mm512_setzero_si512();
+          for (int j = 0; j < OWB; ++j) acc[j] = _mm512_setzero_si512();
+          for (int ic = 0; ic < Cc; ++ic)
+            for (int kh = 0; kh < KH; ++kh) {
+              const int ih = oh * sh + kh - ph;
+              if (ih < 0 || ih >= H) continue;
+              const uint8_t *xrow = x + (((size_t)n * Cc + ic) * H + ih) * (size_t)W * cb;
+              for (int kw = 0; kw < KW; ++kw) {
+                const int8_t *wp = w + ((((size_t)oc * Cc + ic) * KH + kh) * KW + kw) * (size_t)(c4 * 64);
+                const int iwb = ow0 * sw + kw - pw;
+                const int interior = (iwb >= 0) && (iwb + (nw - 1) * sw < W);
+                for (int m = 0; m < c4; ++m) {
+                  const __m512i wv = _mm512_loadu_si512((const void *)(wp + m * 64));
+                  if (interior && nw == OWB) {
+#pragma GCC unroll 14
+                    for (int j = 0; j < OWB; ++j) {
+                      int32_t d;
+                      memcpy(&d, xrow + (size_t)(iwb + j * sw) * cb + m * 4, 4);
+                      acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);
+                    }
+                  } else {
+                    for (int j = 0; j < nw; ++j) {
+                      const int iw = iwb + j * sw;
+                      if (iw < 0 || iw >= W) continue;
+                      int32_t d;
+                      memcpy(&d, xrow + (size_t)iw * cb + m * 4, 4);
+                      acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);
+                    }
+                  }
+                }
+              }
+            }
+          const size_t o = ((((size_t)n * Oc + oc) * OH + oh) * OW + ow0) * 16;
+          if (out_u8) {
+            const __m512i rnd = _mm512_set1_epi32(1 << (shift - 1));
+            for (int j = 0; j < nw; ++j) {
+              __m512i v = _mm512_add_epi32(_mm512_add_epi32(acc[j], vb), rnd);
+              v = _mm512_srai_epi32(v, (unsigned)shift);
+              v = _mm512_max_epi32(v, _mm512_setzero_si512());
+              v = _mm512_min_epi32(v, _mm512_set1_epi32(255));
+              _mm_storeu_si128((__m128i *)(out_u8 + o + (size_t)j * 16), _mm512_cvtepi32_epi8(v));
+            }
+          } else {
+            for (int j = 0; j < nw; ++j)
+              _mm512_storeu_si512((void *)(out_s32 + o + (size_t)j * 16), _mm512_add_epi32(acc[j], vb));
+          }
+        }
+  return 0;
+#else
+  (void)x; (void)w; (void)bias; (void)out_s32; (void)out_u8; (void)shift;
+  (void)N; (void)Cc; (void)H; (void)W; (void)cb; (void)Oc; (void)KH; (void)KW;
+  (void)sh; (void)sw; (void)ph; (void)pw;
+  return -1;
+#endif
+}
+
+/* VNNI dense on the packed B: 16 output columns per accumulator, RB rows kept
+ * in registers.  Requires T % 16 == 0 and K % 4 == 0. */
+#define RB 12
+int vnni_dense_u8s8s32(const uint8_t *A, const int8_t *Bp, int32_t *C,
+                       int M, int N, int K, int T) {
+#if UNIT_HAVE_VNNI
+  if (T % 16 || K % 4 || N % T) return -2;
+  const int K4 = K / 4;
+  const int nrb = (M + RB - 1) / RB;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int rb = 0; rb < nrb; ++rb)
+    for (int jb = 0; jb < N / 16; ++jb) {
+      const int i0 = rb * RB;
+      const int nr = (M - i0 < RB) ? (M - i0) : RB;
+      const int j0 = jb * 16;
+      const int8_t *bp = Bp + ((size_t)(j0 / T) * K4) * T * 4 + (size_t)(j0 % T) * 4;
+      __m512i acc[RB];
+      for (int r = 0; r < RB; ++r) acc[r] = _mm512_setzero_si512();
+      for (int k4 = 0; k4 < K4; ++k4) {
+        const __m512i wv = _mm512_loadu_si512((const void *)(bp + (size_t)k4 * T * 4));
+        if (nr == RB) {
+#pragma GCC unroll 12
+          for (int r = 0; r < RB; ++r) {
+            int32_t d;
+            memcpy(&d, A + (size_t)(i0 + r) * K + k4 * 4, 4);
+            acc[r] = _mm512_dpbusd_epi32(acc[r], _mm512_set1_epi32(d), wv);
+          }
+        } else {
+          for (int r = 0; r < nr; ++r) {
+            int32_t d;
+            memcpy(&d, A + (size_t)(i0 + r) * K + k4 * 4, 4);
+            acc[r] = _mm512_dpbusd_epi32(acc[r], _mm512_set1_epi32(d), wv);
+          }
+        }
+      }
+      for (int r = 0; r < nr; ++r)
+        _mm512_storeu_si512((void *)(C + (size_t)(i0 + r) * N + j0), acc[r]);
+    }
+  return 0;
+#else
+  (void)A; (void)Bp; (void)C; (void)M; (void)N; (void)K; (void)T;
+  return -1;
+#endif
+}
