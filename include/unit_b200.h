@@ -1,0 +1,156 @@
+/*
+ * unit_b200 -- C ABI of the B200 (sm_100a) implementation of the contractions
+ * that were/UNIT tensorizes: u8 x s8 -> s32 conv2d / dense (its AVX-512 VNNI
+ * path) and fp16 -> fp32 conv2d / GEMM (its wmma path).
+ *
+ * Conventions
+ *   - every pointer named d_* is a DEVICE pointer, 16-byte aligned;
+ *   - the caller owns every buffer; the library reads inputs and writes only
+ *     the output (and, for the pack calls, the destination);
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it;
+ *   - every function returns a unit_status; nothing throws, aborts or prints;
+ *   - weights are consumed in a tensor-core-ready copy ("packed weights") that
+ *     the caller produces once per weight tensor with the unit_pack_weights_*
+ *     calls into a buffer of unit_packed_weights_bytes_* bytes.  The packed
+ *     form depends only on the arguments of the pack call.
+ *
+ * Each entry point names the reference interface it replaces (paths inside
+ * were/UNIT).  The reference JIT-compiles a TVM module and calls it as
+ * module(a, b, c) with the caller-allocated output last
+ * (poc/vnni/vnni_dense.py:66, apps/gpu/conv-fused.py:155); the functions
+ * below keep that argument order: inputs, weights, output.
+ */
+#ifndef UNIT_B200_H_
+#define UNIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum unit_status {
+  UNIT_OK = 0,
+  UNIT_ERR_NULL = -1,        /* a required pointer is NULL */
+  UNIT_ERR_SHAPE = -2,       /* a dimension is out of the supported range */
+  UNIT_ERR_ALIGN = -3,       /* a pointer or leading dimension is not 16-byte aligned */
+  UNIT_ERR_LAYOUT = -4,      /* channel block / tile size not supported */
+  UNIT_ERR_ARCH = -5,        /* the current device is not compute capability 10.0 */
+  UNIT_ERR_LAUNCH = -6,      /* the CUDA runtime refused the launch or a copy */
+  UNIT_ERR_DEVICE_WAIT = -7, /* a kernel gave up on an internal wait and flagged it */
+  UNIT_ERR_TOO_LARGE = -8    /* beyond a stated fixed capacity */
+} unit_status;
+
+/* Geometry of one convolution.  Channels are the stored (blocked) counts:
+ * c_in is a multiple of c_block, c_out a multiple of 16.
+ * Data layout  [n][c_in/c_block][h][w][c_block]   (NCHW16c, or NCHW4c when
+ * c_block == 4: apps/cpu/kernel/conv2d.py:18-30).
+ * Output layout [n][c_out/16][oh][ow][16], oh = (h + 2 pad_h - kh)/stride_h + 1.
+ * The reference convolves a pre-padded input with padding 0
+ * (apps/cpu/kernel/conv2d.py:50); pad_h/pad_w here are implicit zero padding
+ * with the same result as padding the input first. */
+typedef struct unit_conv_desc {
+  int32_t n, c_in, h, w;
+  int32_t c_block; /* 16, or 4 (int8 only) */
+  int32_t c_out;
+  int32_t kh, kw;
+  int32_t stride_h, stride_w;
+  int32_t pad_h, pad_w;
+} unit_conv_desc;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int unit_version(void);
+/* Static string for a unit_status value. */
+const char *unit_status_string(int status);
+/* Synchronises `stream`, then reports (and clears) the device-side error word:
+ * UNIT_OK, UNIT_ERR_DEVICE_WAIT if a kernel abandoned a bounded wait, or
+ * UNIT_ERR_LAUNCH for a CUDA error. */
+int unit_device_status(void *stream);
+/* Number of kernels this library has launched in this process (monotonic). */
+uint64_t unit_launch_count(void);
+
+/* ---- packed weights ------------------------------------------------------ */
+
+/* Replaces: the reference hands its packed weight array straight to the
+ * generated kernel (apps/cpu/kernel/conv2d.py:26,30).  Source layout
+ * [c_out/16][c_in/c_block][kh][kw][c_block/4][16][4] s8. */
+size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *desc);
+int unit_pack_weights_conv_i8(const unit_conv_desc *desc, const int8_t *d_w,
+                              void *d_packed, void *stream);
+
+/* Source layout [c_out/16][c_in/16][kh][kw][16 i][16 o] fp16
+ * (python/tensorizer/ops/gpu.py:29-31). */
+size_t unit_packed_weights_bytes_conv_f16(const unit_conv_desc *desc);
+int unit_pack_weights_conv_f16(const unit_conv_desc *desc, const void *d_w,
+                               void *d_packed, void *stream);
+
+/* Source layout [n/tile][k/4][tile][4] s8 (apps/cpu/kernel/int8-gemm.py:11-14). */
+size_t unit_packed_weights_bytes_dense_i8(int32_t n, int32_t k);
+int unit_pack_weights_dense_i8(int32_t n, int32_t k, int32_t tile, const int8_t *d_b,
+                               void *d_packed, void *stream);
+
+/* Source layout B[k][n] fp16 row-major (apps/gpu/gemm.py:8). */
+size_t unit_packed_weights_bytes_gemm_f16(int32_t n, int32_t k);
+int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *d_b,
+                               void *d_packed, void *stream);
+
+/* ---- contractions -------------------------------------------------------- */
+
+/* Replaces topi.nn.conv2d_NCHWc_int8(..., out_dtype='int32') scheduled with
+ * INTRINSICS['vnni'] (apps/cpu/kernel/conv2d.py:50-54).  d_out is s32
+ * [n][c_out/16][oh][ow][16]; d_bias (c_out s32) may be NULL. */
+int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
+                              const void *d_packed_w, const int32_t *d_bias,
+                              int32_t *d_out, void *stream);
+
+/* Same contraction with the fused epilogue
+ *   q = clamp((acc + bias[oc] + 2^(shift-1)) >> shift, 0, 255)  -> u8 NCHW16c.
+ * Replaces the fused conv + bias + scale operator of the reference's graph
+ * flow (apps/cpu/relay/conv2d.py:16-27).  1 <= shift <= 31. */
+int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
+                                   const void *d_packed_w, const int32_t *d_bias,
+                                   int32_t shift, uint8_t *d_out, void *stream);
+
+/* Replaces topi.x86.dense_dotprod(a, b_packed, None, 'int32')
+ * (apps/cpu/kernel/int8-gemm.py:16).  A is u8 [m][k] with row pitch lda
+ * bytes, C is s32 [m][n] with row pitch ldc elements. */
+int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *d_a, int64_t lda,
+                       const void *d_packed_w, int32_t *d_c, int64_t ldc, void *stream);
+
+/* Replaces conv2d_NCHW16c_OHWI16o (python/tensorizer/ops/gpu.py:8-58).
+ * d_x fp16 NCHW16c, d_out fp32 NCHW16c; desc->c_block must be 16. */
+int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *desc, const void *d_x,
+                               const void *d_packed_w, float *d_out, void *stream);
+
+/* Replaces the tensor-core GEMM of apps/gpu/gemm.py:6-19 and
+ * poc/tensorcore/gemm-prefetch.cu:66-164.  A fp16 [m][k] (row pitch lda
+ * bytes), C fp32 [m][n] (row pitch ldc elements). */
+int unit_gemm_f16f32(int32_t m, int32_t n, int32_t k, const void *d_a, int64_t lda,
+                     const void *d_packed_w, float *d_c, int64_t ldc, void *stream);
+
+/* ---- layout transforms --------------------------------------------------- */
+
+/* Replaces the in-graph pack of python/tensorizer/ops/gpu.py:26-28 and the
+ * layout_transform chain of the graph flow.  NCHW (c channels) ->
+ * [n][ceil(c/c_block)][h][w][c_block], missing channels zero; elem_bytes is
+ * 1 (u8) or 2 (fp16) or 4 (s32 / fp32). */
+int unit_pack_data_nchw_to_nchwc(const void *d_src, void *d_dst, int32_t n, int32_t c,
+                                 int32_t h, int32_t w, int32_t c_block, int32_t elem_bytes,
+                                 void *stream);
+/* Inverse: blocked -> NCHW, keeping the first c channels. */
+int unit_unpack_data_nchwc_to_nchw(const void *d_src, void *d_dst, int32_t n, int32_t c,
+                                   int32_t h, int32_t w, int32_t c_block, int32_t elem_bytes,
+                                   void *stream);
+/* OIHW s8 -> [o/16][i/c_block][kh][kw][c_block/4][16][4], zero padded
+ * (the array apps/cpu/kernel/conv2d.py:26,30 declares). */
+int unit_pack_weights_oihw_to_ref_i8(const int8_t *d_src, int8_t *d_dst, int32_t o, int32_t i,
+                                     int32_t kh, int32_t kw, int32_t c_block, void *stream);
+/* OIHW fp16 -> [o/16][i/16][kh][kw][16 i][16 o] (python/tensorizer/ops/gpu.py:29-31). */
+int unit_pack_weights_oihw_to_ref_f16(const void *d_src, void *d_dst, int32_t o, int32_t i,
+                                      int32_t kh, int32_t kw, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UNIT_B200_H_ */

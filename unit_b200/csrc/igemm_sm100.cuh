@@ -1,0 +1,542 @@
+// Implicit-GEMM contraction kernel for sm_100a: tcgen05.mma with the accumulator
+// in tensor memory, a warp-specialised producer / issuer / drain pipeline, and a
+// persistent tile loop (one CTA per SM).
+//
+// GEMM view of every operator this library offers:
+//   D[m][n] = sum_k A[m][k] * B[n][k]
+//   m : output pixel (n_img, oh, ow) flattened, or a row of a plain matrix
+//   n : output channel
+//   k : (kh, kw, input channel), or the K index of a plain matrix
+// K is cut into 16-byte "columns" (16 u8 or 8 fp16 values of one m or n row).
+//
+// Shared-memory operand format: the tensor core's K-major, no-swizzle layout.
+// A "core matrix" is 8 rows x 16 bytes stored as 128 contiguous bytes; a tile
+// of R rows and KC columns is stored column by column, [KC][R][16 B], so
+//   stride between 8-row groups (SBO)     = 128 bytes
+//   stride between adjacent K columns (LBO) = R * 16 bytes.
+// NCHW16c activations fit this format natively: 16 channels of one u8 pixel
+// are one 16-byte core-matrix row and consecutive pixels of an image row are
+// consecutive rows, so the A tile is gathered by 16-byte cp.async copies with
+// zero fill for padding taps and rows past the end.  Weights are repacked once
+// on the device into ready-made [KC][BN][16 B] stage blocks and arrive with a
+// single bulk copy (cp.async.bulk, no tensor map, no multicast) per stage.
+//
+// Warp roles (320 threads):
+//   warps 0-3  drain: tcgen05.ld the finished accumulator (warp w owns TMEM
+//              lanes 32w..32w+31 = tile rows), apply the epilogue, store
+//   warps 4-7  A producers: 128 threads gather A columns with cp.async
+//   warp  8    B producer: one lane issues the bulk copies
+//   warp  9    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
+// Two accumulators (2 x BN <= 512 TMEM columns) let the drain of tile i overlap
+// the main loop of tile i+1.
+//
+// Every wait on an mbarrier is bounded in time.  A wait that runs out sets a
+// CTA-wide abort flag and a global error word; all roles then leave their
+// loops, let their own copies land, and the CTA frees its TMEM and returns.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace unit {
+
+enum AMode : int {
+  A_CONV_I8 = 0,   // u8 NCHW16c: one 16-byte column = one channel chunk of one tap
+  A_CONV_F16 = 1,  // fp16 NCHW16c: one chunk = two 16-byte columns
+  A_STEM_I8 = 2,   // u8 NCHW4c: one column = 4 consecutive kw taps x 4 channels
+  A_DENSE = 3      // plain row-major matrix, K contiguous
+};
+enum EpiMode : int {
+  EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
+  EPI_REQ_NCHWC = 1,  // + bias, round-shift, clamp -> u8 [n][oc/16][oh][ow][16]
+  EPI_RAW_ROWS = 2    // 32-bit accumulator -> row-major [m][n]
+};
+
+constexpr int kTileM = 128;
+constexpr int kMaxStages = 12;
+constexpr int kLag = 2;  // cp.async groups a producer keeps in flight
+constexpr int kNumThreads = 320;
+constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
+
+struct IgemmParams {
+  const uint8_t *a;   // activations / A matrix
+  const uint8_t *b;   // packed weights
+  void *out;
+  const int32_t *bias;
+  unsigned int *err;  // global error word (0 = fine)
+  long long m_total;  // GEMM rows
+  int n_total;        // GEMM columns actually stored (multiple of 16)
+  int bn;             // N tile (multiple of 16, <= 256)
+  int kc;             // 16-byte K columns per pipeline stage (even)
+  int cols;           // real K columns
+  int k_stages;       // ceil(cols_padded / kc)
+  int last_ksteps;    // MMA K-steps (2 columns each) in the last stage
+  int stages;         // pipeline depth
+  int m_tiles, n_tiles;
+  // convolution geometry (unused by A_DENSE)
+  int H, W, Cc, OH, OW, KH, KW, sh, sw, ph, pw;
+  int kwg;            // A_STEM_I8: groups of 4 kw taps per kh
+  long long img_bytes;  // bytes of one input image
+  long long lda;      // A_DENSE: row pitch in bytes
+  long long ldc;      // EPI_RAW_ROWS: row pitch in elements
+  int shift;          // EPI_REQ_NCHWC
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after ~1 s (or when another role already aborted).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          unsigned int *err, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 0; it < (1u << 28); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > 1000000000ull) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(err, 0u, code);
+  return false;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+template <bool F16>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if constexpr (F16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle.
+//   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
+//   bits 61-63 swizzle mode (0 = none)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// Instruction descriptor: D format bits 4-5 (1 = f32, 2 = s32), A format bits 7-9,
+// B format bits 10-12 (i8 kinds: 0 = u8, 1 = s8; f16 kind: 0 = fp16), both operands
+// K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+template <bool F16>
+__device__ __forceinline__ uint32_t make_idesc(int bn) {
+  uint32_t d = F16 ? (1u << 4) : ((2u << 4) | (0u << 7) | (1u << 10));
+  d |= (uint32_t)(bn >> 3) << 17;
+  d |= (uint32_t)(kTileM >> 4) << 24;
+  return d;
+}
+
+struct alignas(8) PipeShared {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long tfull[2];
+  unsigned long long tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <int AMODE, int EPI, bool F16>
+__global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t a_stage_bytes = (uint32_t)p.kc * kTileM * 16u;
+  const uint32_t b_stage_bytes = (uint32_t)p.kc * (uint32_t)p.bn * 16u;
+  const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
+  PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes);
+  const uint32_t smem_base = smem_u32(smem);
+  volatile int *abort_flag = &ps->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ps->full[s]), 4 + 1);  // 4 A-producer warps + the B producer
+      mbar_init(smem_u32(&ps->empty[s]), 1);     // one tcgen05.commit
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ps->tfull[i]), 1);   // one tcgen05.commit
+      mbar_init(smem_u32(&ps->tempty[i]), 4);  // 4 drain warps
+    }
+    ps->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&ps->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ps->tmem_base;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp >= 4 && warp < 8) {
+    // ===================== A producers =====================
+    const int pw = warp - 4;
+    uint32_t it = 0;  // stage iterations issued by this thread
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_tile = tile / p.n_tiles;
+      const long long m0 = (long long)m_tile * kTileM;
+
+      // rows this lane feeds and their decoded positions
+      constexpr int RPT = (AMODE == A_CONV_I8 || AMODE == A_STEM_I8) ? 1 : (AMODE == A_CONV_F16 ? 2 : 4);
+      int row[RPT];
+      bool rvalid[RPT];
+      const uint8_t *rbase[RPT];
+      int ih0[RPT], iw0[RPT];
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        if constexpr (AMODE == A_CONV_I8 || AMODE == A_STEM_I8) row[i] = pw * 32 + lane;
+        else if constexpr (AMODE == A_CONV_F16) row[i] = pw * 32 + i * 16 + (lane >> 4) * 8 + (lane & 7);
+        else row[i] = pw * 32 + i * 8 + (lane & 7);
+        const long long m = m0 + row[i];
+        rvalid[i] = m < p.m_total;
+        if constexpr (AMODE == A_DENSE) {
+          rbase[i] = p.a + (rvalid[i] ? m : 0) * p.lda;
+          ih0[i] = iw0[i] = 0;
+        } else {
+          const long long mm = rvalid[i] ? m : 0;
+          const int ohw = p.OH * p.OW;
+          const int n_img = (int)(mm / ohw);
+          const int rem = (int)(mm - (long long)n_img * ohw);
+          const int oh = rem / p.OW, ow = rem - oh * p.OW;
+          ih0[i] = oh * p.sh - p.ph;
+          iw0[i] = ow * p.sw - p.pw;
+          rbase[i] = p.a + (long long)n_img * p.img_bytes;
+        }
+      }
+
+      int ci = 0, kh = 0, kw = 0;  // position of the next K column (conv modes)
+      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+        const uint32_t s = it % (uint32_t)p.stages;
+        const uint32_t par = ((it / (uint32_t)p.stages) & 1u) ^ 1u;
+        if (!mbar_wait(smem_u32(&ps->empty[s]), par, abort_flag, p.err, kErrWaitEmpty)) {
+          alive = false;
+          break;
+        }
+        const uint32_t a_dst = smem_base + s * stage_bytes;
+        if constexpr (AMODE == A_CONV_I8) {
+          for (int jj = 0; jj < p.kc; ++jj) {
+            const int j = ks * p.kc + jj;
+            const int ih = ih0[0] + kh, iw = iw0[0] + kw;
+            const bool ok = rvalid[0] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+            const uint8_t *src = ok ? rbase[0] + ((long long)(ci * p.H + ih) * p.W + iw) * 16 : p.a;
+            cp_async16(a_dst + (uint32_t)jj * (kTileM * 16u) + (uint32_t)row[0] * 16u, src, ok ? 16u : 0u);
+            if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
+          }
+        } else if constexpr (AMODE == A_CONV_F16) {
+          const int half = (lane >> 3) & 1;
+          for (int jj = 0; jj < p.kc; jj += 2) {
+            const int j = ks * p.kc + jj;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int ih = ih0[i] + kh, iw = iw0[i] + kw;
+              const bool ok = rvalid[i] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+              const uint8_t *src = ok ? rbase[i] + ((long long)(ci * p.H + ih) * p.W + iw) * 32 + half * 16 : p.a;
+              cp_async16(a_dst + (uint32_t)(jj + half) * (kTileM * 16u) + (uint32_t)row[i] * 16u, src, ok ? 16u : 0u);
+            }
+            if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
+          }
+        } else if constexpr (AMODE == A_STEM_I8) {
+          // column = (ci, kh, group of 4 kw taps); ci / kh / kw track (chunk, kh, group)
+          for (int jj = 0; jj < p.kc; ++jj) {
+            const int j = ks * p.kc + jj;
+            const int ih = ih0[0] + kh;
+            const bool rok = rvalid[0] && j < p.cols && (unsigned)ih < (unsigned)p.H;
+            const uint32_t dst = a_dst + (uint32_t)jj * (kTileM * 16u) + (uint32_t)row[0] * 16u;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int tap = kw * 4 + t;
+              const int iw = iw0[0] + tap;
+              const bool ok = rok && tap < p.KW && (unsigned)iw < (unsigned)p.W;
+              const uint8_t *src = ok ? rbase[0] + ((long long)(ci * p.H + ih) * p.W + iw) * 4 : p.a;
+              cp_async4(dst + t * 4u, src, ok ? 4u : 0u);
+            }
+            if (++kw == p.kwg) { kw = 0; if (++kh == p.KH) { kh = 0; ++ci; } }
+          }
+        } else {  // A_DENSE: 8 rows x 4 columns per warp instruction
+          const int csub = lane >> 3;
+          for (int jj = 0; jj < p.kc; jj += 4) {
+            const int jl = jj + csub;
+            const int j = ks * p.kc + jl;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const bool ok = rvalid[i] && j < p.cols && jl < p.kc;
+              const uint8_t *src = ok ? rbase[i] + (long long)j * 16 : p.a;
+              if (jl < p.kc)
+                cp_async16(a_dst + (uint32_t)jl * (kTileM * 16u) + (uint32_t)row[i] * 16u, src, ok ? 16u : 0u);
+            }
+          }
+        }
+        cp_async_commit();
+        if (it >= (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ps->full[(it - kLag) % (uint32_t)p.stages]));
+        }
+      }
+    }
+    // hand over the stages still in flight
+    cp_async_wait<0>();
+    fence_proxy_async();
+    __syncwarp();
+    if (alive && lane == 0) {
+      const uint32_t first = it >= (uint32_t)kLag ? it - kLag : 0u;
+      for (uint32_t q = first; q < it; ++q) mbar_arrive(smem_u32(&ps->full[q % (uint32_t)p.stages]));
+    }
+  } else if (warp == 8) {
+    // ===================== B producer =====================
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int n_tile = tile % p.n_tiles;
+        const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const uint32_t s = it % (uint32_t)p.stages;
+          const uint32_t par = ((it / (uint32_t)p.stages) & 1u) ^ 1u;
+          if (!mbar_wait(smem_u32(&ps->empty[s]), par, abort_flag, p.err, kErrWaitEmpty)) {
+            alive = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&ps->full[s]);
+          mbar_arrive_expect_tx(bar, b_stage_bytes);
+          bulk_copy_g2s(smem_base + s * stage_bytes + a_stage_bytes, src + (size_t)ks * b_stage_bytes,
+                        b_stage_bytes, bar);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<F16>(p.bn);
+      uint32_t it = 0;
+      uint32_t lt = 0;  // tiles done by this CTA
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+        const uint32_t acc = lt & 1u;
+        if (!mbar_wait(smem_u32(&ps->tempty[acc]), ((lt >> 1) & 1u) ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.bn;
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const uint32_t s = it % (uint32_t)p.stages;
+          if (!mbar_wait(smem_u32(&ps->full[s]), (it / (uint32_t)p.stages) & 1u, abort_flag, p.err, kErrWaitFull)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * stage_bytes;
+          const uint32_t b_addr = a_addr + a_stage_bytes;
+          const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
+          for (int k = 0; k < nk; ++k) {
+            const uint64_t adesc = make_smem_desc(a_addr + (uint32_t)k * 2u * (kTileM * 16u), kTileM * 16u, 128u);
+            const uint64_t bdesc =
+                make_smem_desc(b_addr + (uint32_t)k * 2u * ((uint32_t)p.bn * 16u), (uint32_t)p.bn * 16u, 128u);
+            tc_mma<F16>(d_tmem, adesc, bdesc, idesc, (ks | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
+        }
+        if (alive) tc_commit(smem_u32(&ps->tfull[acc]));  // accumulator complete
+      }
+    }
+  } else {
+    // ===================== drain (warps 0-3) =====================
+    uint32_t lt = 0;
+    bool alive = true;
+    const int ohw = p.OH * p.OW;
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+      const int m_tile = tile / p.n_tiles;
+      const int n_tile = tile % p.n_tiles;
+      const uint32_t acc = lt & 1u;
+      if (!mbar_wait(smem_u32(&ps->tfull[acc]), (lt >> 1) & 1u, abort_flag, p.err, kErrWaitTmemFull)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      const long long m = (long long)m_tile * kTileM + warp * 32 + lane;
+      const bool mvalid = m < p.m_total;
+      long long obase = 0;  // element offset of this row's first stored value
+      if constexpr (EPI == EPI_RAW_ROWS) {
+        obase = m * p.ldc + (long long)n_tile * p.bn;
+      } else {
+        const long long mm = mvalid ? m : 0;
+        const long long n_img = mm / ohw;
+        const long long rem = mm - n_img * ohw;
+        // [n][oc/16][ohw][16]: chunk g of this tile adds g * ohw * 16
+        obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
+      }
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.bn;
+      const int groups = p.bn >> 4;
+      for (int g = 0; g < groups; ++g) {
+        uint32_t v[16];
+        tmem_ld16(t_row + (uint32_t)g * 16u, v);
+        tmem_ld_wait();
+        const int col0 = n_tile * p.bn + g * 16;
+        if (!mvalid || col0 >= p.n_total) continue;
+        if constexpr (EPI == EPI_RAW_ROWS) {
+          uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + obase + g * 16);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+          int32_t bv[16];
+          if (p.bias != nullptr) {
+            const int4 *bp = reinterpret_cast<const int4 *>(p.bias + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int4 t = __ldg(bp + q);
+              bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) bv[q] = 0;
+          }
+          const long long o = obase + (long long)g * ohw * 16;
+          if constexpr (EPI == EPI_RAW_NCHWC) {
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_uint4(v[4 * q] + (uint32_t)bv[4 * q], v[4 * q + 1] + (uint32_t)bv[4 * q + 1],
+                                  v[4 * q + 2] + (uint32_t)bv[4 * q + 2], v[4 * q + 3] + (uint32_t)bv[4 * q + 3]);
+          } else {
+            uint32_t w[4];
+            const long long rnd = 1ll << (p.shift - 1);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t packed = 0;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                // 64-bit sum so that acc + bias + rounding cannot wrap
+                long long t = (long long)(int32_t)v[4 * q + e] + (long long)bv[4 * q + e] + rnd;
+                t >>= p.shift;
+                t = t < 0 ? 0 : (t > 255 ? 255 : t);
+                packed |= (uint32_t)t << (8 * e);
+              }
+              w[q] = packed;
+            }
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[acc]));
+    }
+  }
+
+  // ===================== teardown =====================
+  if (*abort_flag) {
+    // let copies this CTA issued land before its shared memory is released
+    cp_async_wait<0>();
+    for (int i = 0; i < 50; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace unit

@@ -1,0 +1,563 @@
+// C ABI of unit_b200: argument checking, tile selection, weight packing and
+// layout kernels, and the launches of the implicit-GEMM kernel.
+#include "../../include/unit_b200.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "igemm_sm100.cuh"
+
+namespace unit {
+
+__device__ unsigned int g_error_word = 0;
+static std::atomic<uint64_t> g_launches{0};
+
+// ---------------------------------------------------------------------------
+// tile selection (a pure function of the problem, shared by pack and launch)
+// ---------------------------------------------------------------------------
+struct TileCfg {
+  int bn = 0, kc = 0, cols = 0, cols_pad = 0, k_stages = 0, last_ksteps = 0, n_tiles = 0, stages = 0;
+  size_t b_stage_bytes = 0, smem_bytes = 0;
+};
+
+constexpr size_t kSmemBudget = 200 * 1024;
+
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static TileCfg make_cfg(int n_total, int cols) {
+  TileCfg c;
+  c.cols = cols;
+  c.cols_pad = round_up(cols, 2);
+  c.n_tiles = (n_total + 255) / 256;
+  c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
+  static const int cand[] = {8, 6, 4, 12, 10, 14, 16};
+  c.kc = 8;
+  for (int kc : cand)
+    if (c.cols_pad % kc == 0) { c.kc = kc; break; }
+  if (c.cols_pad < c.kc) c.kc = c.cols_pad;
+  c.k_stages = (c.cols_pad + c.kc - 1) / c.kc;
+  const int last_cols = c.cols_pad - (c.k_stages - 1) * c.kc;
+  c.last_ksteps = last_cols / 2;
+  c.b_stage_bytes = (size_t)c.kc * c.bn * 16;
+  const size_t stage = (size_t)c.kc * 16 * (kTileM + c.bn);
+  int s = (int)(kSmemBudget / stage);
+  if (s > kMaxStages) s = kMaxStages;
+  if (s < kLag + 1) s = kLag + 1;
+  c.stages = s;
+  c.smem_bytes = (size_t)s * stage + sizeof(PipeShared) + 128;
+  return c;
+}
+
+static int conv_cols_i8(const unit_conv_desc *d) {
+  if (d->c_block == 16) return d->kh * d->kw * (d->c_in / 16);
+  return (d->c_in / 4) * d->kh * ((d->kw + 3) / 4);
+}
+static int conv_cols_f16(const unit_conv_desc *d) { return d->kh * d->kw * (d->c_in / 16) * 2; }
+
+static int check_conv(const unit_conv_desc *d, bool f16) {
+  if (!d) return UNIT_ERR_NULL;
+  if (d->n < 1 || d->c_in < 1 || d->h < 1 || d->w < 1 || d->c_out < 1 || d->kh < 1 || d->kw < 1 ||
+      d->stride_h < 1 || d->stride_w < 1 || d->pad_h < 0 || d->pad_w < 0)
+    return UNIT_ERR_SHAPE;
+  if (d->c_block != 16 && !(d->c_block == 4 && !f16)) return UNIT_ERR_LAYOUT;
+  if (d->c_in % d->c_block || d->c_out % 16) return UNIT_ERR_LAYOUT;
+  if (d->h + 2 * d->pad_h < d->kh || d->w + 2 * d->pad_w < d->kw) return UNIT_ERR_SHAPE;
+  if (d->kh > 64 || d->kw > 64) return UNIT_ERR_SHAPE;
+  const long long img = (long long)d->c_in * d->h * d->w * (f16 ? 2 : 1);
+  if (img >= (1ll << 31)) return UNIT_ERR_TOO_LARGE;
+  return UNIT_OK;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_arch() {
+  static std::once_flag once;
+  static int cached[64];
+  static int ndev = 0;
+  std::call_once(once, [] {
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess) ndev = 0;
+    if (ndev > 64) ndev = 64;
+    for (int i = 0; i < ndev; ++i) {
+      int major = 0, minor = 0;
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, i);
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, i);
+      cached[i] = (major == 10 && minor == 0) ? UNIT_OK : UNIT_ERR_ARCH;
+    }
+  });
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= ndev) return UNIT_ERR_ARCH;
+  return cached[dev];
+}
+
+static int sm_count() {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+// ---------------------------------------------------------------------------
+// weight packing: reference layouts -> [n_tile][k_stage][kc][bn][16 B] blocks
+// ---------------------------------------------------------------------------
+enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4 };
+
+struct PackParams {
+  const uint8_t *src;
+  uint4 *dst;
+  int mode, n_total, bn, kc, cols, k_stages, n_tiles;
+  int Cc, KH, KW, kwg;  // conv
+  int K, T;             // dense / gemm (K in elements)
+};
+
+__global__ void pack_weights_kernel(const PackParams p) {
+  const long long total = (long long)p.n_tiles * p.k_stages * p.kc * p.bn;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(idx % p.bn);
+    long long t = idx / p.bn;
+    const int jj = (int)(t % p.kc);
+    t /= p.kc;
+    const int ks = (int)(t % p.k_stages);
+    const int n_tile = (int)(t / p.k_stages);
+    const int oc = n_tile * p.bn + row;
+    const int j = ks * p.kc + jj;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if (oc < p.n_total && j < p.cols) {
+      if (p.mode == PACK_CONV_I8) {
+        const int tap = j / p.Cc, ci = j % p.Cc;
+        const int kh = tap / p.KW, kw = tap % p.KW;
+        // [oc/16][ci][kh][kw][m][oc%16][r]
+        const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15) * 4;
+        for (int m = 0; m < 4; ++m) w[m] = *reinterpret_cast<const uint32_t *>(s + m * 64);
+      } else if (p.mode == PACK_STEM_I8) {
+        const int g = j % p.kwg;
+        const int t2 = j / p.kwg;
+        const int kh = t2 % p.KH, ci = t2 / p.KH;
+        for (int q = 0; q < 4; ++q) {
+          const int kw = g * 4 + q;
+          if (kw < p.KW) {
+            // [oc/16][ci][kh][kw][0][oc%16][r]
+            const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 64 + (oc & 15) * 4;
+            w[q] = *reinterpret_cast<const uint32_t *>(s);
+          }
+        }
+      } else if (p.mode == PACK_CONV_F16) {
+        const int chunk = j >> 1, half = j & 1;
+        const int tap = chunk / p.Cc, ci = chunk % p.Cc;
+        const int kh = tap / p.KW, kw = tap % p.KW;
+        // [oc/16][ci][kh][kw][i][o]
+        const uint16_t *s = reinterpret_cast<const uint16_t *>(p.src) +
+                            ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t lo = s[(half * 8 + 2 * q) * 16], hi = s[(half * 8 + 2 * q + 1) * 16];
+          w[q] = lo | (hi << 16);
+        }
+      } else if (p.mode == PACK_DENSE_I8) {
+        // [n/T][k/4][T][4]
+        const uint8_t *s = p.src + ((size_t)(oc / p.T) * (p.K / 4)) * p.T * 4 + (size_t)(oc % p.T) * 4;
+        for (int q = 0; q < 4; ++q) w[q] = *reinterpret_cast<const uint32_t *>(s + (size_t)(j * 4 + q) * p.T * 4);
+      } else {  // PACK_GEMM_F16: B[k][n]
+        const uint16_t *s = reinterpret_cast<const uint16_t *>(p.src);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t lo = s[(size_t)(j * 8 + 2 * q) * p.n_total + oc];
+          const uint32_t hi = s[(size_t)(j * 8 + 2 * q + 1) * p.n_total + oc];
+          w[q] = lo | (hi << 16);
+        }
+      }
+    }
+    p.dst[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+static int launch_pack(const PackParams &pp, cudaStream_t st) {
+  const long long total = (long long)pp.n_tiles * pp.k_stages * pp.kc * pp.bn;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  pack_weights_kernel<<<(unsigned)blocks, 256, 0, st>>>(pp);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------
+// layout kernels (bandwidth work: one 16-byte store per thread)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void nchw_to_nchwc_kernel(const T *__restrict__ src, T *__restrict__ dst, int n, int c, int h, int w,
+                                     int cb) {
+  // one thread = one (pixel, channel block): reads cb strided values, writes cb contiguous
+  const int cc = (c + cb - 1) / cb;
+  const long long hw = (long long)h * w;
+  const long long total = (long long)n * cc * hw;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long pix = idx % hw;
+    const long long t = idx / hw;
+    const int chunk = (int)(t % cc);
+    const long long img = t / cc;
+    T *d = dst + idx * cb;
+    for (int k = 0; k < cb; ++k) {
+      const int ch = chunk * cb + k;
+      d[k] = ch < c ? src[(img * c + ch) * hw + pix] : T(0);
+    }
+  }
+}
+
+template <typename T>
+__global__ void nchwc_to_nchw_kernel(const T *__restrict__ src, T *__restrict__ dst, int n, int c, int h, int w,
+                                     int cb) {
+  const int cc = (c + cb - 1) / cb;
+  const long long hw = (long long)h * w;
+  const long long total = (long long)n * c * hw;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long pix = idx % hw;
+    const long long t = idx / hw;
+    const int ch = (int)(t % c);
+    const long long img = t / c;
+    dst[idx] = src[((img * cc + ch / cb) * hw + pix) * cb + ch % cb];
+  }
+}
+
+__global__ void oihw_to_ref_i8_kernel(const int8_t *__restrict__ src, int8_t *__restrict__ dst, int o, int i, int kh,
+                                      int kw, int cb) {
+  const int oc = (o + 15) / 16, icc = (i + cb - 1) / cb, c4 = cb / 4;
+  const long long total = (long long)oc * icc * kh * kw * c4 * 64;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long t = idx;
+    const int r = (int)(t % 4); t /= 4;
+    const int l = (int)(t % 16); t /= 16;
+    const int m = (int)(t % c4); t /= c4;
+    const int x = (int)(t % kw); t /= kw;
+    const int y = (int)(t % kh); t /= kh;
+    const int ic = (int)(t % icc);
+    const int ob = (int)(t / icc);
+    const int och = ob * 16 + l, ich = ic * cb + m * 4 + r;
+    dst[idx] = (och < o && ich < i) ? src[(((size_t)och * i + ich) * kh + y) * kw + x] : (int8_t)0;
+  }
+}
+
+__global__ void oihw_to_ref_f16_kernel(const uint16_t *__restrict__ src, uint16_t *__restrict__ dst, int o, int i,
+                                       int kh, int kw) {
+  const int oc = (o + 15) / 16, icc = (i + 15) / 16;
+  const long long total = (long long)oc * icc * kh * kw * 256;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long t = idx;
+    const int ob = (int)(t % 16); t /= 16;
+    const int ib = (int)(t % 16); t /= 16;
+    const int x = (int)(t % kw); t /= kw;
+    const int y = (int)(t % kh); t /= kh;
+    const int ic = (int)(t % icc);
+    const int occ = (int)(t / icc);
+    const int och = occ * 16 + ob, ich = ic * 16 + ib;
+    dst[idx] = (och < o && ich < i) ? src[(((size_t)och * i + ich) * kh + y) * kw + x] : (uint16_t)0;
+  }
+}
+
+static unsigned grid_for(long long total) {
+  long long b = (total + 255) / 256;
+  if (b > 148 * 32) b = 148 * 32;
+  if (b < 1) b = 1;
+  return (unsigned)b;
+}
+
+// ---------------------------------------------------------------------------
+// launches of the contraction kernel
+// ---------------------------------------------------------------------------
+template <int AMODE, int EPI, bool F16>
+static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st) {
+  static std::once_flag once[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = igemm_kernel<AMODE, EPI, F16>;
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  });
+  if (attr_err != cudaSuccess) return UNIT_ERR_LAUNCH;
+  p.bn = c.bn;
+  p.kc = c.kc;
+  p.cols = c.cols;
+  p.k_stages = c.k_stages;
+  p.last_ksteps = c.last_ksteps;
+  p.stages = c.stages;
+  p.n_tiles = c.n_tiles;
+  p.m_tiles = (int)((p.m_total + kTileM - 1) / kTileM);
+  void *err_ptr = nullptr;
+  if (cudaGetSymbolAddress(&err_ptr, g_error_word) != cudaSuccess) return UNIT_ERR_LAUNCH;
+  p.err = static_cast<unsigned int *>(err_ptr);
+  long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  kern<<<grid, kNumThreads, c.smem_bytes, st>>>(p);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
+  p.H = d->h; p.W = d->w; p.Cc = d->c_in / d->c_block;
+  p.KH = d->kh; p.KW = d->kw; p.sh = d->stride_h; p.sw = d->stride_w; p.ph = d->pad_h; p.pw = d->pad_w;
+  p.OH = (d->h + 2 * d->pad_h - d->kh) / d->stride_h + 1;
+  p.OW = (d->w + 2 * d->pad_w - d->kw) / d->stride_w + 1;
+  p.kwg = (d->kw + 3) / 4;
+  p.img_bytes = (long long)d->c_in * d->h * d->w * elem_bytes;
+  p.m_total = (long long)d->n * p.OH * p.OW;
+  p.n_total = d->c_out;
+}
+
+static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias, int shift,
+                   void *out, bool requant, cudaStream_t st) {
+  int rc = check_conv(d, false);
+  if (rc) return rc;
+  if (!x || !pw || !out) return UNIT_ERR_NULL;
+  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (bias && !aligned16(bias))) return UNIT_ERR_ALIGN;
+  if (requant && (shift < 1 || shift > 31)) return UNIT_ERR_SHAPE;
+  if ((rc = check_arch())) return rc;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  IgemmParams p{};
+  p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
+  fill_conv(p, d, 1);
+  if (d->c_block == 16)
+    return requant ? launch_igemm<A_CONV_I8, EPI_REQ_NCHWC, false>(p, c, st)
+                   : launch_igemm<A_CONV_I8, EPI_RAW_NCHWC, false>(p, c, st);
+  return requant ? launch_igemm<A_STEM_I8, EPI_REQ_NCHWC, false>(p, c, st)
+                 : launch_igemm<A_STEM_I8, EPI_RAW_NCHWC, false>(p, c, st);
+}
+
+}  // namespace unit
+
+using namespace unit;
+
+extern "C" {
+
+int unit_version(void) { return 100; }
+
+const char *unit_status_string(int s) {
+  switch (s) {
+    case UNIT_OK: return "ok";
+    case UNIT_ERR_NULL: return "null pointer";
+    case UNIT_ERR_SHAPE: return "unsupported shape";
+    case UNIT_ERR_ALIGN: return "pointer or pitch not 16-byte aligned";
+    case UNIT_ERR_LAYOUT: return "unsupported channel block or tile";
+    case UNIT_ERR_ARCH: return "device is not compute capability 10.0 (sm_100a)";
+    case UNIT_ERR_LAUNCH: return "CUDA launch or copy failed";
+    case UNIT_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait";
+    case UNIT_ERR_TOO_LARGE: return "beyond a fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+int unit_device_status(void *stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaStreamSynchronize(st) != cudaSuccess) return UNIT_ERR_LAUNCH;
+  unsigned int w = 0;
+  if (cudaMemcpyFromSymbol(&w, g_error_word, sizeof(w)) != cudaSuccess) return UNIT_ERR_LAUNCH;
+  if (w != 0) {
+    const unsigned int zero = 0;
+    cudaMemcpyToSymbol(g_error_word, &zero, sizeof(zero));
+    return UNIT_ERR_DEVICE_WAIT;
+  }
+  return UNIT_OK;
+}
+
+uint64_t unit_launch_count(void) { return g_launches.load(); }
+
+// ---- packed weights --------------------------------------------------------
+size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
+  if (check_conv(d, false)) return 0;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+}
+
+int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *packed, void *stream) {
+  int rc = check_conv(d, false);
+  if (rc) return rc;
+  if (!w || !packed) return UNIT_ERR_NULL;
+  if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  PackParams pp{};
+  pp.src = reinterpret_cast<const uint8_t *>(w);
+  pp.dst = static_cast<uint4 *>(packed);
+  pp.mode = d->c_block == 16 ? PACK_CONV_I8 : PACK_STEM_I8;
+  pp.n_total = d->c_out; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
+  pp.Cc = d->c_in / d->c_block; pp.KH = d->kh; pp.KW = d->kw; pp.kwg = (d->kw + 3) / 4;
+  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+}
+
+size_t unit_packed_weights_bytes_conv_f16(const unit_conv_desc *d) {
+  if (check_conv(d, true)) return 0;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+}
+
+int unit_pack_weights_conv_f16(const unit_conv_desc *d, const void *w, void *packed, void *stream) {
+  int rc = check_conv(d, true);
+  if (rc) return rc;
+  if (!w || !packed) return UNIT_ERR_NULL;
+  if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  PackParams pp{};
+  pp.src = static_cast<const uint8_t *>(w);
+  pp.dst = static_cast<uint4 *>(packed);
+  pp.mode = PACK_CONV_F16;
+  pp.n_total = d->c_out; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
+  pp.Cc = d->c_in / 16; pp.KH = d->kh; pp.KW = d->kw;
+  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+}
+
+size_t unit_packed_weights_bytes_dense_i8(int32_t n, int32_t k) {
+  if (n < 16 || n % 16 || k < 16 || k % 16) return 0;
+  const TileCfg c = make_cfg(n, k / 16);
+  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+}
+
+int unit_pack_weights_dense_i8(int32_t n, int32_t k, int32_t tile, const int8_t *b, void *packed, void *stream) {
+  if (n < 16 || n % 16 || k < 16 || k % 16) return UNIT_ERR_SHAPE;
+  if (tile < 1 || n % tile) return UNIT_ERR_LAYOUT;
+  if (!b || !packed) return UNIT_ERR_NULL;
+  if (!aligned16(b) || !aligned16(packed)) return UNIT_ERR_ALIGN;
+  const TileCfg c = make_cfg(n, k / 16);
+  PackParams pp{};
+  pp.src = reinterpret_cast<const uint8_t *>(b);
+  pp.dst = static_cast<uint4 *>(packed);
+  pp.mode = PACK_DENSE_I8;
+  pp.n_total = n; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
+  pp.K = k; pp.T = tile;
+  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+}
+
+size_t unit_packed_weights_bytes_gemm_f16(int32_t n, int32_t k) {
+  if (n < 16 || n % 16 || k < 8 || k % 8) return 0;
+  const TileCfg c = make_cfg(n, k / 8);
+  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+}
+
+int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *b, void *packed, void *stream) {
+  if (n < 16 || n % 16 || k < 8 || k % 8) return UNIT_ERR_SHAPE;
+  if (!b || !packed) return UNIT_ERR_NULL;
+  if (!aligned16(b) || !aligned16(packed)) return UNIT_ERR_ALIGN;
+  const TileCfg c = make_cfg(n, k / 8);
+  PackParams pp{};
+  pp.src = static_cast<const uint8_t *>(b);
+  pp.dst = static_cast<uint4 *>(packed);
+  pp.mode = PACK_GEMM_F16;
+  pp.n_total = n; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
+  pp.K = k;
+  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+}
+
+// ---- contractions ------------------------------------------------------------
+int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
+                              int32_t *out, void *stream) {
+  return conv_i8(d, x, pw, bias, 0, out, false, static_cast<cudaStream_t>(stream));
+}
+
+int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
+                                   int32_t shift, uint8_t *out, void *stream) {
+  return conv_i8(d, x, pw, bias, shift, out, true, static_cast<cudaStream_t>(stream));
+}
+
+int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_t lda, const void *pw, int32_t *cmat,
+                       int64_t ldc, void *stream) {
+  if (m < 1 || n < 16 || n % 16 || k < 16 || k % 16) return UNIT_ERR_SHAPE;
+  if (!a || !pw || !cmat) return UNIT_ERR_NULL;
+  if (!aligned16(a) || !aligned16(pw) || !aligned16(cmat) || lda % 16 || lda < k || ldc % 4 || ldc < n)
+    return UNIT_ERR_ALIGN;
+  int rc = check_arch();
+  if (rc) return rc;
+  const TileCfg c = make_cfg(n, k / 16);
+  IgemmParams p{};
+  p.a = a; p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
+  p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
+  p.OH = p.OW = 1;
+  return launch_igemm<A_DENSE, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream));
+}
+
+int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const void *pw, float *out, void *stream) {
+  int rc = check_conv(d, true);
+  if (rc) return rc;
+  if (!x || !pw || !out) return UNIT_ERR_NULL;
+  if (!aligned16(x) || !aligned16(pw) || !aligned16(out)) return UNIT_ERR_ALIGN;
+  if ((rc = check_arch())) return rc;
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  IgemmParams p{};
+  p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out;
+  fill_conv(p, d, 2);
+  return launch_igemm<A_CONV_F16, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream));
+}
+
+int unit_gemm_f16f32(int32_t m, int32_t n, int32_t k, const void *a, int64_t lda, const void *pw, float *cmat,
+                     int64_t ldc, void *stream) {
+  if (m < 1 || n < 16 || n % 16 || k < 8 || k % 8) return UNIT_ERR_SHAPE;
+  if (!a || !pw || !cmat) return UNIT_ERR_NULL;
+  if (!aligned16(a) || !aligned16(pw) || !aligned16(cmat) || lda % 16 || lda < 2ll * k || ldc % 4 || ldc < n)
+    return UNIT_ERR_ALIGN;
+  int rc = check_arch();
+  if (rc) return rc;
+  const TileCfg c = make_cfg(n, k / 8);
+  IgemmParams p{};
+  p.a = static_cast<const uint8_t *>(a); p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
+  p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
+  p.OH = p.OW = 1;
+  return launch_igemm<A_DENSE, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream));
+}
+
+// ---- layout transforms ---------------------------------------------------------
+int unit_pack_data_nchw_to_nchwc(const void *src, void *dst, int32_t n, int32_t c, int32_t h, int32_t w, int32_t cb,
+                                 int32_t eb, void *stream) {
+  if (!src || !dst) return UNIT_ERR_NULL;
+  if (n < 1 || c < 1 || h < 1 || w < 1) return UNIT_ERR_SHAPE;
+  if (cb != 4 && cb != 16) return UNIT_ERR_LAYOUT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long total = (long long)n * ((c + cb - 1) / cb) * h * w;
+  const unsigned g = grid_for(total);
+  if (eb == 1) nchw_to_nchwc_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
+  else if (eb == 2) nchw_to_nchwc_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
+  else if (eb == 4) nchw_to_nchwc_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
+  else return UNIT_ERR_LAYOUT;
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+int unit_unpack_data_nchwc_to_nchw(const void *src, void *dst, int32_t n, int32_t c, int32_t h, int32_t w, int32_t cb,
+                                   int32_t eb, void *stream) {
+  if (!src || !dst) return UNIT_ERR_NULL;
+  if (n < 1 || c < 1 || h < 1 || w < 1) return UNIT_ERR_SHAPE;
+  if (cb != 4 && cb != 16) return UNIT_ERR_LAYOUT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned g = grid_for((long long)n * c * h * w);
+  if (eb == 1) nchwc_to_nchw_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
+  else if (eb == 2) nchwc_to_nchw_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
+  else if (eb == 4) nchwc_to_nchw_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
+  else return UNIT_ERR_LAYOUT;
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+int unit_pack_weights_oihw_to_ref_i8(const int8_t *src, int8_t *dst, int32_t o, int32_t i, int32_t kh, int32_t kw,
+                                     int32_t cb, void *stream) {
+  if (!src || !dst) return UNIT_ERR_NULL;
+  if (o < 1 || i < 1 || kh < 1 || kw < 1) return UNIT_ERR_SHAPE;
+  if (cb != 4 && cb != 16) return UNIT_ERR_LAYOUT;
+  const long long total = (long long)((o + 15) / 16) * ((i + cb - 1) / cb) * kh * kw * (cb / 4) * 64;
+  oihw_to_ref_i8_kernel<<<grid_for(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, dst, o, i, kh, kw, cb);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+int unit_pack_weights_oihw_to_ref_f16(const void *src, void *dst, int32_t o, int32_t i, int32_t kh, int32_t kw,
+                                      void *stream) {
+  if (!src || !dst) return UNIT_ERR_NULL;
+  if (o < 1 || i < 1 || kh < 1 || kw < 1) return UNIT_ERR_SHAPE;
+  const long long total = (long long)((o + 15) / 16) * ((i + 15) / 16) * kh * kw * 256;
+  oihw_to_ref_f16_kernel<<<grid_for(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint16_t *)src, (uint16_t *)dst, o, i, kh, kw);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+}  // extern "C"

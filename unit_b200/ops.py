@@ -1,0 +1,470 @@
+"""Operator entry points with the reference's names, argument order and layouts.
+
+Each function takes torch tensors (CUDA tensors, or host tensors which are
+copied to the current device and whose result is copied back), checks the
+layout contract, and calls the C ABI of ``libunit_b200.so`` with raw device
+pointers on torch's current stream.  torch is used for device memory and
+streams only; all arithmetic happens in the library's sm_100a kernels.
+
+Reference counterparts (paths inside were/UNIT):
+
+* ``conv2d_NCHWc_int8``  -- ``topi.nn.conv2d_NCHWc_int8`` as called in
+  apps/cpu/kernel/conv2d.py:50-51 and scheduled by ``INTRINSICS['vnni']``
+* ``dense_dotprod``      -- ``topi.x86.dense_dotprod`` as called in
+  apps/cpu/kernel/int8-gemm.py:16
+* ``conv2d_NCHW16c_OHWI16o`` / ``conv2d_NCHW16c_OHWI16o_compute`` --
+  python/tensorizer/ops/gpu.py:8-58
+* ``gemm_f16f32``        -- the tensor-core GEMM of apps/gpu/gemm.py:6-19
+* ``INTRINSICS``         -- the registry of python/tensorizer/intrinsics/intrinsics.py:7-40
+"""
+from __future__ import annotations
+
+import ctypes
+import weakref
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib
+from ._lib import ConvDesc, check
+
+IntPair = Union[int, Sequence[int]]
+
+
+def _pair(v: IntPair) -> Tuple[int, int]:
+    if isinstance(v, int):
+        return (v, v)
+    v = tuple(int(t) for t in v)
+    if len(v) == 1:
+        return (v[0], v[0])
+    if len(v) == 2:
+        return v
+    if len(v) == 4:  # (top, left, bottom, right), symmetric only
+        if v[0] != v[2] or v[1] != v[3]:
+            raise ValueError('asymmetric padding is not supported')
+        return (v[0], v[1])
+    raise ValueError(f'bad pair {v}')
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _require_cuda_lib():
+    if not torch.cuda.is_available():
+        raise RuntimeError('unit_b200 operators need a CUDA device (sm_100a); there is no CPU fallback')
+    return _lib.lib()
+
+
+def _to_device(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
+    if t.dtype != dtype:
+        raise TypeError(f'{name}: expected {dtype}, got {t.dtype}')
+    if not t.is_cuda:
+        t = t.cuda(non_blocking=True)
+    return t.contiguous()
+
+
+def device_status() -> None:
+    """Synchronise the current stream and raise if a kernel flagged an error."""
+    check(_lib.lib().unit_device_status(ctypes.c_void_p(_stream())), 'unit_device_status')
+
+
+def launch_count() -> int:
+    return int(_lib.lib().unit_launch_count())
+
+
+# --------------------------------------------------------------------------
+# packed weights
+# --------------------------------------------------------------------------
+class PackedWeights:
+    """Tensor-core-ready copy of one weight tensor (device buffer + the geometry it was packed for)."""
+
+    def __init__(self, kind: str, buf: torch.Tensor, key: tuple):
+        self.kind = kind
+        self.buf = buf
+        self.key = key
+
+    @property
+    def nbytes(self) -> int:
+        return self.buf.numel()
+
+
+_PACK_CACHE: dict = {}
+
+
+def _cached(src: torch.Tensor, key: tuple, make) -> PackedWeights:
+    k = (id(src), src.data_ptr(), src._version, key)
+    hit = _PACK_CACHE.get(k)
+    if hit is not None and hit[0]() is src:
+        return hit[1]
+    pw = make()
+    if len(_PACK_CACHE) > 512:
+        _PACK_CACHE.clear()
+    _PACK_CACHE[k] = (weakref.ref(src), pw)
+    return pw
+
+
+def _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, pad) -> ConvDesc:
+    return ConvDesc(n, c_in, h, w, cb, c_out, kh, kw, stride[0], stride[1], pad[0], pad[1])
+
+
+def pack_conv_weights_int8(kernel: torch.Tensor) -> PackedWeights:
+    """kernel: s8 ``[O/16][I/cb][KH][KW][cb/4][16][4]`` (apps/cpu/kernel/conv2d.py:26,30)."""
+    L = _require_cuda_lib()
+    kernel = _to_device(kernel, torch.int8, 'kernel')
+    if kernel.dim() != 7 or kernel.shape[5] != 16 or kernel.shape[6] != 4 or kernel.shape[4] not in (1, 4):
+        raise ValueError(f'kernel must be [O/16][I/cb][KH][KW][cb/4][16][4], got {tuple(kernel.shape)}')
+    oc, icc, kh, kw, c4 = (int(s) for s in kernel.shape[:5])
+    cb = c4 * 4
+    key = ('conv_i8', oc * 16, icc * cb, cb, kh, kw)
+
+    def make():
+        d = _conv_desc(1, icc * cb, kh, kw, cb, oc * 16, kh, kw, (1, 1), (0, 0))
+        nbytes = L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d))
+        if nbytes == 0:
+            raise ValueError('unsupported convolution weights')
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=kernel.device)
+        check(L.unit_pack_weights_conv_i8(ctypes.byref(d), _ptr(kernel), _ptr(buf), _stream()), 'unit_pack_weights_conv_i8')
+        return PackedWeights('conv_i8', buf, key)
+
+    with torch.cuda.device(kernel.device):
+        return _cached(kernel, key, make)
+
+
+def pack_conv_weights_f16(kernel: torch.Tensor) -> PackedWeights:
+    """kernel: fp16 ``[O/16][I/16][KH][KW][16 i][16 o]`` (python/tensorizer/ops/gpu.py:29-31)."""
+    L = _require_cuda_lib()
+    kernel = _to_device(kernel, torch.float16, 'kernel')
+    if kernel.dim() != 6 or kernel.shape[4] != 16 or kernel.shape[5] != 16:
+        raise ValueError(f'kernel must be [O/16][I/16][KH][KW][16][16], got {tuple(kernel.shape)}')
+    oc, icc, kh, kw = (int(s) for s in kernel.shape[:4])
+    key = ('conv_f16', oc * 16, icc * 16, kh, kw)
+
+    def make():
+        d = _conv_desc(1, icc * 16, kh, kw, 16, oc * 16, kh, kw, (1, 1), (0, 0))
+        nbytes = L.unit_packed_weights_bytes_conv_f16(ctypes.byref(d))
+        if nbytes == 0:
+            raise ValueError('unsupported convolution weights')
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=kernel.device)
+        check(L.unit_pack_weights_conv_f16(ctypes.byref(d), _ptr(kernel), _ptr(buf), _stream()), 'unit_pack_weights_conv_f16')
+        return PackedWeights('conv_f16', buf, key)
+
+    with torch.cuda.device(kernel.device):
+        return _cached(kernel, key, make)
+
+
+def pack_dense_weights_int8(weight: torch.Tensor) -> PackedWeights:
+    """weight: s8 ``[N/T][K/4][T][4]`` (apps/cpu/kernel/int8-gemm.py:11-14)."""
+    L = _require_cuda_lib()
+    weight = _to_device(weight, torch.int8, 'weight')
+    if weight.dim() != 4 or weight.shape[3] != 4:
+        raise ValueError(f'weight must be [N/T][K/4][T][4], got {tuple(weight.shape)}')
+    nt, k4, t = (int(s) for s in weight.shape[:3])
+    n, k = nt * t, k4 * 4
+    key = ('dense_i8', n, k, t)
+
+    def make():
+        nbytes = L.unit_packed_weights_bytes_dense_i8(n, k)
+        if nbytes == 0:
+            raise ValueError(f'dense weights need N % 16 == 0 and K % 16 == 0, got N={n} K={k}')
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
+        check(L.unit_pack_weights_dense_i8(n, k, t, _ptr(weight), _ptr(buf), _stream()), 'unit_pack_weights_dense_i8')
+        return PackedWeights('dense_i8', buf, key)
+
+    with torch.cuda.device(weight.device):
+        return _cached(weight, key, make)
+
+
+def pack_gemm_weights_f16(b: torch.Tensor) -> PackedWeights:
+    """b: fp16 ``[K][N]`` row-major (apps/gpu/gemm.py:8)."""
+    L = _require_cuda_lib()
+    b = _to_device(b, torch.float16, 'b')
+    if b.dim() != 2:
+        raise ValueError('b must be [K][N]')
+    k, n = int(b.shape[0]), int(b.shape[1])
+    key = ('gemm_f16', n, k)
+
+    def make():
+        nbytes = L.unit_packed_weights_bytes_gemm_f16(n, k)
+        if nbytes == 0:
+            raise ValueError(f'gemm needs N % 16 == 0 and K % 8 == 0, got N={n} K={k}')
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=b.device)
+        check(L.unit_pack_weights_gemm_f16(n, k, _ptr(b), _ptr(buf), _stream()), 'unit_pack_weights_gemm_f16')
+        return PackedWeights('gemm_f16', buf, key)
+
+    with torch.cuda.device(b.device):
+        return _cached(b, key, make)
+
+
+# --------------------------------------------------------------------------
+# int8 path
+# --------------------------------------------------------------------------
+def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: IntPair = 0, dilation: IntPair = 1,
+                      layout: str = 'NCHW4c', out_layout: str = 'NCHW16c', out_dtype: str = 'int32', *,
+                      bias: Optional[torch.Tensor] = None, requant_shift: Optional[int] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """u8 x s8 -> s32 convolution on blocked layouts.
+
+    data   u8  ``[N][C/cb][H][W][cb]``, cb = 16 (or 4 for a 3/4-channel stem)
+    kernel s8  ``[O/16][C/cb][KH][KW][cb/4][16][4]`` or a ``PackedWeights``
+    result s32 ``[N][O/16][OH][OW][16]``; with ``out_dtype='uint8'`` (or
+    ``requant_shift``) the fused epilogue
+    ``clamp((acc + bias + 2^(shift-1)) >> shift, 0, 255)`` gives u8 instead.
+    ``layout`` is accepted for signature compatibility; the channel block is
+    read from ``data``'s last dimension as the reference's compute does.
+    """
+    L = _require_cuda_lib()
+    if _pair(dilation) != (1, 1):
+        raise ValueError('dilation other than 1 is not supported (the reference only uses 1)')
+    if out_layout != 'NCHW16c':
+        raise ValueError("out_layout must be 'NCHW16c'")
+    if out_dtype not in ('int32', 'uint8'):
+        raise ValueError("out_dtype must be 'int32' or 'uint8'")
+    stride, padding = _pair(stride), _pair(padding)
+    host = not data.is_cuda
+    data = _to_device(data, torch.uint8, 'data')
+    if data.dim() != 5 or data.shape[4] not in (4, 16):
+        raise ValueError(f'data must be [N][C/cb][H][W][cb] with cb in (4, 16), got {tuple(data.shape)}')
+    n, cc, h, w, cb = (int(s) for s in data.shape)
+    with torch.cuda.device(data.device):
+        pw = kernel if isinstance(kernel, PackedWeights) else pack_conv_weights_int8(kernel)
+        if pw.kind != 'conv_i8':
+            raise ValueError('kernel was packed for a different operator')
+        _, c_out, c_in, pcb, kh, kw = pw.key
+        if c_in != cc * cb or pcb != cb:
+            raise ValueError(f'channel mismatch: data has {cc}x{cb}, kernel expects {c_in} in blocks of {pcb}')
+        requant = out_dtype == 'uint8' or requant_shift is not None
+        shift = 8 if requant_shift is None else int(requant_shift)
+        d = _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, padding)
+        if h + 2 * padding[0] < kh or w + 2 * padding[1] < kw:
+            raise ValueError('kernel larger than padded input')
+        oh = (h + 2 * padding[0] - kh) // stride[0] + 1
+        ow = (w + 2 * padding[1] - kw) // stride[1] + 1
+        if bias is not None:
+            bias = _to_device(bias, torch.int32, 'bias')
+            if bias.numel() != c_out:
+                raise ValueError(f'bias must have {c_out} elements')
+        oshape = (n, c_out // 16, oh, ow, 16)
+        odt = torch.uint8 if requant else torch.int32
+        if out is None:
+            out_t = torch.empty(oshape, dtype=odt, device=data.device)
+        else:
+            out_t = out
+            if tuple(out_t.shape) != oshape or out_t.dtype != odt or not out_t.is_cuda or not out_t.is_contiguous():
+                raise ValueError(f'out must be a contiguous CUDA {odt} tensor of shape {oshape}')
+        if requant:
+            check(L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), shift,
+                                                   _ptr(out_t), _stream()), 'unit_conv2d_u8s8_requant_nchwc')
+        else:
+            check(L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), _ptr(out_t),
+                                              _stream()), 'unit_conv2d_u8s8s32_nchwc')
+    return out_t.cpu() if (host and out is None) else out_t
+
+
+def dense_dotprod(data: torch.Tensor, weight, bias: Optional[torch.Tensor] = None, out_dtype: str = 'int32', *,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[i][j] = sum_k u8 data[i][k] * s8 weight[j/T][k/4][j%T][k%4]  -> s32 [M][N]."""
+    L = _require_cuda_lib()
+    if out_dtype != 'int32':
+        raise ValueError("out_dtype must be 'int32'")
+    if bias is not None:
+        raise ValueError('bias is not supported (the reference passes None)')
+    host = not data.is_cuda
+    data = _to_device(data, torch.uint8, 'data')
+    if data.dim() != 2:
+        raise ValueError('data must be [M][K]')
+    m, k = int(data.shape[0]), int(data.shape[1])
+    with torch.cuda.device(data.device):
+        pw = weight if isinstance(weight, PackedWeights) else pack_dense_weights_int8(weight)
+        if pw.kind != 'dense_i8':
+            raise ValueError('weight was packed for a different operator')
+        _, n, pk, _t = pw.key
+        if pk != k:
+            raise ValueError(f'K mismatch: data has {k}, weight has {pk}')
+        if out is None:
+            out_t = torch.empty((m, n), dtype=torch.int32, device=data.device)
+        else:
+            out_t = out
+            if tuple(out_t.shape) != (m, n) or out_t.dtype != torch.int32 or not out_t.is_cuda or not out_t.is_contiguous():
+                raise ValueError('out must be a contiguous CUDA int32 [M][N] tensor')
+        if m > 0:
+            check(L.unit_dense_u8s8s32(m, n, k, _ptr(data), k, _ptr(pw.buf), _ptr(out_t), n, _stream()),
+                  'unit_dense_u8s8s32')
+    return out_t.cpu() if (host and out is None) else out_t
+
+
+# --------------------------------------------------------------------------
+# fp16 path
+# --------------------------------------------------------------------------
+def pack_data_nchwc(x: torch.Tensor, c_block: int = 16) -> torch.Tensor:
+    """NCHW -> ``[N][ceil(C/cb)][H][W][cb]`` on the device (python/tensorizer/ops/gpu.py:26-28)."""
+    L = _require_cuda_lib()
+    if x.dim() != 4:
+        raise ValueError('x must be NCHW')
+    if not x.is_cuda:
+        x = x.cuda(non_blocking=True)
+    x = x.contiguous()
+    n, c, h, w = (int(s) for s in x.shape)
+    cc = (c + c_block - 1) // c_block
+    y = torch.empty((n, cc, h, w, c_block), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.unit_pack_data_nchw_to_nchwc(_ptr(x), _ptr(y), n, c, h, w, c_block, x.element_size(), _stream()),
+              'unit_pack_data_nchw_to_nchwc')
+    return y
+
+
+def unpack_data_nchwc(x: torch.Tensor, channels: Optional[int] = None) -> torch.Tensor:
+    """``[N][C/cb][H][W][cb]`` -> NCHW, keeping the first ``channels`` channels."""
+    L = _require_cuda_lib()
+    if x.dim() != 5:
+        raise ValueError('x must be [N][C/cb][H][W][cb]')
+    if not x.is_cuda:
+        x = x.cuda(non_blocking=True)
+    x = x.contiguous()
+    n, cc, h, w, cb = (int(s) for s in x.shape)
+    c = cc * cb if channels is None else int(channels)
+    if c < 1 or c > cc * cb:
+        raise ValueError('channels out of range')
+    y = torch.empty((n, c, h, w), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.unit_unpack_data_nchwc_to_nchw(_ptr(x), _ptr(y), n, c, h, w, cb, x.element_size(), _stream()),
+              'unit_unpack_data_nchwc_to_nchw')
+    return y
+
+
+def pack_weights_oihw_int8(w: torch.Tensor, c_block: int = 16) -> torch.Tensor:
+    """OIHW s8 -> the reference's ``[O/16][I/cb][KH][KW][cb/4][16][4]`` array, zero padded."""
+    L = _require_cuda_lib()
+    w = _to_device(w, torch.int8, 'w')
+    o, i, kh, kw = (int(s) for s in w.shape)
+    y = torch.empty(((o + 15) // 16, (i + c_block - 1) // c_block, kh, kw, c_block // 4, 16, 4), dtype=torch.int8,
+                    device=w.device)
+    with torch.cuda.device(w.device):
+        check(L.unit_pack_weights_oihw_to_ref_i8(_ptr(w), _ptr(y), o, i, kh, kw, c_block, _stream()),
+              'unit_pack_weights_oihw_to_ref_i8')
+    return y
+
+
+def pack_weights_oihw_f16(w: torch.Tensor) -> torch.Tensor:
+    """OIHW fp16 -> ``[O/16][I/16][KH][KW][16 i][16 o]`` (python/tensorizer/ops/gpu.py:29-31)."""
+    L = _require_cuda_lib()
+    w = _to_device(w, torch.float16, 'w')
+    o, i, kh, kw = (int(s) for s in w.shape)
+    y = torch.empty(((o + 15) // 16, (i + 15) // 16, kh, kw, 16, 16), dtype=torch.float16, device=w.device)
+    with torch.cuda.device(w.device):
+        check(L.unit_pack_weights_oihw_to_ref_f16(_ptr(w), _ptr(y), o, i, kh, kw, _stream()),
+              'unit_pack_weights_oihw_to_ref_f16')
+    return y
+
+
+def conv2d_NCHW16c_OHWI16o(a: torch.Tensor, b, stride_h: int = 1, stride_w: int = 1, out_type: str = 'float32', *,
+                           padding: IntPair = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp16 x fp16 -> fp32 convolution, the tensor-core operator of the reference.
+
+    Like the reference's compute it takes either 4-D NCHW data with OIHW
+    weights (packed here first) or 5-D ``[N][C/16][H][W][16]`` data with 6-D
+    ``[O/16][C/16][KH][KW][16][16]`` weights; the result is always
+    ``[N][O/16][OH][OW][16]`` fp32.  The reference convolves without padding;
+    ``padding`` adds implicit zero padding.
+    """
+    L = _require_cuda_lib()
+    if out_type != 'float32':
+        raise ValueError("out_type must be 'float32'")
+    padding = _pair(padding)
+    host = not a.is_cuda
+    a = _to_device(a, torch.float16, 'a')
+    if a.dim() == 4:
+        if isinstance(b, PackedWeights) or b.dim() != 4:
+            raise ValueError('4-D data needs 4-D OIHW weights')
+        a = pack_data_nchwc(a, 16)
+        b = pack_weights_oihw_f16(b if b.is_cuda else b.cuda(non_blocking=True))
+    elif a.dim() != 5 or a.shape[4] != 16:
+        raise ValueError('a must be NCHW or [N][C/16][H][W][16]')
+    n, cc, h, w, _ = (int(s) for s in a.shape)
+    with torch.cuda.device(a.device):
+        pw = b if isinstance(b, PackedWeights) else pack_conv_weights_f16(b)
+        if pw.kind != 'conv_f16':
+            raise ValueError('b was packed for a different operator')
+        _, c_out, c_in, kh, kw = pw.key
+        if c_in != cc * 16:
+            raise ValueError(f'channel mismatch: data has {cc * 16}, weights expect {c_in}')
+        if h + 2 * padding[0] < kh or w + 2 * padding[1] < kw:
+            raise ValueError('kernel larger than padded input')
+        d = _conv_desc(n, c_in, h, w, 16, c_out, kh, kw, (int(stride_h), int(stride_w)), padding)
+        oh = (h + 2 * padding[0] - kh) // int(stride_h) + 1
+        ow = (w + 2 * padding[1] - kw) // int(stride_w) + 1
+        oshape = (n, c_out // 16, oh, ow, 16)
+        if out is None:
+            out_t = torch.empty(oshape, dtype=torch.float32, device=a.device)
+        else:
+            out_t = out
+            if tuple(out_t.shape) != oshape or out_t.dtype != torch.float32 or not out_t.is_cuda or not out_t.is_contiguous():
+                raise ValueError(f'out must be a contiguous CUDA float32 tensor of shape {oshape}')
+        check(L.unit_conv2d_f16f32_nchw16c(ctypes.byref(d), _ptr(a), _ptr(pw.buf), _ptr(out_t), _stream()),
+              'unit_conv2d_f16f32_nchw16c')
+    return out_t.cpu() if (host and out is None) else out_t
+
+
+class _Attrs:
+    """Minimal stand-in for the relay attrs object the reference's compute receives."""
+
+    def __init__(self, strides=(1, 1), padding=(0, 0)):
+        self._v = {'strides': tuple(strides), 'padding': tuple(padding)}
+
+    def get_int_tuple(self, name):
+        return self._v[name]
+
+
+def conv2d_NCHW16c_OHWI16o_compute(attrs, inputs, out_type='float32'):
+    """Same call shape as python/tensorizer/ops/gpu.py:56-58: returns a one-element list."""
+    strides = attrs.get_int_tuple('strides')
+    out_dtype = getattr(out_type, 'dtype', out_type)
+    return [conv2d_NCHW16c_OHWI16o(inputs[0], inputs[1], strides[0], strides[1], out_dtype)]
+
+
+def gemm_f16f32(a: torch.Tensor, b, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[M][N] fp32 = A[M][K] fp16 . B[K][N] fp16 with fp32 accumulation."""
+    L = _require_cuda_lib()
+    host = not a.is_cuda
+    a = _to_device(a, torch.float16, 'a')
+    if a.dim() != 2:
+        raise ValueError('a must be [M][K]')
+    m, k = int(a.shape[0]), int(a.shape[1])
+    with torch.cuda.device(a.device):
+        pw = b if isinstance(b, PackedWeights) else pack_gemm_weights_f16(b)
+        if pw.kind != 'gemm_f16':
+            raise ValueError('b was packed for a different operator')
+        _, n, pk = pw.key
+        if pk != k:
+            raise ValueError(f'K mismatch: a has {k}, b has {pk}')
+        if out is None:
+            out_t = torch.empty((m, n), dtype=torch.float32, device=a.device)
+        else:
+            out_t = out
+            if tuple(out_t.shape) != (m, n) or out_t.dtype != torch.float32 or not out_t.is_cuda or not out_t.is_contiguous():
+                raise ValueError('out must be a contiguous CUDA float32 [M][N] tensor')
+        if m > 0:
+            check(L.unit_gemm_f16f32(m, n, k, _ptr(a), 2 * k, _ptr(pw.buf), _ptr(out_t), n, _stream()),
+                  'unit_gemm_f16f32')
+    return out_t.cpu() if (host and out is None) else out_t
+
+
+# The reference registers its instructions in a dict keyed by instruction name
+# (python/tensorizer/intrinsics/intrinsics.py:7-40).  The same keys map to the
+# contraction each instruction performs and to the operators built on it here.
+INTRINSICS = {
+    'vnni': {
+        'pattern': {'out_lanes': 16, 'reduce_lanes': 4, 'a_dtype': 'uint8', 'b_dtype': 'int8', 'out_dtype': 'int32'},
+        'conv2d': conv2d_NCHWc_int8,
+        'dense': dense_dotprod,
+    },
+    'tensorcore': {
+        'pattern': {'m': 16, 'n': 16, 'k': 16, 'a_dtype': 'float16', 'b_dtype': 'float16', 'out_dtype': 'float32'},
+        'conv2d': conv2d_NCHW16c_OHWI16o,
+        'gemm': gemm_f16f32,
+    },
+}
