@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 convolution hot path: the ResNet-50 conv-layer sweep.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl unit|reference]
+
+One *step* is one pass over all 53 convolutions of ResNet-50 (u8 activations,
+s8 weights, fused bias + requantise to u8, NCHW16c) on a batch of 256 images.
+With N GPUs the batch is split 256/N per GPU, weights replicated, no collective
+on the data path (strong scaling).  Every convolution instance has its own
+input and output buffers (about 5.6 GB per step in total at batch 256), so no
+layer finds its data in L2 from an earlier launch.
+
+Prints one JSON line (rank 0).  ``value`` is whole-job TOPS with inputs
+resident in HBM; ``e2e`` is the same sweep through the Python operator with
+pinned host buffers copied in and results copied out inside the timed region.
+``--impl reference`` times the AVX-512 VNNI + OpenMP restatement of the
+reference's CPU loop nest on the host cores over a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOTAL_BATCH = 256
+METRIC = 'int8 conv2d TOPS (ResNet-50 conv-layer sweep, batch 256)'
+
+
+def _peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {'hbm_gbs': float(p['hbm_gbs']), 'bf16_burst': float(p['bf16_tflops']),
+                'bf16_sustained': float(p.get('bf16_tflops_sustained', p['bf16_tflops'])), 'source': 'measured'}
+    except Exception:
+        return {'hbm_gbs': 6650.0, 'bf16_burst': 1590.0, 'bf16_sustained': 1400.0, 'source': 'fallback'}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+              'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self._stop = threading.Event()
+        self._thr = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
+                                      '-i', str(self.gpu)], capture_output=True, text=True, timeout=5).stdout
+                for line in out.strip().splitlines():
+                    self.rows.append([t.strip() for t in line.split(',')])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thr.join(timeout=10)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for i, n in enumerate(names):
+                if len(r) > 4 + i and r[4 + i].lower().startswith('active'):
+                    reasons.add(n)
+        if not sm:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        return {'sm_mhz': statistics.median(sm), 'sm_max_mhz': max(mx), 'reasons': sorted(reasons),
+                'samples': len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU legs (the oracle is the thing timed here, never the thing shipped)
+# ---------------------------------------------------------------------------
+def cpu_sweep(sample_batch: int, min_seconds: float, max_passes: int = 50):
+    """Times the VNNI/OpenMP restatement over the 53 convolutions at a small batch."""
+    import numpy as np
+    from oracle import c_oracle as co
+    from unit_b200 import resnet50 as R
+    vnni = co.host_has_vnni()
+    data = []
+    for i, l in enumerate(R.LAYERS):
+        x, w, b = R.make_layer_inputs(l, i, sample_batch, config=5)
+        data.append((l, x, w, b))
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for l, x, w, b in data:
+            for _ in range(l.count):
+                co.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
+        return time.perf_counter() - t0
+
+    one_pass()  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_passes and (not times or time.perf_counter() - t_start < min_seconds):
+        times.append(one_pass())
+    ops = R.sweep_ops(sample_batch)
+    return {'times': times, 'ops': ops, 'cores': int(co.lib().oracle_max_threads()), 'vnni': vnni,
+            'tops': ops / statistics.median(times) / 1e12}
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return 0
+    sample = 8
+    import numpy as np  # noqa: F401
+    from oracle import c_oracle as co
+    from unit_b200 import resnet50 as R
+    vnni = co.host_has_vnni()
+    data = [(l,) + R.make_layer_inputs(l, i, sample, config=5) for i, l in enumerate(R.LAYERS)]
+
+    def step():
+        for l, x, w, b in data:
+            for _ in range(l.count):
+                co.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = R.sweep_ops(sample) / dt / 1e12
+    cores = int(co.lib().oracle_max_threads())
+    kind = 'port'
+    sample_txt = (f'all 53 convolutions at batch {sample} of {TOTAL_BATCH} per step, '
+                  f'{"AVX-512 VNNI + OpenMP" if vnni else "scalar + OpenMP"} restatement of the reference loop nest')
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': tops, 'unit': 'TOPS', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
+        'config': {'workload': 'resnet50-int8-conv-sweep', 'global_batch': TOTAL_BATCH, 'sample_batch': sample,
+                   'convolutions': 53, 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c'},
+        'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': cores, 'kind': kind, 'sample': sample_txt},
+        'e2e': {'value': tops, 'unit': 'TOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_unit(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit('launch with torch.distributed.run --nproc-per-node N for --gpus N')
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the unit_b200 operators have no CPU fallback')
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+
+    import unit_b200 as U
+    from unit_b200 import resnet50 as R
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if TOTAL_BATCH % world:
+        raise SystemExit('--gpus must divide 256')
+    batch = TOTAL_BATCH // world
+    gen = torch.Generator(device=dev)
+
+    # ---- build the 53 instances: packed weights shared per shape, own activations/outputs per instance
+    instances = []   # (layer, x, packed, bias, out)
+    per_layer = []   # (layer, [instance indices])
+    for li, l in enumerate(R.LAYERS):
+        cb, cs = l.c_block, l.c_in_stored
+        gen.manual_seed(R.layer_seed(5, li, 1) + 7919 * rank)
+        w = torch.randn((l.c_out // 16, cs // cb, l.k, l.k, cb // 4, 16, 4), device=dev, generator=gen)
+        w = (w * 32.0).round_().clamp_(-128, 127).to(torch.int8)
+        bias = torch.randint(-2 ** 15, 2 ** 15, (l.c_out,), dtype=torch.int32, device=dev, generator=gen)
+        packed = U.pack_conv_weights_int8(w)
+        idxs = []
+        for c in range(l.count):
+            gen.manual_seed(R.layer_seed(5, li, 0) + 101 * c + 7919 * rank)
+            shape = (batch, cs // cb, l.hw, l.hw, cb)
+            x = torch.randint(1, 256, shape, dtype=torch.uint8, device=dev, generator=gen)
+            x *= torch.randint(0, 2, shape, dtype=torch.uint8, device=dev, generator=gen)
+            if cs != l.c_in:
+                x[..., l.c_in:] = 0
+            out = torch.empty((batch, l.c_out // 16, l.out_hw, l.out_hw, 16), dtype=torch.uint8, device=dev)
+            idxs.append(len(instances))
+            instances.append((l, x, packed, bias, out))
+        per_layer.append((l, idxs))
+        del w
+    U.device_status()
+
+    def run_instance(inst):
+        l, x, packed, bias, out = inst
+        U.conv2d_NCHWc_int8(x, packed, stride=l.stride, padding=l.pad, bias=bias, out_dtype='uint8', out=out)
+
+    def step():
+        for inst in instances:
+            run_instance(inst)
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    n0 = U.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as cs_:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        launches = U.launch_count() - n0
+        # nvidia-smi needs ~0.1 s per sample: when the timed region was shorter than a few
+        # samples, keep the same load running (untimed) until the sampler has seen it
+        t_end = time.time() + 1.5
+        extended = False
+        while len(cs_.rows) < 6 and time.time() < t_end:
+            extended = True
+            step()
+            torch.cuda.synchronize()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    U.device_status()
+    total_ops = R.sweep_ops(TOTAL_BATCH)
+    value = total_ops / (ms_step * 1e-3) / 1e12
+    clocks = cs_.summary()
+    clocks['sampled'] = 'timed region plus the same load continued untimed' if extended else 'timed region'
+    gpu_launches = int(launches)
+
+    # ---- per-layer timing (explains the number; not part of `value`)
+    peaks = _peaks()
+    int8_peak = 2.0 * peaks['bf16_sustained']
+    layer_rows = []
+    sum_kernel_ms = 0.0
+    sum_roof_ms = 0.0
+    reps = 5
+    for l, idxs in ([] if args.kernels_only else per_layer):
+        for i in idxs:
+            run_instance(instances[i])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            for i in idxs:
+                run_instance(instances[i])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / (reps * len(idxs))
+        ops, byts = l.ops(batch), l.bytes(batch)
+        t_tensor = ops / (int8_peak * 1e12) * 1e3
+        t_hbm = byts / (peaks['hbm_gbs'] * 1e9) * 1e3
+        bound = 'tensor' if t_tensor >= t_hbm else 'hbm'
+        roof = max(t_tensor, t_hbm)
+        sum_kernel_ms += ms * len(idxs)
+        sum_roof_ms += roof * len(idxs)
+        layer_rows.append({'layer': l.name, 'count': l.count, 'us': round(ms * 1e3, 2),
+                           'tops': round(ops / ms / 1e9, 1), 'gbs': round(byts / ms / 1e6, 1), 'bound': bound,
+                           'frac': round(roof / ms, 3)})
+    if args.kernels_only:
+        sum_kernel_ms, sum_roof_ms = ms_step, None
+    kernel_tops = R.sweep_ops(batch) / (sum_kernel_ms * 1e-3) / 1e12
+
+    e2e_value = e2e_ms = None
+    h2d = d2h = 0
+    e2e_steps = 0
+    # ---- end-to-end: pinned host buffers in, results out, through the Python operator
+    if not args.kernels_only:
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        host_in, host_out = {}, {}
+        h2d = d2h = 0
+        for li, (l, idxs) in enumerate(per_layer):
+            _, x, _, _, out = instances[idxs[0]]
+            host_in[li] = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+            host_in[li].copy_(x)
+            host_out[li] = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+            h2d += x.numel() * len(idxs)
+            d2h += out.numel() * len(idxs)
+        torch.cuda.synchronize()
+
+        def e2e_step():
+            for li, (l, idxs) in enumerate(per_layer):
+                for i in idxs:
+                    _, x, packed, bias, out = instances[i]
+                    x.copy_(host_in[li], non_blocking=True)
+                    U.conv2d_NCHWc_int8(x, packed, stride=l.stride, padding=l.pad, bias=bias, out_dtype='uint8', out=out)
+                    host_out[li].copy_(out, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = max_over_ranks(a.elapsed_time(b) / e2e_steps)
+        e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
+        U.device_status()
+
+    # ---- host-CPU baseline beside it (rank 0, single-GPU runs only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.kernels_only:
+        sample = 8
+        r = cpu_sweep(sample, min_seconds=10.0)
+        cpu = {'value': r['tops'], 'unit': 'TOPS', 'cores': r['cores'], 'kind': 'port',
+               'sample': (f'all 53 convolutions at batch {sample} of {TOTAL_BATCH}, {len(r["times"])} passes, median; '
+                          f'{"AVX-512 VNNI + OpenMP" if r["vnni"] else "scalar + OpenMP"} restatement of the '
+                          'reference loop nest')}
+
+    if rank == 0:
+        line = {
+            'metric': METRIC, 'value': value, 'unit': 'TOPS', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
+            'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
+            'config': {'workload': 'resnet50-int8-conv-sweep', 'global_batch': TOTAL_BATCH, 'per_gpu_batch': batch,
+                       'convolutions': 53, 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
+                       'parallelism': f'batch-split x{world}, weights replicated, no collective',
+                       'l2': 'every convolution instance has its own buffers; %.2f GB touched per step per GPU, '
+                             'larger than L2' % (R.sweep_bytes(batch) / 1e9)},
+            'clocks': clocks,
+            'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+                    'ms_per_step': e2e_ms, 'steps': e2e_steps},
+            'gpu_launches': gpu_launches,
+            'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
+                         'frac': kernel_tops / int8_peak, 'traffic': None,
+                         'peak_source': f'2 x bf16_tflops_sustained of {peaks["source"]} peaks '
+                                        '(dense int8 issues at twice the bf16 rate)',
+                         'kernel': 'igemm_kernel<A_CONV_I8, EPI_REQ_NCHWC> over the 53 launches of one step',
+                         'mixed_bound_frac': (sum_roof_ms / sum_kernel_ms) if sum_roof_ms else None,
+                         'hbm_peak_gbs': peaks['hbm_gbs']},
+            'layers': layer_rows,
+            'cpu_baseline': cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='unit', choices=['unit', 'reference'])
+    ap.add_argument('--e2e-steps', type=int, default=2)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--kernels-only', action='store_true',
+                    help='timed region only: skip the per-layer pass, the end-to-end leg and the CPU baseline '
+                         '(for profiler runs)')
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == 'unit':
+        args.warmup = 3
+    if args.impl == 'reference':
+        return run_reference(args)
+    return run_unit(args)
+
+
+if __name__ == '__main__':
+    sys.exit(main())

@@ -1,0 +1,361 @@
+"""Parity of the CUDA path against the oracle, through the operator entry points
+(which call the C ABI).  Bit-exact for the int8 path; rel 1e-2 / abs 1e-3 for fp16."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import np_oracle as no
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-2, 1e-3  # fp16 path tolerance stated by the task
+
+
+@pytest.fixture(scope='module')
+def U():
+    assert torch.cuda.is_available(), 'GPU tests need a CUDA device'
+    import unit_b200
+    from unit_b200 import _lib
+    _lib.lib()  # fails loudly if the CUDA library is missing
+    return unit_b200
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def conv_case(U, oracle, rng, n, ci, h, w, co, kh, kw, s, p, cb=16, vnni=True, dist='uniform'):
+    cs = (ci + cb - 1) // cb * cb
+    if dist == 'uniform':
+        x = rng.integers(0, 256, (n, cs // cb, h, w, cb), dtype=np.uint8)
+        wt = rng.integers(-128, 128, (co // 16, cs // cb, kh, kw, cb // 4, 16, 4), dtype=np.int8)
+    else:
+        from unit_b200 import resnet50 as R
+        x = R.synth_activations(rng, (n, cs // cb, h, w, cb))
+        wt = R.synth_weights(rng, (co // 16, cs // cb, kh, kw, cb // 4, 16, 4))
+    b = rng.integers(-2 ** 15, 2 ** 15, co, dtype=np.int32)
+    use_vnni = vnni and oracle.host_has_vnni()
+    ref = oracle.conv2d_u8s8(x, wt, (s, s), (p, p), vnni=use_vnni)
+    refq = oracle.conv2d_u8s8(x, wt, (s, s), (p, p), bias=b, requant_shift=8, vnni=use_vnni)
+    xd, wd, bd = dev(x), dev(wt), dev(b)
+    got = U.conv2d_NCHWc_int8(xd, wd, stride=s, padding=p)
+    gotq = U.conv2d_NCHWc_int8(xd, wd, stride=s, padding=p, bias=bd, out_dtype='uint8')
+    U.device_status()
+    assert np.array_equal(got.cpu().numpy(), ref)
+    assert np.array_equal(gotq.cpu().numpy(), refq)
+
+
+# ---------------------------------------------------------------------------
+# golden fixtures
+# ---------------------------------------------------------------------------
+def test_golden_vectors(U, golden):
+    g = golden
+    x, w, b = dev(g['c1_x']), dev(g['c1_w']), dev(g['c1_bias'])
+    assert np.array_equal(U.conv2d_NCHWc_int8(x, w, stride=1, padding=1).cpu().numpy(), g['c1_out'])
+    assert np.array_equal(U.conv2d_NCHWc_int8(x, w, stride=2, padding=1).cpu().numpy(), g['c2_out'])
+    assert np.array_equal(U.conv2d_NCHWc_int8(x, w, stride=1, padding=1, bias=b, out_dtype='uint8').cpu().numpy(),
+                          g['c1_req'])
+    assert np.array_equal(U.conv2d_NCHWc_int8(dev(g['st_x']), dev(g['st_w']), stride=2, padding=3).cpu().numpy(),
+                          g['st_out'])
+    assert np.array_equal(U.dense_dotprod(dev(g['d_a']), dev(g['d_bp'])).cpu().numpy(), g['d_c'])
+    # small-integer fp16 inputs: exact in fp32
+    assert np.array_equal(U.conv2d_NCHW16c_OHWI16o(dev(g['f_x']), dev(g['f_w']), 1, 1).cpu().numpy(), g['f_out'])
+    np.testing.assert_allclose(U.gemm_f16f32(dev(g['g_a']), dev(g['g_b'])).cpu().numpy(), g['g_c'],
+                               rtol=RTOL, atol=ATOL)
+    U.device_status()
+
+
+def test_vnni_known_answer_through_the_gpu(U):
+    """poc/vnni/poc.cc's vector as a 1x1 convolution: 16 lanes x 4-way dot."""
+    import json, os
+    with open(os.path.join(os.path.dirname(__file__), 'golden', 'poc_vnni_kat.json')) as f:
+        want = json.load(f)['d']
+    a = (np.arange(64) + 1).astype(np.uint8)
+    b = (64 - np.arange(64)).astype(np.int8)
+    # lane x uses a[4x..4x+3] and b[4x..4x+3]: 16 pixels with 16 channels (4 real), weights per lane
+    for lane in range(16):
+        x = np.zeros((1, 1, 1, 1, 16), np.uint8)
+        x[0, 0, 0, 0, :4] = a[4 * lane:4 * lane + 4]
+        w = np.zeros((1, 1, 1, 1, 4, 16, 4), np.int8)
+        w[0, 0, 0, 0, 0, lane, :] = b[4 * lane:4 * lane + 4]
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w)).cpu().numpy().reshape(16)
+        assert got[lane] == want[lane] and got.sum() == want[lane]
+
+
+# ---------------------------------------------------------------------------
+# int8 convolution
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize('n,ci,h,w,co,kh,kw,s,p', [
+    (1, 16, 1, 1, 16, 1, 1, 1, 0),        # a single pixel, a single chunk
+    (1, 16, 8, 8, 16, 3, 3, 1, 1),        # odd K-column count (9): zero-padded column
+    (1, 64, 56, 56, 64, 3, 3, 1, 1),      # BASELINE config 1
+    (2, 64, 14, 14, 128, 3, 3, 2, 1),
+    (3, 32, 13, 11, 48, 3, 3, 1, 1),      # ragged: 429 pixels, tile straddles images, N tile of 48
+    (1, 48, 9, 9, 320, 1, 1, 1, 0),       # two N tiles of 160
+    (2, 16, 12, 9, 16, 1, 7, 1, 0),       # 1x7 and 7x1 kernels of the reference's shape corpus
+    (2, 16, 12, 9, 16, 7, 1, 1, 3),
+    (1, 80, 10, 10, 64, 5, 5, 2, 2),      # K columns not a multiple of any stage size
+    (5, 256, 14, 14, 512, 1, 1, 1, 0),
+    (2, 512, 7, 7, 2048, 1, 1, 2, 0),     # strided 1x1 projection
+    (1, 2048, 7, 7, 512, 1, 1, 1, 0),     # deepest 1x1 reduction
+    (1, 512, 7, 7, 512, 3, 3, 1, 1),      # deepest 3x3 reduction (4608)
+    (1, 16, 40, 40, 16, 3, 3, 1, 0),      # valid convolution (no padding), as the reference calls it
+])
+def test_conv_int8_bit_exact(U, oracle, n, ci, h, w, co, kh, kw, s, p):
+    rng = np.random.default_rng(hash((n, ci, h, w, co, kh, kw, s, p)) % 2 ** 32)
+    if kh != kw:
+        # the entry point takes one stride/pad per axis; rectangular kernels use (p, p) on both
+        pass
+    conv_case(U, oracle, rng, n, ci, h, w, co, kh, kw, s, p)
+
+
+def test_conv_int8_extremes_and_signedness(U, oracle):
+    """All-255 activations against all -128 / +127 weights: u8 x s8, no saturation before the clamp."""
+    x = np.full((1, 32, 6, 6, 16), 255, np.uint8)
+    for val in (-128, 127):
+        w = np.full((2, 32, 3, 3, 4, 16, 4), val, np.int8)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=1, padding=0).cpu().numpy()
+        assert (got == 255 * val * 512 * 9).all()
+    U.device_status()
+
+
+def test_conv_int8_impulse(U):
+    x = np.zeros((1, 32, 5, 6), np.uint8)
+    w = np.zeros((32, 32, 3, 3), np.int8)
+    x[0, 19, 2, 3] = 7
+    w[21, 19, 0, 2] = -5
+    got = U.conv2d_NCHWc_int8(dev(no.pack_nchw_to_nchwc(x)), dev(no.pack_oihw_to_int8_weights(w)), stride=1, padding=1)
+    got = no.unpack_nchwc_to_nchw(got.cpu().numpy())
+    assert np.argwhere(got).tolist() == [[0, 21, 3, 2]] and got[0, 21, 3, 2] == -35
+
+
+def test_requant_rounding_and_bias_only_s32(U, oracle):
+    rng = np.random.default_rng(2)
+    x = rng.integers(0, 256, (1, 1, 4, 4, 16), dtype=np.uint8)
+    w = rng.integers(-128, 128, (1, 1, 1, 1, 4, 16, 4), dtype=np.int8)
+    b = np.array([-1, 126, 127, 128, 383, 384, 65151, 65152, 10 ** 6, -10 ** 6, -129, -128, 0, 255, 256, 2 ** 31 - 1],
+                 np.int32)
+    for shift in (1, 8, 15, 31):
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), bias=dev(b), requant_shift=shift).cpu().numpy()
+        assert np.array_equal(got, oracle.conv2d_u8s8(x, w, bias=b, requant_shift=shift))
+    got = U.conv2d_NCHWc_int8(dev(x), dev(w), bias=dev(b)).cpu().numpy()  # s32 + bias, wrapping like the oracle
+    assert np.array_equal(got, oracle.conv2d_u8s8(x, w, bias=b))
+    U.device_status()
+
+
+def test_stem_nchw4c(U, oracle):
+    rng = np.random.default_rng(4)
+    for (n, hw) in ((2, 32), (1, 224)):
+        x = rng.integers(0, 256, (n, 1, hw, hw, 4), dtype=np.uint8)
+        x[..., 3] = 0
+        w = rng.integers(-128, 128, (4, 1, 7, 7, 1, 16, 4), dtype=np.int8)
+        b = rng.integers(-2 ** 15, 2 ** 15, 64, dtype=np.int32)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=2, padding=3, bias=dev(b), out_dtype='uint8')
+        U.device_status()
+        ref = oracle.conv2d_u8s8(x, w, (2, 2), (3, 3), bias=b, requant_shift=8, vnni=oracle.host_has_vnni())
+        assert np.array_equal(got.cpu().numpy(), ref)
+    # two NCHW4c chunks (8 stored channels), 3x3
+    x = rng.integers(0, 256, (2, 2, 9, 9, 4), dtype=np.uint8)
+    w = rng.integers(-128, 128, (2, 2, 3, 3, 1, 16, 4), dtype=np.int8)
+    got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=1, padding=1)
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, w, (1, 1), (1, 1)))
+
+
+@pytest.mark.parametrize('batch', [1, 16])
+def test_resnet50_sweep_config3(U, oracle, batch):
+    """BASELINE config 3: every ResNet-50 conv shape, batch 1 and 16, fused bias + requant, bit-exact."""
+    from unit_b200 import resnet50 as R
+    vnni = oracle.host_has_vnni()
+    for li, l in enumerate(R.LAYERS):
+        b_eff = batch if (vnni or batch == 1) else 2
+        x, w, b = R.make_layer_inputs(l, li, b_eff, config=3)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=l.stride, padding=l.pad, bias=dev(b), out_dtype='uint8')
+        U.device_status()
+        ref = oracle.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
+        assert np.array_equal(got.cpu().numpy(), ref), l.name
+
+
+# ---------------------------------------------------------------------------
+# int8 dense
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize('m,n,k,t', [
+    (1, 16, 16, 16), (128, 3072, 768, 128), (100, 128, 128, 128), (300, 512, 1024, 128), (129, 48, 80, 16),
+    (1024, 1024, 1024, 16),
+])
+def test_dense_int8_bit_exact(U, oracle, m, n, k, t):
+    rng = np.random.default_rng(m * 7 + n + k)
+    a = rng.integers(0, 256, (m, k), dtype=np.uint8)
+    b = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    bp = no.pack_dense_weights(b, t)
+    got = U.dense_dotprod(dev(a), dev(bp))
+    U.device_status()
+    ref = oracle.dense_u8s8s32(a, bp, vnni=oracle.host_has_vnni())
+    assert np.array_equal(got.cpu().numpy(), ref)
+
+
+def test_dense_4096_config2(U, oracle):
+    """BASELINE config 2: M = N = K = 4096, bit-exact."""
+    rng = np.random.default_rng(2)
+    a = rng.integers(0, 256, (4096, 4096), dtype=np.uint8)
+    b = rng.integers(-128, 128, (4096, 4096), dtype=np.int8)
+    bp = no.pack_dense_weights(b, 128)
+    got = U.dense_dotprod(dev(a), dev(bp))
+    U.device_status()
+    if oracle.host_has_vnni():
+        assert np.array_equal(got.cpu().numpy(), oracle.dense_u8s8s32(a, bp, vnni=True))
+    else:  # scalar oracle on a row sample
+        rows = rng.choice(4096, 64, replace=False)
+        assert np.array_equal(got.cpu().numpy()[rows], oracle.dense_u8s8s32(a[rows], bp))
+    # size-independent property: linearity in A over the integers (A1 + A2 with no u8 overflow)
+    a1 = (a // 2).astype(np.uint8)
+    a2 = (a - a1).astype(np.uint8)
+    pw = U.pack_dense_weights_int8(dev(bp))
+    s = U.dense_dotprod(dev(a1), pw) + U.dense_dotprod(dev(a2), pw)
+    assert torch.equal(s, got)
+
+
+# ---------------------------------------------------------------------------
+# fp16 path
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize('n,ci,h,w,co,k,s,p', [
+    (1, 16, 6, 6, 16, 3, 1, 0), (2, 32, 10, 10, 32, 3, 1, 1), (3, 64, 14, 14, 128, 3, 2, 1), (2, 256, 14, 14, 256, 1, 1, 0),
+    (1, 1024, 14, 14, 256, 1, 1, 0), (4, 256, 14, 14, 256, 3, 1, 1),
+])
+def test_conv_fp16(U, oracle, n, ci, h, w, co, k, s, p):
+    rng = np.random.default_rng(n + ci + co + k)
+    x = rng.standard_normal((n, ci // 16, h, w, 16)).astype(np.float16)
+    wt = (rng.standard_normal((co // 16, ci // 16, k, k, 16, 16)) * 0.05).astype(np.float16)
+    got = U.conv2d_NCHW16c_OHWI16o(dev(x), dev(wt), s, s, padding=p)
+    U.device_status()
+    np.testing.assert_allclose(got.cpu().numpy(), oracle.conv2d_f16f32(x, wt, (s, s), (p, p)), rtol=RTOL, atol=ATOL)
+
+
+def test_conv_fp16_config4_batch256(U, oracle):
+    """BASELINE config 4: N=256, 256->256, 14x14, 3x3 pad 1.  The oracle checks a sample of images;
+    the whole batch is checked through batch independence (each image equals its batch-8 result)."""
+    rng = np.random.default_rng(44)
+    x = rng.standard_normal((256, 16, 14, 14, 16)).astype(np.float16)
+    wt = (rng.standard_normal((16, 16, 3, 3, 16, 16)) * 0.05).astype(np.float16)
+    xd = dev(x)
+    pw = U.pack_conv_weights_f16(dev(wt))
+    got = U.conv2d_NCHW16c_OHWI16o(xd, pw, 1, 1, padding=1)
+    U.device_status()
+    sample = [0, 1, 127, 255]
+    ref = oracle.conv2d_f16f32(x[sample], wt, (1, 1), (1, 1))
+    np.testing.assert_allclose(got[sample].cpu().numpy(), ref, rtol=RTOL, atol=ATOL)
+    for s0 in range(0, 256, 64):
+        part = U.conv2d_NCHW16c_OHWI16o(xd[s0:s0 + 64], pw, 1, 1, padding=1)
+        torch.testing.assert_close(part, got[s0:s0 + 64], rtol=RTOL, atol=ATOL)
+
+
+def test_conv_fp16_accepts_nchw_and_oihw_like_the_reference(U, oracle):
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((2, 32, 9, 9)).astype(np.float16)
+    w = (rng.standard_normal((48, 32, 3, 3)) * 0.05).astype(np.float16)
+    got = U.conv2d_NCHW16c_OHWI16o(dev(x), dev(w), 1, 1)
+    ref = oracle.conv2d_f16f32(no.pack_nchw_to_nchwc(x), no.pack_oihw_to_f16_weights(w))
+    assert tuple(got.shape) == (2, 3, 7, 7, 16)
+    np.testing.assert_allclose(got.cpu().numpy(), ref, rtol=RTOL, atol=ATOL)
+    from unit_b200.ops import _Attrs
+    out = U.conv2d_NCHW16c_OHWI16o_compute(_Attrs(strides=(1, 1)), [dev(x), dev(w)], 'float32')
+    assert isinstance(out, list) and torch.equal(out[0], got)
+
+
+@pytest.mark.parametrize('m,n,k', [(128, 768, 3072), (64, 192, 1024), (1, 16, 8), (130, 48, 72)])
+def test_gemm_fp16(U, oracle, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    b = (rng.standard_normal((k, n)) * 0.05).astype(np.float16)
+    got = U.gemm_f16f32(dev(a), dev(b))
+    U.device_status()
+    np.testing.assert_allclose(got.cpu().numpy(), no.gemm_f32(a, b), rtol=RTOL, atol=ATOL)
+
+
+# ---------------------------------------------------------------------------
+# layout kernels, host buffers, batch split, errors
+# ---------------------------------------------------------------------------
+def test_layout_kernels_match_numpy(U):
+    rng = np.random.default_rng(6)
+    x = rng.integers(0, 256, (3, 19, 5, 7), dtype=np.uint8)
+    for cb in (4, 16):
+        y = U.pack_data_nchwc(dev(x), cb)
+        assert np.array_equal(y.cpu().numpy(), no.pack_nchw_to_nchwc(x, cb))
+        assert np.array_equal(U.unpack_data_nchwc(y, 19).cpu().numpy(), x)
+    xf = rng.standard_normal((2, 32, 4, 4)).astype(np.float16)
+    assert np.array_equal(U.pack_data_nchwc(dev(xf)).cpu().numpy(), no.pack_nchw_to_nchwc(xf))
+    xi = rng.integers(-2 ** 31, 2 ** 31 - 1, (2, 16, 3, 3), dtype=np.int32)
+    assert np.array_equal(U.unpack_data_nchwc(U.pack_data_nchwc(dev(xi))).cpu().numpy(), xi)
+    w = rng.integers(-128, 128, (40, 19, 3, 2), dtype=np.int8)
+    assert np.array_equal(U.pack_weights_oihw_int8(dev(w)).cpu().numpy(), no.pack_oihw_to_int8_weights(w))
+    assert np.array_equal(U.pack_weights_oihw_int8(dev(w[:, :3]), 4).cpu().numpy(), no.pack_oihw_to_int8_weights(w[:, :3], 4))
+    wf = rng.standard_normal((40, 19, 3, 2)).astype(np.float16)
+    assert np.array_equal(U.pack_weights_oihw_f16(dev(wf)).cpu().numpy(), no.pack_oihw_to_f16_weights(wf))
+    U.device_status()
+
+
+def test_host_tensors_in_host_tensor_out(U, oracle):
+    rng = np.random.default_rng(12)
+    x = rng.integers(0, 256, (2, 4, 14, 14, 16), dtype=np.uint8)
+    w = rng.integers(-128, 128, (4, 4, 3, 3, 4, 16, 4), dtype=np.int8)
+    got = U.conv2d_NCHWc_int8(torch.from_numpy(x), torch.from_numpy(w), stride=1, padding=1)
+    assert not got.is_cuda
+    assert np.array_equal(got.numpy(), oracle.conv2d_u8s8(x, w, (1, 1), (1, 1)))
+
+
+def test_batch_split_equals_whole_batch(U):
+    """The multi-GPU partition: concatenating per-slice results equals the whole-batch result."""
+    from unit_b200 import resnet50 as R
+    from unit_b200.sharding import shard
+    l = R.LAYERS[9]
+    x, w, b = R.make_layer_inputs(l, 9, 24, config=5)
+    xd, bd = dev(x), dev(b)
+    pw = U.pack_conv_weights_int8(dev(w))
+    whole = U.conv2d_NCHWc_int8(xd, pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
+    for world in (2, 8):
+        parts = [U.conv2d_NCHWc_int8(shard(xd, r, world), pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
+                 for r in range(world)]
+        assert torch.equal(torch.cat(parts), whole)
+    U.device_status()
+
+
+def test_large_batch_property_config5(U, oracle):
+    """Full-size check (batch 256): a sample of images against the oracle, the rest by slice equality."""
+    from unit_b200 import resnet50 as R
+    for li in (3, 15):  # 3x3 64->64 @56 and 3x3 256->256 @14
+        l = R.LAYERS[li]
+        x, w, b = R.make_layer_inputs(l, li, 256, config=5)
+        xd, bd = dev(x), dev(b)
+        pw = U.pack_conv_weights_int8(dev(w))
+        got = U.conv2d_NCHWc_int8(xd, pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
+        U.device_status()
+        sample = [0, 100, 255]
+        ref = oracle.conv2d_u8s8(x[sample], w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8,
+                                 vnni=oracle.host_has_vnni())
+        assert np.array_equal(got[sample].cpu().numpy(), ref)
+        for s0 in range(0, 256, 32):
+            part = U.conv2d_NCHWc_int8(xd[s0:s0 + 32], pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
+            assert torch.equal(part, got[s0:s0 + 32])
+
+
+def test_error_behaviour(U):
+    x = torch.zeros((1, 4, 8, 8, 16), dtype=torch.uint8, device='cuda')
+    w = torch.zeros((4, 4, 3, 3, 4, 16, 4), dtype=torch.int8, device='cuda')
+    with pytest.raises(TypeError):
+        U.conv2d_NCHWc_int8(x.to(torch.int8), w)
+    with pytest.raises(ValueError):
+        U.conv2d_NCHWc_int8(x[:, :2], w)                       # channel mismatch
+    with pytest.raises(ValueError):
+        U.conv2d_NCHWc_int8(x, w, dilation=2)
+    with pytest.raises(ValueError):
+        U.conv2d_NCHWc_int8(x[:, :, :2, :2], w)                # kernel larger than input
+    with pytest.raises(ValueError):
+        U.conv2d_NCHWc_int8(x, w, out=torch.empty((1,), dtype=torch.int32, device='cuda'))
+    with pytest.raises(ValueError):
+        U.dense_dotprod(torch.zeros((4, 32), dtype=torch.uint8, device='cuda'),
+                        torch.zeros((1, 16, 16, 4), dtype=torch.int8, device='cuda'))   # K mismatch
+    empty = U.dense_dotprod(torch.zeros((0, 64), dtype=torch.uint8, device='cuda'),
+                            torch.zeros((1, 16, 16, 4), dtype=torch.int8, device='cuda'))
+    assert tuple(empty.shape) == (0, 16)
+    assert tuple(U.conv2d_NCHWc_int8(x[:0], w, padding=1).shape) == (0, 4, 8, 8, 16)   # empty batch
+    U.device_status()
+    assert U.launch_count() > 0

@@ -256,6 +256,8 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
             out_t = out
             if tuple(out_t.shape) != oshape or out_t.dtype != odt or not out_t.is_cuda or not out_t.is_contiguous():
                 raise ValueError(f'out must be a contiguous CUDA {odt} tensor of shape {oshape}')
+        if n == 0:
+            return out_t.cpu() if (host and out is None) else out_t
         if requant:
             check(L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), shift,
                                                    _ptr(out_t), _stream()), 'unit_conv2d_u8s8_requant_nchwc')
@@ -404,6 +406,8 @@ def conv2d_NCHW16c_OHWI16o(a: torch.Tensor, b, stride_h: int = 1, stride_w: int 
             out_t = out
             if tuple(out_t.shape) != oshape or out_t.dtype != torch.float32 or not out_t.is_cuda or not out_t.is_contiguous():
                 raise ValueError(f'out must be a contiguous CUDA float32 tensor of shape {oshape}')
+        if n == 0:
+            return out_t.cpu() if (host and out is None) else out_t
         check(L.unit_conv2d_f16f32_nchw16c(ctypes.byref(d), _ptr(a), _ptr(pw.buf), _ptr(out_t), _stream()),
               'unit_conv2d_f16f32_nchw16c')
     return out_t.cpu() if (host and out is None) else out_t
