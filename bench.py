@@ -210,7 +210,11 @@ def run_unit(args):
     # ---- build the 53 instances: packed weights shared per shape, own activations/outputs per instance
     instances = []   # (layer, x, packed, bias, out)
     per_layer = []   # (layer, [instance indices])
-    for li, l in enumerate(R.LAYERS):
+    layer_set = [l for l in R.LAYERS if not args.layer or l.name in args.layer]
+    if not layer_set:
+        raise SystemExit('no such layer; names: ' + ', '.join(l.name for l in R.LAYERS))
+    for l in layer_set:
+        li = R.LAYERS.index(l)
         cb, cs = l.c_block, l.c_in_stored
         gen.manual_seed(R.layer_seed(5, li, 1) + 7919 * rank)
         w = torch.randn((l.c_out // 16, cs // cb, l.k, l.k, cb // 4, 16, 4), device=dev, generator=gen)
@@ -263,7 +267,7 @@ def run_unit(args):
             torch.cuda.synchronize()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     U.device_status()
-    total_ops = R.sweep_ops(TOTAL_BATCH)
+    total_ops = sum(l.ops(TOTAL_BATCH) * l.count for l in layer_set)
     value = total_ops / (ms_step * 1e-3) / 1e12
     clocks = cs_.summary()
     clocks['sampled'] = 'timed region plus the same load continued untimed' if extended else 'timed region'
@@ -300,7 +304,7 @@ def run_unit(args):
                            'frac': round(roof / ms, 3)})
     if args.kernels_only:
         sum_kernel_ms, sum_roof_ms = ms_step, None
-    kernel_tops = R.sweep_ops(batch) / (sum_kernel_ms * 1e-3) / 1e12
+    kernel_tops = total_ops / world / (sum_kernel_ms * 1e-3) / 1e12
 
     e2e_value = e2e_ms = None
     h2d = d2h = 0
@@ -354,11 +358,12 @@ def run_unit(args):
             'metric': METRIC, 'value': value, 'unit': 'TOPS', 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
-            'config': {'workload': 'resnet50-int8-conv-sweep', 'global_batch': TOTAL_BATCH, 'per_gpu_batch': batch,
-                       'convolutions': 53, 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
+            'config': {'workload': 'resnet50-int8-conv-sweep' + ('' if not args.layer else ':' + '+'.join(args.layer)),
+                       'global_batch': TOTAL_BATCH, 'per_gpu_batch': batch,
+                       'convolutions': sum(l.count for l in layer_set), 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
                        'parallelism': f'batch-split x{world}, weights replicated, no collective',
                        'l2': 'every convolution instance has its own buffers; %.2f GB touched per step per GPU, '
-                             'larger than L2' % (R.sweep_bytes(batch) / 1e9)},
+                             'larger than L2' % (sum(l.bytes(batch) * l.count for l in layer_set) / 1e9)},
             'clocks': clocks,
             'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
@@ -387,6 +392,9 @@ def main():
     ap.add_argument('--impl', default='unit', choices=['unit', 'reference'])
     ap.add_argument('--e2e-steps', type=int, default=2)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--layer', action='append', default=None,
+                    help='restrict the sweep to the named layer(s) of unit_b200.resnet50.LAYERS (diagnostic runs; '
+                         'the JSON line then describes that subset)')
     ap.add_argument('--kernels-only', action='store_true',
                     help='timed region only: skip the per-layer pass, the end-to-end leg and the CPU baseline '
                          '(for profiler runs)')

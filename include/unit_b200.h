@@ -69,6 +69,15 @@ const char *unit_status_string(int status);
 int unit_device_status(void *stream);
 /* Number of kernels this library has launched in this process (monotonic). */
 uint64_t unit_launch_count(void);
+/* Tile trace for tuning (the counterpart of the reference's per-pass / per-op timers,
+ * apps/cpu/relay/conv2d.py:31-49).  While a buffer is attached, the first thread block of
+ * every contraction kernel writes 8 device-clock timestamps (u64 ns) per tile it processes,
+ * for its first capacity_tiles tiles:  [0] A producer starts the tile, [1] A producer has
+ * issued all copies, [2] B producer has issued all copies, [3] MMA issuer owns an
+ * accumulator, [4] first stage landed, [5] last MMA issued, [6] drain sees the accumulator
+ * complete, [7] drain has stored the tile.  d_buf: capacity_tiles * 64 bytes of device
+ * memory owned by the caller; NULL detaches.  Not for use while kernels are running. */
+int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 
 /* ---- packed weights ------------------------------------------------------ */
 

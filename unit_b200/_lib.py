@@ -35,6 +35,7 @@ SIGNATURES = {
     'unit_status_string': (ctypes.c_char_p, [_ci]),
     'unit_device_status': (_ci, [_vp]),
     'unit_launch_count': (ctypes.c_uint64, []),
+    'unit_trace_attach': (_ci, [_vp, _ci]),
     'unit_packed_weights_bytes_conv_i8': (_sz, [_dp]),
     'unit_pack_weights_conv_i8': (_ci, [_dp, _vp, _vp, _vp]),
     'unit_packed_weights_bytes_conv_f16': (_sz, [_dp]),

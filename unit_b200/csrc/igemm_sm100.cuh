@@ -21,14 +21,21 @@
 // on the device into ready-made [KC][BN][16 B] stage blocks and arrive with a
 // single bulk copy (cp.async.bulk, no tensor map, no multicast) per stage.
 //
-// Warp roles (320 threads):
-//   warps 0-3  drain: tcgen05.ld the finished accumulator (warp w owns TMEM
-//              lanes 32w..32w+31 = tile rows), apply the epilogue, store
-//   warps 4-7  A producers: 128 threads gather A columns with cp.async
-//   warp  8    B producer: one lane issues the bulk copies
-//   warp  9    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
-// Two accumulators (2 x BN <= 512 TMEM columns) let the drain of tile i overlap
-// the main loop of tile i+1.
+// A CTA tile is MT x 128 rows by BN columns (MT = 1 or 2): with MT = 2 one B
+// stage feeds two accumulators, which halves the weight bytes fetched per MAC.
+//
+// Warp roles (448 threads):
+//   warps 0-7   drain: tcgen05.ld the finished accumulator (warp w may touch
+//               TMEM lanes 32(w%4)..+31 = tile rows), apply the epilogue, store;
+//               the two warps of a lane quadrant split the sub-tiles (MT = 2)
+//               or the columns (MT = 1)
+//   warps 8-11  A producers: 128 threads gather A columns with cp.async; each
+//               thread's copies arrive on the stage barrier by themselves
+//               (cp.async.mbarrier.arrive.noinc), so no producer waits for data
+//   warp  12    B producer: one lane issues the bulk copies
+//   warp  13    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
+// When two accumulator sets fit in the 512 TMEM columns, the drain of tile i
+// overlaps the main loop of tile i+1.
 //
 // Every wait on an mbarrier is bounded in time.  A wait that runs out sets a
 // CTA-wide abort flag and a global error word; all roles then leave their
@@ -53,8 +60,9 @@ enum EpiMode : int {
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 12;
-constexpr int kLag = 2;  // cp.async groups a producer keeps in flight
-constexpr int kNumThreads = 320;
+constexpr int kNumThreads = 448;
+constexpr int kDrainWarps = 8, kFirstProducerWarp = 8, kBWarp = 12, kMmaWarp = 13;
+constexpr int kBiasSmem = 2048;  // output channels whose bias is staged in shared memory
 constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
 
 struct IgemmParams {
@@ -79,6 +87,8 @@ struct IgemmParams {
   long long lda;      // A_DENSE: row pitch in bytes
   long long ldc;      // EPI_RAW_ROWS: row pitch in elements
   int shift;          // EPI_REQ_NCHWC
+  unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
+  int trace_cap;              // tiles the trace buffer holds
 };
 
 // ---------------------------------------------------------------------------
@@ -142,6 +152,12 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// The barrier receives one arrival from this thread once all of the thread's earlier
+// cp.async copies have landed (the pending count is not raised: the arrival is part of
+// the count the barrier was initialised with).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -198,7 +214,34 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ int32_t add_sat(int32_t a, int32_t b) {
+  int32_t d;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// d = (c << 16) | (sat_u8(a) << 8) | sat_u8(b)
+__device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c) {
+  uint32_t d;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Tile trace: CTA 0 records when each role passes a point of tile `lt` (slot 0-7).
+__device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 8u + slot] = global_timer_ns();
+}
 
 // Shared-memory matrix descriptor, K-major, no swizzle.
 //   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
@@ -219,7 +262,8 @@ __device__ __forceinline__ uint32_t make_idesc(int bn) {
   return d;
 }
 
-struct alignas(8) PipeShared {
+struct alignas(16) PipeShared {
+  int32_t bias[kBiasSmem];  // copy of the bias vector (zeros when there is none)
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
   unsigned long long tfull[2];
@@ -231,35 +275,110 @@ struct alignas(8) PipeShared {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int AMODE, int EPI, bool F16>
+// Epilogue for 16 consecutive columns of one row: v = accumulator words.
+template <int EPI>
+__device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, const uint32_t *v, int col0,
+                                              long long o) {
+  if constexpr (EPI == EPI_RAW_ROWS) {
+    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  } else {
+    int32_t bv[16];
+    if (bias_s != nullptr) {  // staged in shared memory: one broadcast read per 4 values
+      const int4 *bp = reinterpret_cast<const int4 *>(bias_s + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int4 t = bp[q];
+        bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+      }
+    } else if (p.bias != nullptr) {
+      const int4 *bp = reinterpret_cast<const int4 *>(p.bias + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int4 t = __ldg(bp + q);
+        bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) bv[q] = 0;
+    }
+    if constexpr (EPI == EPI_RAW_NCHWC) {
+      uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(v[4 * q] + (uint32_t)bv[4 * q], v[4 * q + 1] + (uint32_t)bv[4 * q + 1],
+                            v[4 * q + 2] + (uint32_t)bv[4 * q + 2], v[4 * q + 3] + (uint32_t)bv[4 * q + 3]);
+    } else {
+      uint32_t w[4];
+      if (p.shift <= 23) {
+        // 32-bit path.  Saturating adds keep the order of acc + bias + rounding; a sum that
+        // saturates is >= 2^31 - 1 or <= -2^31, and for shift <= 23 both ends still clamp to
+        // 255 and 0, so the result equals the 64-bit definition.
+        const int32_t rnd = 1 << (p.shift - 1);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          int32_t t[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) t[e] = add_sat(add_sat((int32_t)v[4 * q + e], bv[4 * q + e]), rnd) >> p.shift;
+          w[q] = pack_sat_u8(t[1], t[0], pack_sat_u8(t[3], t[2], 0u));
+        }
+      } else {
+        const long long rnd = 1ll << (p.shift - 1);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t packed = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            long long t = (long long)(int32_t)v[4 * q + e] + (long long)bv[4 * q + e] + rnd;
+            t >>= p.shift;
+            t = t < 0 ? 0 : (t > 255 ? 255 : t);
+            packed |= (uint32_t)t << (8 * e);
+          }
+          w[q] = packed;
+        }
+      }
+      *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+template <int AMODE, int EPI, bool F16, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const uint32_t a_stage_bytes = (uint32_t)p.kc * kTileM * 16u;
+  constexpr uint32_t kSubBytes = kTileM * 16u;                       // one K column of one 128-row sub-tile
+  const uint32_t a_sub_bytes = (uint32_t)p.kc * kSubBytes;           // one sub-tile of one stage
+  const uint32_t a_stage_bytes = (uint32_t)MT * a_sub_bytes;
   const uint32_t b_stage_bytes = (uint32_t)p.kc * (uint32_t)p.bn * 16u;
   const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
   PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes);
   const uint32_t smem_base = smem_u32(smem);
   volatile int *abort_flag = &ps->abort_flag;
+  // accumulator sets that fit in the 512 TMEM columns (2 = drain overlaps the next main loop)
+  const uint32_t nslots = (512u / ((uint32_t)MT * (uint32_t)p.bn)) >= 2u ? 2u : 1u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&ps->full[s]), 4 + 1);  // 4 A-producer warps + the B producer
-      mbar_init(smem_u32(&ps->empty[s]), 1);     // one tcgen05.commit
+      mbar_init(smem_u32(&ps->full[s]), 128 + 1);  // 128 A-producer threads + the B producer
+      mbar_init(smem_u32(&ps->empty[s]), 1);       // one tcgen05.commit
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ps->tfull[i]), 1);   // one tcgen05.commit
-      mbar_init(smem_u32(&ps->tempty[i]), 4);  // 4 drain warps
+      mbar_init(smem_u32(&ps->tfull[i]), 1);             // one tcgen05.commit
+      mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps);  // the drain warps
     }
     ps->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&ps->tmem_base), 512);
     tmem_relinquish();
   }
+  const bool bias_staged = EPI != EPI_RAW_ROWS && p.n_total <= kBiasSmem;
+  if (bias_staged)
+    for (int i = threadIdx.x; i < p.n_total; i += kNumThreads) ps->bias[i] = p.bias != nullptr ? __ldg(p.bias + i) : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -267,48 +386,52 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (warp >= 4 && warp < 8) {
+  if (warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A producers =====================
-    const int pw = warp - 4;
-    uint32_t it = 0;  // stage iterations issued by this thread
+    const int pw = warp - kFirstProducerWarp;
+    uint32_t s = 0, ring_phase = 0;  // ring position and the number of wraps (mod 2)
+    uint32_t lt = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
       const int m_tile = tile / p.n_tiles;
-      const long long m0 = (long long)m_tile * kTileM;
+      const long long m0 = (long long)m_tile * (kTileM * MT);
 
-      // rows this lane feeds and their decoded positions
+      // rows this lane feeds (per sub-tile) and their decoded positions
       constexpr int RPT = (AMODE == A_CONV_I8 || AMODE == A_STEM_I8) ? 1 : (AMODE == A_CONV_F16 ? 2 : 4);
       int row[RPT];
-      bool rvalid[RPT];
-      const uint8_t *rbase[RPT];
-      int ih0[RPT], iw0[RPT];
+      bool rvalid[MT][RPT];
+      const uint8_t *rbase[MT][RPT];
+      int ih0[MT][RPT], iw0[MT][RPT];
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
         if constexpr (AMODE == A_CONV_I8 || AMODE == A_STEM_I8) row[i] = pw * 32 + lane;
         else if constexpr (AMODE == A_CONV_F16) row[i] = pw * 32 + i * 16 + (lane >> 4) * 8 + (lane & 7);
         else row[i] = pw * 32 + i * 8 + (lane & 7);
-        const long long m = m0 + row[i];
-        rvalid[i] = m < p.m_total;
-        if constexpr (AMODE == A_DENSE) {
-          rbase[i] = p.a + (rvalid[i] ? m : 0) * p.lda;
-          ih0[i] = iw0[i] = 0;
-        } else {
-          const long long mm = rvalid[i] ? m : 0;
-          const int ohw = p.OH * p.OW;
-          const int n_img = (int)(mm / ohw);
-          const int rem = (int)(mm - (long long)n_img * ohw);
-          const int oh = rem / p.OW, ow = rem - oh * p.OW;
-          ih0[i] = oh * p.sh - p.ph;
-          iw0[i] = ow * p.sw - p.pw;
-          rbase[i] = p.a + (long long)n_img * p.img_bytes;
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          const long long m = m0 + t * kTileM + row[i];
+          rvalid[t][i] = m < p.m_total;
+          if constexpr (AMODE == A_DENSE) {
+            rbase[t][i] = p.a + (rvalid[t][i] ? m : 0) * p.lda;
+            ih0[t][i] = iw0[t][i] = 0;
+          } else {
+            // m_total < 2^31 is checked on the host: 32-bit divisions
+            const unsigned mm = rvalid[t][i] ? (unsigned)m : 0u;
+            const unsigned ohw = (unsigned)(p.OH * p.OW);
+            const int n_img = (int)(mm / ohw);
+            const int rem = (int)(mm - (unsigned)n_img * ohw);
+            const int oh = rem / p.OW, ow = rem - oh * p.OW;
+            ih0[t][i] = oh * p.sh - p.ph;
+            iw0[t][i] = ow * p.sw - p.pw;
+            rbase[t][i] = p.a + (long long)n_img * p.img_bytes;
+          }
         }
       }
 
+      if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 0);
       int ci = 0, kh = 0, kw = 0;  // position of the next K column (conv modes)
-      for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-        const uint32_t s = it % (uint32_t)p.stages;
-        const uint32_t par = ((it / (uint32_t)p.stages) & 1u) ^ 1u;
-        if (!mbar_wait(smem_u32(&ps->empty[s]), par, abort_flag, p.err, kErrWaitEmpty)) {
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
           alive = false;
           break;
         }
@@ -316,10 +439,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
         if constexpr (AMODE == A_CONV_I8) {
           for (int jj = 0; jj < p.kc; ++jj) {
             const int j = ks * p.kc + jj;
-            const int ih = ih0[0] + kh, iw = iw0[0] + kw;
-            const bool ok = rvalid[0] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-            const uint8_t *src = ok ? rbase[0] + ((long long)(ci * p.H + ih) * p.W + iw) * 16 : p.a;
-            cp_async16(a_dst + (uint32_t)jj * (kTileM * 16u) + (uint32_t)row[0] * 16u, src, ok ? 16u : 0u);
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+              const int ih = ih0[t][0] + kh, iw = iw0[t][0] + kw;
+              const bool ok = rvalid[t][0] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+              const uint8_t *src = ok ? rbase[t][0] + ((long long)(ci * p.H + ih) * p.W + iw) * 16 : p.a;
+              cp_async16(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes + (uint32_t)row[0] * 16u, src,
+                         ok ? 16u : 0u);
+            }
             if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
           }
         } else if constexpr (AMODE == A_CONV_F16) {
@@ -327,11 +454,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
           for (int jj = 0; jj < p.kc; jj += 2) {
             const int j = ks * p.kc + jj;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int ih = ih0[i] + kh, iw = iw0[i] + kw;
-              const bool ok = rvalid[i] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-              const uint8_t *src = ok ? rbase[i] + ((long long)(ci * p.H + ih) * p.W + iw) * 32 + half * 16 : p.a;
-              cp_async16(a_dst + (uint32_t)(jj + half) * (kTileM * 16u) + (uint32_t)row[i] * 16u, src, ok ? 16u : 0u);
+            for (int t = 0; t < MT; ++t) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int ih = ih0[t][i] + kh, iw = iw0[t][i] + kw;
+                const bool ok =
+                    rvalid[t][i] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+                const uint8_t *src = ok ? rbase[t][i] + ((long long)(ci * p.H + ih) * p.W + iw) * 32 + half * 16 : p.a;
+                cp_async16(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)(jj + half) * kSubBytes + (uint32_t)row[i] * 16u,
+                           src, ok ? 16u : 0u);
+              }
             }
             if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
           }
@@ -339,16 +471,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
           // column = (ci, kh, group of 4 kw taps); ci / kh / kw track (chunk, kh, group)
           for (int jj = 0; jj < p.kc; ++jj) {
             const int j = ks * p.kc + jj;
-            const int ih = ih0[0] + kh;
-            const bool rok = rvalid[0] && j < p.cols && (unsigned)ih < (unsigned)p.H;
-            const uint32_t dst = a_dst + (uint32_t)jj * (kTileM * 16u) + (uint32_t)row[0] * 16u;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const int tap = kw * 4 + t;
-              const int iw = iw0[0] + tap;
-              const bool ok = rok && tap < p.KW && (unsigned)iw < (unsigned)p.W;
-              const uint8_t *src = ok ? rbase[0] + ((long long)(ci * p.H + ih) * p.W + iw) * 4 : p.a;
-              cp_async4(dst + t * 4u, src, ok ? 4u : 0u);
+            for (int t = 0; t < MT; ++t) {
+              const int ih = ih0[t][0] + kh;
+              const bool rok = rvalid[t][0] && j < p.cols && (unsigned)ih < (unsigned)p.H;
+              const uint32_t dst = a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes + (uint32_t)row[0] * 16u;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int tap = kw * 4 + q;
+                const int iw = iw0[t][0] + tap;
+                const bool ok = rok && tap < p.KW && (unsigned)iw < (unsigned)p.W;
+                const uint8_t *src = ok ? rbase[t][0] + ((long long)(ci * p.H + ih) * p.W + iw) * 4 : p.a;
+                cp_async4(dst + q * 4u, src, ok ? 4u : 0u);
+              }
             }
             if (++kw == p.kwg) { kw = 0; if (++kh == p.KH) { kh = 0; ++ci; } }
           }
@@ -357,44 +492,37 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
           for (int jj = 0; jj < p.kc; jj += 4) {
             const int jl = jj + csub;
             const int j = ks * p.kc + jl;
+            if (jl < p.kc) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const bool ok = rvalid[i] && j < p.cols && jl < p.kc;
-              const uint8_t *src = ok ? rbase[i] + (long long)j * 16 : p.a;
-              if (jl < p.kc)
-                cp_async16(a_dst + (uint32_t)jl * (kTileM * 16u) + (uint32_t)row[i] * 16u, src, ok ? 16u : 0u);
+              for (int t = 0; t < MT; ++t) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const bool ok = rvalid[t][i] && j < p.cols;
+                  const uint8_t *src = ok ? rbase[t][i] + (long long)j * 16 : p.a;
+                  cp_async16(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jl * kSubBytes + (uint32_t)row[i] * 16u, src,
+                             ok ? 16u : 0u);
+                }
+              }
             }
           }
         }
-        cp_async_commit();
-        if (it >= (uint32_t)kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ps->full[(it - kLag) % (uint32_t)p.stages]));
-        }
+        cp_async_arrive_noinc(smem_u32(&ps->full[s]));
+        if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
       }
+      if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 1);
     }
-    // hand over the stages still in flight
-    cp_async_wait<0>();
-    fence_proxy_async();
-    __syncwarp();
-    if (alive && lane == 0) {
-      const uint32_t first = it >= (uint32_t)kLag ? it - kLag : 0u;
-      for (uint32_t q = first; q < it; ++q) mbar_arrive(smem_u32(&ps->full[q % (uint32_t)p.stages]));
-    }
-  } else if (warp == 8) {
+    cp_async_wait<0>();  // nothing of this thread is in flight when the CTA winds down
+  } else if (warp == kBWarp) {
     // ===================== B producer =====================
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, ring_phase = 0;
+      uint32_t lt = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
         const int n_tile = tile % p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const uint32_t s = it % (uint32_t)p.stages;
-          const uint32_t par = ((it / (uint32_t)p.stages) & 1u) ^ 1u;
-          if (!mbar_wait(smem_u32(&ps->empty[s]), par, abort_flag, p.err, kErrWaitEmpty)) {
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
             alive = false;
             break;
           }
@@ -402,126 +530,114 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
           mbar_arrive_expect_tx(bar, b_stage_bytes);
           bulk_copy_g2s(smem_base + s * stage_bytes + a_stage_bytes, src + (size_t)ks * b_stage_bytes,
                         b_stage_bytes, bar);
+          if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
+        trace_mark(p, lt, 2);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn);
-      uint32_t it = 0;
+      uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;  // tiles done by this CTA
       bool alive = true;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
-        const uint32_t acc = lt & 1u;
-        if (!mbar_wait(smem_u32(&ps->tempty[acc]), ((lt >> 1) & 1u) ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
+        const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
+        const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
+        if (!mbar_wait(smem_u32(&ps->tempty[slot]), (use & 1u) ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
           alive = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.bn;
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const uint32_t s = it % (uint32_t)p.stages;
-          if (!mbar_wait(smem_u32(&ps->full[s]), (it / (uint32_t)p.stages) & 1u, abort_flag, p.err, kErrWaitFull)) {
+        trace_mark(p, lt, 3);
+        const uint32_t d_tmem = tmem_base + slot * (uint32_t)MT * (uint32_t)p.bn;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, abort_flag, p.err, kErrWaitFull)) {
             alive = false;
             break;
           }
           tc_fence_after();
+          if (ks == 0) trace_mark(p, lt, 4);
           const uint32_t a_addr = smem_base + s * stage_bytes;
           const uint32_t b_addr = a_addr + a_stage_bytes;
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
           for (int k = 0; k < nk; ++k) {
-            const uint64_t adesc = make_smem_desc(a_addr + (uint32_t)k * 2u * (kTileM * 16u), kTileM * 16u, 128u);
             const uint64_t bdesc =
                 make_smem_desc(b_addr + (uint32_t)k * 2u * ((uint32_t)p.bn * 16u), (uint32_t)p.bn * 16u, 128u);
-            tc_mma<F16>(d_tmem, adesc, bdesc, idesc, (ks | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+              const uint64_t adesc =
+                  make_smem_desc(a_addr + (uint32_t)t * a_sub_bytes + (uint32_t)k * 2u * kSubBytes, kSubBytes, 128u);
+              tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, (ks | k) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
+          if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
-        if (alive) tc_commit(smem_u32(&ps->tfull[acc]));  // accumulator complete
+        if (alive) tc_commit(smem_u32(&ps->tfull[slot]));  // accumulators complete
+        trace_mark(p, lt, 5);
       }
     }
-  } else {
-    // ===================== drain (warps 0-3) =====================
+  } else if (warp < kDrainWarps) {
+    // ===================== drain (warps 0-7) =====================
     uint32_t lt = 0;
     bool alive = true;
     const int ohw = p.OH * p.OW;
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    const int part = warp >> 2;  // MT = 2: sub-tile; MT = 1: which share of the column groups
+    const int groups = p.bn >> 4;
+    const int sub = (MT == 2) ? part : 0;
+    const int g_begin = (MT == 2) ? 0 : (part ? (groups + 1) / 2 : 0);
+    const int g_end = (MT == 2) ? groups : (part ? groups : (groups + 1) / 2);
+    const int32_t *bias_s = bias_staged ? ps->bias : nullptr;
     for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile % p.n_tiles;
-      const uint32_t acc = lt & 1u;
-      if (!mbar_wait(smem_u32(&ps->tfull[acc]), (lt >> 1) & 1u, abort_flag, p.err, kErrWaitTmemFull)) {
+      const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
+      const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
+      if (!mbar_wait(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull)) {
         alive = false;
         break;
       }
       tc_fence_after();
-      const long long m = (long long)m_tile * kTileM + warp * 32 + lane;
+      if (threadIdx.x == 0) trace_mark(p, lt, 6);
+      const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + quad * 32 + lane;
       const bool mvalid = m < p.m_total;
       long long obase = 0;  // element offset of this row's first stored value
+      long long gstride = 16;  // element distance between consecutive 16-column groups
       if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
       } else {
-        const long long mm = mvalid ? m : 0;
-        const long long n_img = mm / ohw;
-        const long long rem = mm - n_img * ohw;
-        // [n][oc/16][ohw][16]: chunk g of this tile adds g * ohw * 16
+        const unsigned mm = mvalid ? (unsigned)m : 0u;
+        const long long n_img = (long long)(mm / (unsigned)ohw);
+        const long long rem = (long long)mm - n_img * ohw;
+        // [n][oc/16][ohw][16]: column group g of this tile adds g * ohw * 16
         obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
+        gstride = (long long)ohw * 16;
       }
-      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.bn;
-      const int groups = p.bn >> 4;
-      for (int g = 0; g < groups; ++g) {
+      const uint32_t t_row =
+          tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
+      int g = g_begin;
+      for (; g + 2 <= g_end; g += 2) {
+        uint32_t v[32];
+        tmem_ld32(t_row + (uint32_t)g * 16u, v);
+        tmem_ld_wait();
+        const int col0 = n_tile * p.bn + g * 16;
+        if (mvalid && col0 < p.n_total) store_group16<EPI>(p, bias_s, v, col0, obase + g * gstride);
+        if (mvalid && col0 + 16 < p.n_total) store_group16<EPI>(p, bias_s, v + 16, col0 + 16, obase + (g + 1) * gstride);
+      }
+      if (g < g_end) {
         uint32_t v[16];
         tmem_ld16(t_row + (uint32_t)g * 16u, v);
         tmem_ld_wait();
         const int col0 = n_tile * p.bn + g * 16;
-        if (!mvalid || col0 >= p.n_total) continue;
-        if constexpr (EPI == EPI_RAW_ROWS) {
-          uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + obase + g * 16);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        } else {
-          int32_t bv[16];
-          if (p.bias != nullptr) {
-            const int4 *bp = reinterpret_cast<const int4 *>(p.bias + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int4 t = __ldg(bp + q);
-              bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 16; ++q) bv[q] = 0;
-          }
-          const long long o = obase + (long long)g * ohw * 16;
-          if constexpr (EPI == EPI_RAW_NCHWC) {
-            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_uint4(v[4 * q] + (uint32_t)bv[4 * q], v[4 * q + 1] + (uint32_t)bv[4 * q + 1],
-                                  v[4 * q + 2] + (uint32_t)bv[4 * q + 2], v[4 * q + 3] + (uint32_t)bv[4 * q + 3]);
-          } else {
-            uint32_t w[4];
-            const long long rnd = 1ll << (p.shift - 1);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t packed = 0;
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                // 64-bit sum so that acc + bias + rounding cannot wrap
-                long long t = (long long)(int32_t)v[4 * q + e] + (long long)bv[4 * q + e] + rnd;
-                t >>= p.shift;
-                t = t < 0 ? 0 : (t > 255 ? 255 : t);
-                packed |= (uint32_t)t << (8 * e);
-              }
-              w[q] = packed;
-            }
-            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
+        if (mvalid && col0 < p.n_total) store_group16<EPI>(p, bias_s, v, col0, obase + g * gstride);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[acc]));
+      if (threadIdx.x == 0) trace_mark(p, lt, 7);
+      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
     }
   }
 
@@ -533,7 +649,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "igemm_sm100.cuh"
@@ -14,41 +15,64 @@ namespace unit {
 
 __device__ unsigned int g_error_word = 0;
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<unsigned long long *> g_trace{nullptr};
+static std::atomic<int> g_trace_cap{0};
 
 // ---------------------------------------------------------------------------
 // tile selection (a pure function of the problem, shared by pack and launch)
 // ---------------------------------------------------------------------------
 struct TileCfg {
-  int bn = 0, kc = 0, cols = 0, cols_pad = 0, k_stages = 0, last_ksteps = 0, n_tiles = 0, stages = 0;
-  size_t b_stage_bytes = 0, smem_bytes = 0;
+  int bn = 0, kc = 0, cols = 0, cols_pad = 0, k_stages = 0, last_ksteps = 0, n_tiles = 0;
+  size_t b_stage_bytes = 0;
 };
 
 constexpr size_t kSmemBudget = 200 * 1024;
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// Depends on the weight tensor only (never on the batch), so packed weights stay valid
+// for every input size.  kc is chosen so that four stages of the larger (two sub-tile)
+// CTA tile fit in shared memory.
 static TileCfg make_cfg(int n_total, int cols) {
   TileCfg c;
   c.cols = cols;
   c.cols_pad = round_up(cols, 2);
   c.n_tiles = (n_total + 255) / 256;
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
+  const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
   static const int cand[] = {8, 6, 4, 12, 10, 14, 16};
-  c.kc = 8;
+  c.kc = 0;
   for (int kc : cand)
-    if (c.cols_pad % kc == 0) { c.kc = kc; break; }
+    if (kc <= kc_max && c.cols_pad % kc == 0) { c.kc = kc; break; }
+  if (c.kc == 0) c.kc = kc_max >= 8 ? 8 : (kc_max & ~1);  // last stage is partial
   if (c.cols_pad < c.kc) c.kc = c.cols_pad;
   c.k_stages = (c.cols_pad + c.kc - 1) / c.kc;
   const int last_cols = c.cols_pad - (c.k_stages - 1) * c.kc;
   c.last_ksteps = last_cols / 2;
   c.b_stage_bytes = (size_t)c.kc * c.bn * 16;
-  const size_t stage = (size_t)c.kc * 16 * (kTileM + c.bn);
+  return c;
+}
+
+// Rows per CTA tile: two 128-row sub-tiles share each weight stage when the larger tiles
+// still occupy at least half of the SMs and the reduction is long enough for the weight
+// traffic to matter (measured: fewer weight bytes per MAC outweighs a partly idle GPU).
+static int choose_mt(const TileCfg &c, long long m_total, int sms) {
+  static const int forced = [] {
+    const char *e = getenv("UNIT_B200_MT");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2) return forced;
+  const long long tiles2 = (m_total + 2 * kTileM - 1) / (2 * kTileM) * c.n_tiles;
+  return (2 * tiles2 >= sms && c.cols_pad >= 16) ? 2 : 1;
+}
+
+static int stages_for(const TileCfg &c, int mt, size_t *smem_bytes) {
+  const size_t stage = (size_t)c.kc * 16 * ((size_t)mt * kTileM + c.bn);
   int s = (int)(kSmemBudget / stage);
   if (s > kMaxStages) s = kMaxStages;
-  if (s < kLag + 1) s = kLag + 1;
-  c.stages = s;
-  c.smem_bytes = (size_t)s * stage + sizeof(PipeShared) + 128;
-  return c;
+  if (s < 2) s = 2;
+  *smem_bytes = (size_t)s * stage + sizeof(PipeShared) + 128;
+  return s;
 }
 
 static int conv_cols_i8(const unit_conv_desc *d) {
@@ -68,6 +92,8 @@ static int check_conv(const unit_conv_desc *d, bool f16) {
   if (d->kh > 64 || d->kw > 64) return UNIT_ERR_SHAPE;
   const long long img = (long long)d->c_in * d->h * d->w * (f16 ? 2 : 1);
   if (img >= (1ll << 31)) return UNIT_ERR_TOO_LARGE;
+  const long long oh = (d->h + 2 * d->pad_h - d->kh) / d->stride_h + 1, ow = (d->w + 2 * d->pad_w - d->kw) / d->stride_w + 1;
+  if ((long long)d->n * oh * ow >= (1ll << 31) - 512) return UNIT_ERR_TOO_LARGE;  // output pixels index in 32 bits
   return UNIT_OK;
 }
 
@@ -268,34 +294,43 @@ static unsigned grid_for(long long total) {
 // ---------------------------------------------------------------------------
 // launches of the contraction kernel
 // ---------------------------------------------------------------------------
-template <int AMODE, int EPI, bool F16>
-static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st) {
+template <int AMODE, int EPI, bool F16, int MT>
+static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, int sms) {
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = igemm_kernel<AMODE, EPI, F16>;
+  auto kern = igemm_kernel<AMODE, EPI, F16, MT>;
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   });
   if (attr_err != cudaSuccess) return UNIT_ERR_LAUNCH;
+  size_t smem_bytes = 0;
+  p.stages = stages_for(c, MT, &smem_bytes);
+  p.m_tiles = (int)((p.m_total + kTileM * MT - 1) / (kTileM * MT));
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  kern<<<grid, kNumThreads, smem_bytes, st>>>(p);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+}
+
+template <int AMODE, int EPI, bool F16>
+static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st) {
   p.bn = c.bn;
   p.kc = c.kc;
   p.cols = c.cols;
   p.k_stages = c.k_stages;
   p.last_ksteps = c.last_ksteps;
-  p.stages = c.stages;
   p.n_tiles = c.n_tiles;
-  p.m_tiles = (int)((p.m_total + kTileM - 1) / kTileM);
   void *err_ptr = nullptr;
   if (cudaGetSymbolAddress(&err_ptr, g_error_word) != cudaSuccess) return UNIT_ERR_LAUNCH;
   p.err = static_cast<unsigned int *>(err_ptr);
-  long long tiles = (long long)p.m_tiles * p.n_tiles;
+  p.trace = g_trace.load();
+  p.trace_cap = g_trace_cap.load();
   const int sms = sm_count();
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kNumThreads, c.smem_bytes, st>>>(p);
-  g_launches.fetch_add(1);
-  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+  if (choose_mt(c, p.m_total, sms) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms);
+  return launch_igemm_mt<AMODE, EPI, F16, 1>(p, c, st, sms);
 }
 
 static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
@@ -365,6 +400,13 @@ int unit_device_status(void *stream) {
 }
 
 uint64_t unit_launch_count(void) { return g_launches.load(); }
+
+int unit_trace_attach(void *d_buf, int32_t capacity_tiles) {
+  if (d_buf != nullptr && (capacity_tiles < 1 || !aligned16(d_buf))) return UNIT_ERR_SHAPE;
+  g_trace_cap.store(d_buf ? capacity_tiles : 0);
+  g_trace.store(static_cast<unsigned long long *>(d_buf));
+  return UNIT_OK;
+}
 
 // ---- packed weights --------------------------------------------------------
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
