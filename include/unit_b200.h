@@ -71,11 +71,12 @@ int unit_device_status(void *stream);
 uint64_t unit_launch_count(void);
 /* Tile trace for tuning (the counterpart of the reference's per-pass / per-op timers,
  * apps/cpu/relay/conv2d.py:31-49).  While a buffer is attached, the first thread block of
- * every contraction kernel writes 8 device-clock timestamps (u64 ns) per tile it processes,
+ * every contraction kernel writes 16 u64 timestamps per tile it processes,
  * for its first capacity_tiles tiles:  [0] A producer starts the tile, [1] A producer has
  * issued all copies, [2] B producer has issued all copies, [3] MMA issuer owns an
  * accumulator, [4] first stage landed, [5] last MMA issued, [6] drain sees the accumulator
- * complete, [7] drain has stored the tile.  d_buf: capacity_tiles * 64 bytes of device
+ * complete, [7] drain has stored the tile; the rest unused.  Timestamps are SM cycle counts
+ * (clock64) of the SM that runs that block.  d_buf: capacity_tiles * 128 bytes of device
  * memory owned by the caller; NULL detaches.  Not for use while kernels are running. */
 int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 

@@ -24,16 +24,17 @@
 // A CTA tile is MT x 128 rows by BN columns (MT = 1 or 2): with MT = 2 one B
 // stage feeds two accumulators, which halves the weight bytes fetched per MAC.
 //
-// Warp roles (448 threads):
-//   warps 0-7   drain: tcgen05.ld the finished accumulator (warp w may touch
+// Warp roles (704 threads):
+//   warps 0-15  drain: tcgen05.ld the finished accumulator (warp w may touch
 //               TMEM lanes 32(w%4)..+31 = tile rows), apply the epilogue, store;
-//               the two warps of a lane quadrant split the sub-tiles (MT = 2)
-//               or the columns (MT = 1)
-//   warps 8-11  A producers: 128 threads gather A columns with cp.async; each
+//               the four warps of a lane quadrant split the sub-tiles and the
+//               columns.  The drain is plain integer code whose speed comes from
+//               warp-level parallelism, hence the many warps
+//   warps 16-19 A producers: 128 threads gather A columns with cp.async; each
 //               thread's copies arrive on the stage barrier by themselves
 //               (cp.async.mbarrier.arrive.noinc), so no producer waits for data
-//   warp  12    B producer: one lane issues the bulk copies
-//   warp  13    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
+//   warp  20    B producer: one lane issues the bulk copies
+//   warp  21    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
 // When two accumulator sets fit in the 512 TMEM columns, the drain of tile i
 // overlaps the main loop of tile i+1.
 //
@@ -60,9 +61,9 @@ enum EpiMode : int {
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 12;
-constexpr int kNumThreads = 448;
-constexpr int kDrainWarps = 8, kFirstProducerWarp = 8, kBWarp = 12, kMmaWarp = 13;
-constexpr int kBiasSmem = 2048;  // output channels whose bias is staged in shared memory
+constexpr int kNumThreads = 704;
+constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21;
+constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
 constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
 
 struct IgemmParams {
@@ -87,6 +88,7 @@ struct IgemmParams {
   long long lda;      // A_DENSE: row pitch in bytes
   long long ldc;      // EPI_RAW_ROWS: row pitch in elements
   int shift;          // EPI_REQ_NCHWC
+  long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
 };
@@ -123,14 +125,29 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up after ~1 s (or when another role already aborted).
+// Same test, but the thread may stay suspended for up to `hint_ns` before it reports "not yet".
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~1 s (or when another role already aborted).  Retries back
+// off (suspended try_wait plus a short sleep) so that waiting threads leave the issue slots
+// and the shared-memory pipe to the warps that have work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           unsigned int *err, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
-  for (uint32_t it = 0; it < (1u << 28); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u) {
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    if (mbar_try_wait_hint(bar, parity, 400u)) return true;
+    __nanosleep(32);
+    if ((it & 15u) == 15u) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > 1000000000ull) break;
     }
@@ -138,6 +155,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   atomicCAS(err, 0u, code);
   return false;
+}
+// Warp-collective form: lane 0 waits, the result is broadcast (32x fewer barrier probes).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                               unsigned int *err, uint32_t code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, err, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
@@ -236,11 +260,31 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
   asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
+// Waits for this thread's TMEM reads; the registers are operands so that the compiler keeps
+// every use of them behind the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
+// Named barrier 1 over the drain warps; returns the OR of `flag` over all of them.
+__device__ __forceinline__ bool drain_barrier_or(int flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(flag), "n"(kDrainWarps * 32)
+      : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Tile trace: CTA 0 records when each role passes a point of tile `lt` (slot 0-7).
 __device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, int slot) {
-  if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 8u + slot] = global_timer_ns();
+  if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 16u + slot] = (unsigned long long)clock64();
 }
 
 // Shared-memory matrix descriptor, K-major, no swizzle.
@@ -263,7 +307,7 @@ __device__ __forceinline__ uint32_t make_idesc(int bn) {
 }
 
 struct alignas(16) PipeShared {
-  int32_t bias[kBiasSmem];  // copy of the bias vector (zeros when there is none)
+  int32_t bias[2][kBiasSmem];  // per accumulator set: bias (+ rounding constant) of the tile's columns
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
   unsigned long long tfull[2];
@@ -275,9 +319,11 @@ struct alignas(16) PipeShared {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-// Epilogue for 16 consecutive columns of one row: v = accumulator words.
+// Epilogue for 16 consecutive columns of one row: v = accumulator words, bias_s = this
+// group's 16 staged bias values in shared memory (bias + rounding constant for the
+// requantising epilogue).
 template <int EPI>
-__device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, const uint32_t *v, int col0,
+__device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, bool wide, const uint32_t *v,
                                               long long o) {
   if constexpr (EPI == EPI_RAW_ROWS) {
     uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
@@ -285,23 +331,11 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
     for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
   } else {
     int32_t bv[16];
-    if (bias_s != nullptr) {  // staged in shared memory: one broadcast read per 4 values
-      const int4 *bp = reinterpret_cast<const int4 *>(bias_s + col0);
+    const int4 *bp = reinterpret_cast<const int4 *>(bias_s);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int4 t = bp[q];
-        bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
-      }
-    } else if (p.bias != nullptr) {
-      const int4 *bp = reinterpret_cast<const int4 *>(p.bias + col0);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int4 t = __ldg(bp + q);
-        bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
-      }
-    } else {
-#pragma unroll
-      for (int q = 0; q < 16; ++q) bv[q] = 0;
+    for (int q = 0; q < 4; ++q) {
+      const int4 t = bp[q];  // same address in every lane: a broadcast read
+      bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
     }
     if constexpr (EPI == EPI_RAW_NCHWC) {
       uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
@@ -311,19 +345,18 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
                             v[4 * q + 2] + (uint32_t)bv[4 * q + 2], v[4 * q + 3] + (uint32_t)bv[4 * q + 3]);
     } else {
       uint32_t w[4];
-      if (p.shift <= 23) {
-        // 32-bit path.  Saturating adds keep the order of acc + bias + rounding; a sum that
-        // saturates is >= 2^31 - 1 or <= -2^31, and for shift <= 23 both ends still clamp to
-        // 255 and 0, so the result equals the 64-bit definition.
-        const int32_t rnd = 1 << (p.shift - 1);
+      if (!wide) {
+        // bv holds bias + 2^(shift-1); the host-side bound on |acc| and the staging check
+        // guarantee that acc + bv cannot leave the s32 range, so one add and one shift do it
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           int32_t t[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) t[e] = add_sat(add_sat((int32_t)v[4 * q + e], bv[4 * q + e]), rnd) >> p.shift;
+          for (int e = 0; e < 4; ++e) t[e] = ((int32_t)v[4 * q + e] + bv[4 * q + e]) >> p.shift;
           w[q] = pack_sat_u8(t[1], t[0], pack_sat_u8(t[3], t[2], 0u));
         }
       } else {
+        // bv holds the plain bias: 64-bit sum, for shifts and magnitudes the 32-bit path cannot take
         const long long rnd = 1ll << (p.shift - 1);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -376,9 +409,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
     tmem_alloc(smem_u32(&ps->tmem_base), 512);
     tmem_relinquish();
   }
-  const bool bias_staged = EPI != EPI_RAW_ROWS && p.n_total <= kBiasSmem;
-  if (bias_staged)
-    for (int i = threadIdx.x; i < p.n_total; i += kNumThreads) ps->bias[i] = p.bias != nullptr ? __ldg(p.bias + i) : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -431,7 +461,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 0);
       int ci = 0, kh = 0, kw = 0;  // position of the next K column (conv modes)
       for (int ks = 0; ks < p.k_stages; ++ks) {
-        if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
+        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
           alive = false;
           break;
         }
@@ -580,23 +610,55 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
       }
     }
   } else if (warp < kDrainWarps) {
-    // ===================== drain (warps 0-7) =====================
+    // ===================== drain (warps 0-15) =====================
     uint32_t lt = 0;
     bool alive = true;
     const int ohw = p.OH * p.OW;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
-    const int part = warp >> 2;  // MT = 2: sub-tile; MT = 1: which share of the column groups
+    const int part = warp >> 2;  // 0-3: which sub-tile / share of the column groups
     const int groups = p.bn >> 4;
-    const int sub = (MT == 2) ? part : 0;
-    const int g_begin = (MT == 2) ? 0 : (part ? (groups + 1) / 2 : 0);
-    const int g_end = (MT == 2) ? groups : (part ? groups : (groups + 1) / 2);
-    const int32_t *bias_s = bias_staged ? ps->bias : nullptr;
+    const int sub = (MT == 2) ? (part >> 1) : 0;
+    const int nparts = (MT == 2) ? 2 : 4;
+    const int cpart = (MT == 2) ? (part & 1) : part;
+    const int per = (groups + nparts - 1) / nparts;
+    const int g_begin = min(cpart * per, groups);
+    const int g_end = min(g_begin + per, groups);
+    const int dtid = threadIdx.x;  // 0..511 within the drain warps
+    const bool static_wide = EPI == EPI_REQ_NCHWC && (p.shift > 23 || p.acc_bound >= (1ll << 30));
     for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile % p.n_tiles;
       const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
       const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
-      if (!mbar_wait(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull)) {
+      // Stage this tile's bias values (plus the rounding constant on the 32-bit requantise
+      // path).  Barrier A: every drain warp has left the previous tile, so bias[slot] is free;
+      // it also ORs the per-column "needs 64 bits" tests so that all threads take the same
+      // path.  Barrier B (after the wait for the accumulator): publishes the staged values and
+      // ORs the outcome of the bounded wait, so that the drain warps give up together.
+      bool wide = false;
+      if constexpr (EPI != EPI_RAW_ROWS) {
+        int32_t b = 0;
+        long long br = 0;
+        int need_wide = 0;
+        if (dtid < p.bn) {
+          const int col = n_tile * p.bn + dtid;
+          b = (p.bias != nullptr && col < p.n_total) ? __ldg(p.bias + col) : 0;
+          if constexpr (EPI == EPI_REQ_NCHWC) {
+            br = (long long)b + (1ll << (p.shift - 1));
+            const long long mag = br < 0 ? -br : br;
+            need_wide = (mag + p.acc_bound >= (1ll << 31)) ? 1 : 0;
+          }
+        }
+        if constexpr (EPI == EPI_REQ_NCHWC) {
+          wide = drain_barrier_or(need_wide) || static_wide;
+          if (dtid < p.bn) ps->bias[slot][dtid] = wide ? b : (int32_t)br;
+        } else {
+          drain_barrier_or(0);
+          if (dtid < p.bn) ps->bias[slot][dtid] = b;
+        }
+      }
+      const bool got = mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull);
+      if (drain_barrier_or(got ? 0 : 1)) {
         alive = false;
         break;
       }
@@ -604,7 +666,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
       if (threadIdx.x == 0) trace_mark(p, lt, 6);
       const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + quad * 32 + lane;
       const bool mvalid = m < p.m_total;
-      long long obase = 0;  // element offset of this row's first stored value
+      long long obase = 0;     // element offset of this row's first stored value
       long long gstride = 16;  // element distance between consecutive 16-column groups
       if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
@@ -618,21 +680,22 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
       }
       const uint32_t t_row =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
-      int g = g_begin;
-      for (; g + 2 <= g_end; g += 2) {
-        uint32_t v[32];
-        tmem_ld32(t_row + (uint32_t)g * 16u, v);
-        tmem_ld_wait();
-        const int col0 = n_tile * p.bn + g * 16;
-        if (mvalid && col0 < p.n_total) store_group16<EPI>(p, bias_s, v, col0, obase + g * gstride);
-        if (mvalid && col0 + 16 < p.n_total) store_group16<EPI>(p, bias_s, v + 16, col0 + 16, obase + (g + 1) * gstride);
+      // software pipeline: the read of group g + 1 is in flight while group g is processed
+      uint32_t va[16], vb[16];
+      if (g_begin < g_end) {
+        tmem_ld16(t_row + (uint32_t)g_begin * 16u, va);
+        tmem_ld_wait16(va);
       }
-      if (g < g_end) {
-        uint32_t v[16];
-        tmem_ld16(t_row + (uint32_t)g * 16u, v);
-        tmem_ld_wait();
-        const int col0 = n_tile * p.bn + g * 16;
-        if (mvalid && col0 < p.n_total) store_group16<EPI>(p, bias_s, v, col0, obase + g * gstride);
+      for (int g = g_begin; g < g_end; g += 2) {
+        const bool has_b = g + 1 < g_end;
+        if (has_b) tmem_ld16(t_row + (uint32_t)(g + 1) * 16u, vb);
+        if (mvalid && n_tile * p.bn + g * 16 < p.n_total)
+          store_group16<EPI>(p, &ps->bias[slot][g * 16], wide, va, obase + g * gstride);
+        tmem_ld_wait16(vb);
+        if (g + 2 < g_end) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
+        if (has_b && mvalid && n_tile * p.bn + (g + 1) * 16 < p.n_total)
+          store_group16<EPI>(p, &ps->bias[slot][(g + 1) * 16], wide, vb, obase + (g + 1) * gstride);
+        tmem_ld_wait16(va);
       }
       tc_fence_before();
       __syncwarp();

@@ -356,6 +356,7 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
   IgemmParams p{};
   p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
   fill_conv(p, d, 1);
+  p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
   if (d->c_block == 16)
     return requant ? launch_igemm<A_CONV_I8, EPI_REQ_NCHWC, false>(p, c, st)
                    : launch_igemm<A_CONV_I8, EPI_RAW_NCHWC, false>(p, c, st);
