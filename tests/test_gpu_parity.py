@@ -143,6 +143,20 @@ def test_requant_rounding_and_bias_only_s32(U, oracle):
     U.device_status()
 
 
+def test_wide_layer_bias_beyond_staged_vector(U, oracle):
+    """More output channels than the kernel keeps in shared memory (2048), with ordinary and extreme biases."""
+    rng = np.random.default_rng(21)
+    x = rng.integers(0, 256, (1, 2, 5, 5, 16), dtype=np.uint8)
+    w = rng.integers(-128, 128, (136, 2, 1, 1, 4, 16, 4), dtype=np.int8)   # 2176 output channels
+    for hi in (2 ** 15, 2 ** 31 - 1):
+        b = rng.integers(-hi, hi, 2176, dtype=np.int64).astype(np.int32)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), bias=dev(b), out_dtype='uint8')
+        gots = U.conv2d_NCHWc_int8(dev(x), dev(w), bias=dev(b))
+        U.device_status()
+        assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, w, bias=b, requant_shift=8))
+        assert np.array_equal(gots.cpu().numpy(), oracle.conv2d_u8s8(x, w, bias=b))
+
+
 def test_stem_nchw4c(U, oracle):
     rng = np.random.default_rng(4)
     for (n, hw) in ((2, 32), (1, 224)):

@@ -42,6 +42,7 @@
 // CTA-wide abort flag and a global error word; all roles then leave their
 // loops, let their own copies land, and the CTA frees its TMEM and returns.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -51,7 +52,8 @@ enum AMode : int {
   A_CONV_I8 = 0,   // u8 NCHW16c: one 16-byte column = one channel chunk of one tap
   A_CONV_F16 = 1,  // fp16 NCHW16c: one chunk = two 16-byte columns
   A_STEM_I8 = 2,   // u8 NCHW4c: one column = 4 consecutive kw taps x 4 channels
-  A_DENSE = 3      // plain row-major matrix, K contiguous
+  A_DENSE = 3,     // plain row-major matrix, K contiguous
+  A_CONV_TMA = 4   // NCHW16c (u8 or fp16) fetched by im2col-mode TMA: one bulk tensor copy per K column
 };
 enum EpiMode : int {
   EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
@@ -65,6 +67,14 @@ constexpr int kNumThreads = 704;
 constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21;
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
 constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
+
+// n / d for 0 <= n < 2^31 with a host-computed multiplier (mul == 0: d is a power of two).
+struct FastDiv {
+  uint32_t mul, shr;
+};
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, FastDiv f) {
+  return f.mul != 0u ? (__umulhi(n, f.mul) >> f.shr) : (n >> f.shr);
+}
 
 struct IgemmParams {
   const uint8_t *a;   // activations / A matrix
@@ -88,6 +98,8 @@ struct IgemmParams {
   long long lda;      // A_DENSE: row pitch in bytes
   long long ldc;      // EPI_RAW_ROWS: row pitch in elements
   int shift;          // EPI_REQ_NCHWC
+  FastDiv div_ohw, div_ow;  // divisions by OH*OW and OW (A_CONV_TMA)
+  int cols_per_chunk;       // A_CONV_TMA: 16-byte columns per channel chunk (1 for u8, 2 for fp16)
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
@@ -189,6 +201,16 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
       "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// im2col-mode tensor copy: `pixelsPerColumn` consecutive output positions, starting at the
+// filter-window origin (w, h, d) of the first one, tap offset (woff, hoff), channel c of chunk n.
+__device__ __forceinline__ void tma_im2col_5d(uint32_t dst, const CUtensorMap *tmap, int c, int w, int h, int d, int n,
+                                              uint16_t woff, uint16_t hoff, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
+      "%5, %6}], [%7], {%8, %9, %10};" ::"r"(dst),
+      "l"(tmap), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "r"(bar), "h"(woff), "h"(hoff), "h"((uint16_t)0)
       : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -377,7 +399,8 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
 }
 
 template <int AMODE, int EPI, bool F16, int MT>
-__global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams p) {
+__global__ void __launch_bounds__(kNumThreads, 1)
+    igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -395,7 +418,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&ps->full[s]), 128 + 1);  // 128 A-producer threads + the B producer
+      // 128 A-producer threads + the B producer; with TMA-fed A only the thread that issues all copies
+      mbar_init(smem_u32(&ps->full[s]), AMODE == A_CONV_TMA ? 1 : 128 + 1);
       mbar_init(smem_u32(&ps->empty[s]), 1);       // one tcgen05.commit
     }
     for (int i = 0; i < 2; ++i) {
@@ -416,7 +440,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
+  if (AMODE != A_CONV_TMA && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A producers =====================
     const int pw = warp - kFirstProducerWarp;
     uint32_t s = 0, ring_phase = 0;  // ring position and the number of wraps (mod 2)
@@ -543,7 +567,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
     }
     cp_async_wait<0>();  // nothing of this thread is in flight when the CTA winds down
   } else if (warp == kBWarp) {
-    // ===================== B producer =====================
+    // ===================== B producer (and, with A_CONV_TMA, the A copies) =====================
     if (lane == 0) {
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;
@@ -551,13 +575,48 @@ __global__ void __launch_bounds__(kNumThreads, 1) igemm_kernel(const IgemmParams
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
         const int n_tile = tile % p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
+        // A_CONV_TMA: filter-window origin of the first output position of each sub-tile
+        int w0[MT], h0[MT], d0[MT];
+        if constexpr (AMODE == A_CONV_TMA) {
+          const int m_tile = tile / p.n_tiles;
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            long long m = ((long long)m_tile * MT + t) * kTileM;
+            if (m >= p.m_total) m = 0;  // a sub-tile past the end: fetch valid data, nothing of it is stored
+            const uint32_t n_img = fast_div((uint32_t)m, p.div_ohw);
+            const uint32_t rem = (uint32_t)m - n_img * (uint32_t)(p.OH * p.OW);
+            const uint32_t oh = fast_div(rem, p.div_ow);
+            const uint32_t ow = rem - oh * (uint32_t)p.OW;
+            w0[t] = (int)ow * p.sw - p.pw;
+            h0[t] = (int)oh * p.sh - p.ph;
+            d0[t] = (int)n_img;
+          }
+        }
+        int ci = 0, kh = 0, kw = 0, sub = 0;  // position of the next K column (A_CONV_TMA)
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
             alive = false;
             break;
           }
           const uint32_t bar = smem_u32(&ps->full[s]);
-          mbar_arrive_expect_tx(bar, b_stage_bytes);
+          if constexpr (AMODE == A_CONV_TMA) {
+            int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
+            real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
+            mbar_arrive_expect_tx(bar, b_stage_bytes + (uint32_t)(real * MT) * kSubBytes);
+            const uint32_t a_dst = smem_base + s * stage_bytes;
+            for (int jj = 0; jj < real; ++jj) {
+#pragma unroll
+              for (int t = 0; t < MT; ++t)
+                tma_im2col_5d(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes, &tmap, sub * 8, w0[t], h0[t],
+                              d0[t], ci, (uint16_t)kw, (uint16_t)kh, bar);
+              if (++sub == p.cols_per_chunk) {
+                sub = 0;
+                if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
+              }
+            }
+          } else {
+            mbar_arrive_expect_tx(bar, b_stage_bytes);
+          }
           bulk_copy_g2s(smem_base + s * stage_bytes + a_stage_bytes, src + (size_t)ks * b_stage_bytes,
                         b_stage_bytes, bar);
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }

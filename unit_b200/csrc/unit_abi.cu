@@ -2,6 +2,7 @@
 // layout kernels, and the launches of the implicit-GEMM kernel.
 #include "../../include/unit_b200.h"
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -295,7 +296,7 @@ static unsigned grid_for(long long total) {
 // launches of the contraction kernel
 // ---------------------------------------------------------------------------
 template <int AMODE, int EPI, bool F16, int MT>
-static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, int sms) {
+static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, int sms, const CUtensorMap &tmap) {
   static std::once_flag once[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -310,13 +311,15 @@ static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, in
   p.m_tiles = (int)((p.m_total + kTileM * MT - 1) / (kTileM * MT));
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kNumThreads, smem_bytes, st>>>(p);
+  kern<<<grid, kNumThreads, smem_bytes, st>>>(p, tmap);
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
 }
 
 template <int AMODE, int EPI, bool F16>
-static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st) {
+static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const CUtensorMap *tmap_in = nullptr) {
+  static const CUtensorMap no_map{};
+  const CUtensorMap &tmap = tmap_in ? *tmap_in : no_map;
   p.bn = c.bn;
   p.kc = c.kc;
   p.cols = c.cols;
@@ -329,8 +332,68 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st) {
   p.trace = g_trace.load();
   p.trace_cap = g_trace_cap.load();
   const int sms = sm_count();
-  if (choose_mt(c, p.m_total, sms) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms);
-  return launch_igemm_mt<AMODE, EPI, F16, 1>(p, c, st, sms);
+  if (choose_mt(c, p.m_total, sms) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms, tmap);
+  return launch_igemm_mt<AMODE, EPI, F16, 1>(p, c, st, sms, tmap);
+}
+
+// Multiplier for n / d, valid for 0 <= n < 2^31: q = umulhi(n, mul) >> shr (mul == 0: shift only).
+static FastDiv make_fast_div(uint32_t d) {
+  FastDiv f{0u, 0u};
+  if (d == 0) d = 1;
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l;  // ceil(log2 d)
+  if ((d & (d - 1)) == 0) {
+    f.shr = l;
+  } else {
+    f.mul = (uint32_t)((1ull << (31 + l)) / d + 1);
+    f.shr = l - 1;
+  }
+  return f;
+}
+
+// im2col-mode tensor map over NCHW16c activations, seen as the 5-D tensor
+//   (c = 16 channels of a chunk, w, h, d = image, n = channel chunk)
+// so that one copy walks kTileM consecutive output positions (w, then h, then image) of one
+// chunk.  Returns false when the driver entry point is missing or rejects the geometry; the
+// caller then uses the cp.async gather.
+static bool make_im2col_map(CUtensorMap *map, const unit_conv_desc *d, const void *x, bool f16) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  // small tensors stay on the cp.async path (the driver needs a descriptor fix-up for them)
+  if ((long long)d->n * d->c_in * d->h * d->w * (f16 ? 2 : 1) < 131072) return false;
+  if (d->c_block != 16 || d->pad_w > 15 || d->pad_h > 15 || d->kw > 16 || d->kh > 16 || d->stride_w > 8 || d->stride_h > 8)
+    return false;
+  const cuuint64_t eb = f16 ? 2 : 1;
+  const cuuint64_t cc = (cuuint64_t)d->c_in / 16;
+  const cuuint64_t dims[5] = {16, (cuuint64_t)d->w, (cuuint64_t)d->h, (cuuint64_t)d->n, cc};
+  const cuuint64_t plane = (cuuint64_t)d->h * d->w * 16 * eb;
+  const cuuint64_t strides[4] = {16 * eb, (cuuint64_t)d->w * 16 * eb, cc * plane, plane};
+  const int lower[3] = {-d->pad_w, -d->pad_h, 0};
+  const int upper[3] = {d->pad_w - (d->kw - 1), d->pad_h - (d->kh - 1), 0};
+  const cuuint32_t estr[5] = {1, (cuuint32_t)d->stride_w, (cuuint32_t)d->stride_h, 1, 1};
+  const CUresult r = encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 5,
+                            const_cast<void *>(x), dims, strides, lower, upper, f16 ? 8 : 16, kTileM, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool use_tma() {
+  static const int v = [] {
+    const char *e = getenv("UNIT_B200_TMA");
+    return e ? atoi(e) : 0;
+  }();
+  return v != 0;
 }
 
 static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
@@ -342,6 +405,9 @@ static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
   p.img_bytes = (long long)d->c_in * d->h * d->w * elem_bytes;
   p.m_total = (long long)d->n * p.OH * p.OW;
   p.n_total = d->c_out;
+  p.div_ohw = make_fast_div((uint32_t)(p.OH * p.OW));
+  p.div_ow = make_fast_div((uint32_t)p.OW);
+  p.cols_per_chunk = elem_bytes;
 }
 
 static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias, int shift,
@@ -357,9 +423,14 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
   p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
   fill_conv(p, d, 1);
   p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
-  if (d->c_block == 16)
+  if (d->c_block == 16) {
+    CUtensorMap map;
+    if (use_tma() && make_im2col_map(&map, d, x, false))
+      return requant ? launch_igemm<A_CONV_TMA, EPI_REQ_NCHWC, false>(p, c, st, &map)
+                     : launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, false>(p, c, st, &map);
     return requant ? launch_igemm<A_CONV_I8, EPI_REQ_NCHWC, false>(p, c, st)
                    : launch_igemm<A_CONV_I8, EPI_RAW_NCHWC, false>(p, c, st);
+  }
   return requant ? launch_igemm<A_STEM_I8, EPI_REQ_NCHWC, false>(p, c, st)
                  : launch_igemm<A_STEM_I8, EPI_RAW_NCHWC, false>(p, c, st);
 }
