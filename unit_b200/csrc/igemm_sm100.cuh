@@ -53,7 +53,9 @@ enum AMode : int {
   A_CONV_F16 = 1,  // fp16 NCHW16c: one chunk = two 16-byte columns
   A_STEM_I8 = 2,   // u8 NCHW4c: one column = 4 consecutive kw taps x 4 channels
   A_DENSE = 3,     // plain row-major matrix, K contiguous
-  A_CONV_TMA = 4   // NCHW16c (u8 or fp16) fetched by im2col-mode TMA: one bulk tensor copy per K column
+  A_CONV_TMA = 4,  // NCHW16c (u8 or fp16) fetched by im2col-mode TMA: one bulk tensor copy per K column
+  A_CONV_BOX = 5   // u8 NCHW16c, stride 1: each sub-tile is a box of (images x output rows x
+                   // row segment) fetched by tiled-mode TMA, whole pixel rows at a time
 };
 enum EpiMode : int {
   EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
@@ -100,6 +102,11 @@ struct IgemmParams {
   int shift;          // EPI_REQ_NCHWC
   FastDiv div_ohw, div_ow;  // divisions by OH*OW and OW (A_CONV_TMA)
   int cols_per_chunk;       // A_CONV_TMA: 16-byte columns per channel chunk (1 for u8, 2 for fp16)
+  // A_CONV_BOX: a 128-row sub-tile holds box_n images x box_h output rows x box_w output columns,
+  // rows ordered (image, row, column); sub-tile index = (n block, h block, w block), w fastest
+  int box_n, box_h, box_w, blocks_h, blocks_w, n_img;
+  long long sub_tiles;      // number of sub-tiles
+  FastDiv div_box_hw, div_box_w, div_blocks_w, div_blocks_h;
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
@@ -213,6 +220,16 @@ __device__ __forceinline__ void tma_im2col_5d(uint32_t dst, const CUtensorMap *t
       "l"(tmap), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "r"(bar), "h"(woff), "h"(hoff), "h"((uint16_t)0)
       : "memory");
 }
+// tiled-mode tensor copy of one box of the 4-D tensor (x, y, z, w) = (16-byte units of a pixel row,
+// image row, channel chunk, image)
+__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap *tmap, int x, int y, int z, int w,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
+      "%5}], [%6];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -270,6 +287,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr)
       : "memory");
+}
+// d = (sat_u16(a) << 16) | sat_u16(b)
+__device__ __forceinline__ uint32_t pack_sat_u16(int32_t a, int32_t b) {
+  uint32_t d;
+  asm("cvt.pack.sat.u16.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 __device__ __forceinline__ int32_t add_sat(int32_t a, int32_t b) {
   int32_t d;
@@ -369,13 +392,21 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
       uint32_t w[4];
       if (!wide) {
         // bv holds bias + 2^(shift-1); the host-side bound on |acc| and the staging check
-        // guarantee that acc + bv cannot leave the s32 range, so one add and one shift do it
+        // guarantee that acc + bv cannot leave the s32 range
+        int32_t t[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          int32_t t[4];
+        for (int q = 0; q < 16; ++q) t[q] = (int32_t)v[q] + bv[q];
+        if (p.shift == 8) {
+          // clamp to [0, 65535] while packing pairs, then keep the high byte of each half-word:
+          // min(max(x, 0), 65535) >> 8 == min(max(x >> 8, 0), 255)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) t[e] = ((int32_t)v[4 * q + e] + bv[4 * q + e]) >> p.shift;
-          w[q] = pack_sat_u8(t[1], t[0], pack_sat_u8(t[3], t[2], 0u));
+          for (int q = 0; q < 4; ++q)
+            w[q] = __byte_perm(pack_sat_u16(t[4 * q + 1], t[4 * q]), pack_sat_u16(t[4 * q + 3], t[4 * q + 2]), 0x7531);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            w[q] = pack_sat_u8(t[4 * q + 1] >> p.shift, t[4 * q] >> p.shift,
+                               pack_sat_u8(t[4 * q + 3] >> p.shift, t[4 * q + 2] >> p.shift, 0u));
         }
       } else {
         // bv holds the plain bias: 64-bit sum, for shifts and magnitudes the 32-bit path cannot take
@@ -419,7 +450,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       // 128 A-producer threads + the B producer; with TMA-fed A only the thread that issues all copies
-      mbar_init(smem_u32(&ps->full[s]), AMODE == A_CONV_TMA ? 1 : 128 + 1);
+      mbar_init(smem_u32(&ps->full[s]), (AMODE == A_CONV_TMA || AMODE == A_CONV_BOX) ? 2 : 128 + 1);
       mbar_init(smem_u32(&ps->empty[s]), 1);       // one tcgen05.commit
     }
     for (int i = 0; i < 2; ++i) {
@@ -440,7 +471,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (AMODE != A_CONV_TMA && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
+  if (AMODE != A_CONV_TMA && AMODE != A_CONV_BOX && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A producers =====================
     const int pw = warp - kFirstProducerWarp;
     uint32_t s = 0, ring_phase = 0;  // ring position and the number of wraps (mod 2)
@@ -566,8 +597,89 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 1);
     }
     cp_async_wait<0>();  // nothing of this thread is in flight when the CTA winds down
+  } else if ((AMODE == A_CONV_TMA || AMODE == A_CONV_BOX) && warp >= kFirstProducerWarp &&
+             warp < kFirstProducerWarp + 4) {
+    // ===================== A copies by TMA =====================
+    // One tensor copy brings one K column of one sub-tile (2 KB at most).  Measured: a thread
+    // needs ~330 cycles per copy and a warp ~70, so the copies of a stage (column x sub-tile)
+    // are dealt round-robin to the four producer warps and, within a warp, to its lanes; each
+    // warp then issues its share with one instruction.
+    const int copy_id = lane * 4 + (warp - kFirstProducerWarp);
+    const int jj = copy_id / MT, t = copy_id % MT;
+    const bool lane_active = jj < p.kc;
+    const bool tx_poster = warp == kFirstProducerWarp && lane == 0;  // announces the stage's A bytes
+    uint32_t s = 0, ring_phase = 0;
+    uint32_t lt = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+      const int m_tile = tile / p.n_tiles;
+      // origin of this lane's sub-tile
+      int c0 = 0, c1 = 0, c2 = 0;  // BOX: x (8-byte units), y, first image; TMA: w, h, image
+      bool sub_ok = true;
+      if constexpr (AMODE == A_CONV_BOX) {
+        long long st = (long long)m_tile * MT + t;
+        sub_ok = st < p.sub_tiles;
+        if (!sub_ok) st = 0;
+        const uint32_t q = fast_div((uint32_t)st, p.div_blocks_w);
+        const uint32_t wb = (uint32_t)st - q * (uint32_t)p.blocks_w;
+        const uint32_t nb = fast_div(q, p.div_blocks_h);
+        const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
+        c0 = ((int)wb * p.box_w - p.pw) * 2;
+        c1 = (int)hb * p.box_h - p.ph;
+        c2 = (int)nb * p.box_n;
+      } else {
+        long long m = ((long long)m_tile * MT + t) * kTileM;
+        if (m >= p.m_total) m = 0;  // a sub-tile past the end: fetch valid data, nothing of it is stored
+        const uint32_t n_img = fast_div((uint32_t)m, p.div_ohw);
+        const uint32_t rem = (uint32_t)m - n_img * (uint32_t)(p.OH * p.OW);
+        const uint32_t oh = fast_div(rem, p.div_ow);
+        const uint32_t ow = rem - oh * (uint32_t)p.OW;
+        c0 = (int)ow * p.sw - p.pw;
+        c1 = (int)oh * p.sh - p.ph;
+        c2 = (int)n_img;
+      }
+      // sub-tiles that exist in this tile, and the bytes one copy delivers
+      int nsub = MT;
+      uint32_t copy_bytes = kSubBytes;
+      if constexpr (AMODE == A_CONV_BOX) {
+        const long long left = p.sub_tiles - (long long)m_tile * MT;
+        nsub = left < MT ? (int)left : MT;
+        copy_bytes = (uint32_t)(p.box_n * p.box_h * p.box_w) * 16u;
+      }
+      // this lane's K column: chunk position (ci, kw, kh) and, for fp16, which 16-byte half
+      const int cpc = (AMODE == A_CONV_BOX) ? 1 : p.cols_per_chunk;
+      const int half = jj % cpc;
+      int q0 = jj / cpc;  // chunk index along K
+      int kh = q0 / (p.Cc * p.KW);
+      int kw = (q0 / p.Cc) % p.KW;
+      int ci = q0 % p.Cc;
+      const int chunk_step = p.kc / cpc;
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
+          alive = false;
+          break;
+        }
+        const uint32_t bar = smem_u32(&ps->full[s]);
+        int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
+        real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
+        if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(real * nsub) * copy_bytes);
+        __syncwarp();
+        if (lane_active && jj < real && (AMODE != A_CONV_BOX || sub_ok)) {
+          const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes;
+          if constexpr (AMODE == A_CONV_BOX)
+            tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2, bar);
+          else
+            tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, bar);
+        }
+        // advance this lane's column by one stage
+        ci += chunk_step;
+        while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; ++kh; } }
+        if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
+      }
+      if (tx_poster) trace_mark(p, lt, 1);
+    }
   } else if (warp == kBWarp) {
-    // ===================== B producer (and, with A_CONV_TMA, the A copies) =====================
+    // ===================== B producer =====================
     if (lane == 0) {
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;
@@ -575,48 +687,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
         const int n_tile = tile % p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
-        // A_CONV_TMA: filter-window origin of the first output position of each sub-tile
-        int w0[MT], h0[MT], d0[MT];
-        if constexpr (AMODE == A_CONV_TMA) {
-          const int m_tile = tile / p.n_tiles;
-#pragma unroll
-          for (int t = 0; t < MT; ++t) {
-            long long m = ((long long)m_tile * MT + t) * kTileM;
-            if (m >= p.m_total) m = 0;  // a sub-tile past the end: fetch valid data, nothing of it is stored
-            const uint32_t n_img = fast_div((uint32_t)m, p.div_ohw);
-            const uint32_t rem = (uint32_t)m - n_img * (uint32_t)(p.OH * p.OW);
-            const uint32_t oh = fast_div(rem, p.div_ow);
-            const uint32_t ow = rem - oh * (uint32_t)p.OW;
-            w0[t] = (int)ow * p.sw - p.pw;
-            h0[t] = (int)oh * p.sh - p.ph;
-            d0[t] = (int)n_img;
-          }
-        }
-        int ci = 0, kh = 0, kw = 0, sub = 0;  // position of the next K column (A_CONV_TMA)
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
             alive = false;
             break;
           }
           const uint32_t bar = smem_u32(&ps->full[s]);
-          if constexpr (AMODE == A_CONV_TMA) {
-            int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
-            real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
-            mbar_arrive_expect_tx(bar, b_stage_bytes + (uint32_t)(real * MT) * kSubBytes);
-            const uint32_t a_dst = smem_base + s * stage_bytes;
-            for (int jj = 0; jj < real; ++jj) {
-#pragma unroll
-              for (int t = 0; t < MT; ++t)
-                tma_im2col_5d(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes, &tmap, sub * 8, w0[t], h0[t],
-                              d0[t], ci, (uint16_t)kw, (uint16_t)kh, bar);
-              if (++sub == p.cols_per_chunk) {
-                sub = 0;
-                if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
-              }
-            }
-          } else {
-            mbar_arrive_expect_tx(bar, b_stage_bytes);
-          }
+          mbar_arrive_expect_tx(bar, b_stage_bytes);
           bulk_copy_g2s(smem_base + s * stage_bytes + a_stage_bytes, src + (size_t)ks * b_stage_bytes,
                         b_stage_bytes, bar);
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
@@ -628,6 +705,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     // ===================== MMA issuer =====================
     if (lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn);
+      const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
+      const uint64_t b_desc0 = make_smem_desc(0u, (uint32_t)p.bn * 16u, 128u);
+      const uint32_t a_step = (2u * kSubBytes) >> 4;               // one MMA K-step = two 16-byte columns
+      const uint32_t b_step = (2u * (uint32_t)p.bn * 16u) >> 4;
+      const uint32_t a_sub_enc = a_sub_bytes >> 4;
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;  // tiles done by this CTA
       bool alive = true;
@@ -648,16 +730,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           }
           tc_fence_after();
           if (ks == 0) trace_mark(p, lt, 4);
-          const uint32_t a_addr = smem_base + s * stage_bytes;
-          const uint32_t b_addr = a_addr + a_stage_bytes;
+          // descriptors differ only in the start-address field (address >> 4, 14 bits)
+          const uint32_t a_enc = (smem_base + s * stage_bytes) >> 4;
+          const uint32_t b_enc = a_enc + (a_stage_bytes >> 4);
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
           for (int k = 0; k < nk; ++k) {
-            const uint64_t bdesc =
-                make_smem_desc(b_addr + (uint32_t)k * 2u * ((uint32_t)p.bn * 16u), (uint32_t)p.bn * 16u, 128u);
+            const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
-              const uint64_t adesc =
-                  make_smem_desc(a_addr + (uint32_t)t * a_sub_bytes + (uint32_t)k * 2u * kSubBytes, kSubBytes, 128u);
+              const uint64_t adesc = a_desc0 | (uint64_t)(a_enc + (uint32_t)t * a_sub_enc + (uint32_t)k * a_step);
               tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, (ks | k) != 0 ? 1u : 0u);
             }
           }
@@ -695,6 +776,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // path.  Barrier B (after the wait for the accumulator): publishes the staged values and
       // ORs the outcome of the bounded wait, so that the drain warps give up together.
       bool wide = false;
+      const int32_t *tile_bias = &ps->bias[slot][0];
       if constexpr (EPI != EPI_RAW_ROWS) {
         int32_t b = 0;
         long long br = 0;
@@ -724,10 +806,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       tc_fence_after();
       if (threadIdx.x == 0) trace_mark(p, lt, 6);
       const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + quad * 32 + lane;
-      const bool mvalid = m < p.m_total;
+      bool mvalid = m < p.m_total;
       long long obase = 0;     // element offset of this row's first stored value
       long long gstride = 16;  // element distance between consecutive 16-column groups
-      if constexpr (EPI == EPI_RAW_ROWS) {
+      if constexpr (AMODE == A_CONV_BOX) {
+        // sub-tile -> (image block, row block, column block); row -> (image, row, column) inside the box
+        const long long st = (long long)m_tile * MT + sub;
+        const uint32_t r = (uint32_t)(quad * 32 + lane);
+        const uint32_t stc = st < p.sub_tiles ? (uint32_t)st : 0u;
+        const uint32_t q = fast_div(stc, p.div_blocks_w);
+        const uint32_t wb = stc - q * (uint32_t)p.blocks_w;
+        const uint32_t nb = fast_div(q, p.div_blocks_h);
+        const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
+        const uint32_t dn = fast_div(r, p.div_box_hw);
+        const uint32_t rr = r - dn * (uint32_t)(p.box_h * p.box_w);
+        const uint32_t dh = fast_div(rr, p.div_box_w);
+        const uint32_t dw = rr - dh * (uint32_t)p.box_w;
+        const int n_i = (int)nb * p.box_n + (int)dn, oh = (int)hb * p.box_h + (int)dh, ow = (int)wb * p.box_w + (int)dw;
+        mvalid = st < p.sub_tiles && (int)dn < p.box_n && n_i < p.n_img && oh < p.OH && ow < p.OW;
+        obase = (((long long)n_i * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + (long long)oh * p.OW + ow) * 16;
+        gstride = (long long)ohw * 16;
+      } else if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
       } else {
         const unsigned mm = mvalid ? (unsigned)m : 0u;
@@ -749,11 +848,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const bool has_b = g + 1 < g_end;
         if (has_b) tmem_ld16(t_row + (uint32_t)(g + 1) * 16u, vb);
         if (mvalid && n_tile * p.bn + g * 16 < p.n_total)
-          store_group16<EPI>(p, &ps->bias[slot][g * 16], wide, va, obase + g * gstride);
+          store_group16<EPI>(p, tile_bias + g * 16, wide, va, obase + g * gstride);
         tmem_ld_wait16(vb);
         if (g + 2 < g_end) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
         if (has_b && mvalid && n_tile * p.bn + (g + 1) * 16 < p.n_total)
-          store_group16<EPI>(p, &ps->bias[slot][(g + 1) * 16], wide, vb, obase + (g + 1) * gstride);
+          store_group16<EPI>(p, tile_bias + (g + 1) * 16, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait16(va);
       }
       tc_fence_before();

@@ -388,10 +388,68 @@ static bool make_im2col_map(CUtensorMap *map, const unit_conv_desc *d, const voi
   return r == CUDA_SUCCESS;
 }
 
+// Box geometry for A_CONV_BOX: a 128-row sub-tile covers box_n images x box_h output rows x box_w
+// output columns.  Picks the split with the fewest sub-tiles (least idle MMA rows), preferring
+// taller boxes (longer contiguous runs per image).
+struct BoxGeom {
+  int bw, bh, bn, blocks_w, blocks_h, blocks_n;
+  long long sub_tiles;
+};
+static BoxGeom choose_box(int n, int oh, int ow) {
+  BoxGeom g{};
+  g.bw = ow < kTileM ? ow : kTileM;
+  g.blocks_w = (ow + g.bw - 1) / g.bw;
+  long long best = -1;
+  for (int bh = 1; bh <= oh && bh * g.bw <= kTileM; ++bh) {
+    int bn = kTileM / (g.bw * bh);
+    if (bn > n) bn = n;
+    if (bn < 1) bn = 1;
+    const long long tiles = (long long)((n + bn - 1) / bn) * ((oh + bh - 1) / bh) * g.blocks_w;
+    if (best < 0 || tiles <= best) {
+      best = tiles;
+      g.bh = bh;
+      g.bn = bn;
+    }
+  }
+  g.blocks_h = (oh + g.bh - 1) / g.bh;
+  g.blocks_n = (n + g.bn - 1) / g.bn;
+  g.sub_tiles = (long long)g.blocks_n * g.blocks_h * g.blocks_w;
+  return g;
+}
+
+// Tiled-mode tensor map over u8 NCHW16c activations seen as (8-byte units of a pixel row, image
+// row, channel chunk, image): one copy fetches box_n x box_h row segments of box_w pixels, and
+// out-of-range coordinates (the zero padding) are filled with zeros by the copy engine.
+static bool make_box_map(CUtensorMap *map, const unit_conv_desc *d, const void *x, const BoxGeom &g) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  const cuuint64_t cc = (cuuint64_t)d->c_in / 16;
+  const cuuint64_t dims[4] = {(cuuint64_t)d->w * 2, (cuuint64_t)d->h, cc, (cuuint64_t)d->n};
+  const cuuint64_t row = (cuuint64_t)d->w * 16;
+  const cuuint64_t strides[3] = {row, row * d->h, row * d->h * cc};
+  const cuuint32_t box[4] = {(cuuint32_t)g.bw * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// The im2col TMA path is the default; UNIT_B200_TMA=0 selects the cp.async gather (for comparison runs).
 static bool use_tma() {
   static const int v = [] {
     const char *e = getenv("UNIT_B200_TMA");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : 1;
   }();
   return v != 0;
 }
@@ -425,6 +483,22 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
   p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
   if (d->c_block == 16) {
     CUtensorMap map;
+    if (use_tma() && d->stride_h == 1 && d->stride_w == 1) {
+      // stride 1: whole pixel rows per copy
+      const BoxGeom g = choose_box(d->n, p.OH, p.OW);
+      if (make_box_map(&map, d, x, g)) {
+        p.box_n = g.bn; p.box_h = g.bh; p.box_w = g.bw; p.blocks_h = g.blocks_h; p.blocks_w = g.blocks_w;
+        p.n_img = d->n;
+        p.sub_tiles = g.sub_tiles;
+        p.div_box_hw = make_fast_div((uint32_t)(g.bh * g.bw));
+        p.div_box_w = make_fast_div((uint32_t)g.bw);
+        p.div_blocks_w = make_fast_div((uint32_t)g.blocks_w);
+        p.div_blocks_h = make_fast_div((uint32_t)g.blocks_h);
+        p.m_total = g.sub_tiles * kTileM;  // rows of the padded tiling; the kernel masks the idle ones
+        return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(p, c, st, &map)
+                       : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(p, c, st, &map);
+      }
+    }
     if (use_tma() && make_im2col_map(&map, d, x, false))
       return requant ? launch_igemm<A_CONV_TMA, EPI_REQ_NCHWC, false>(p, c, st, &map)
                      : launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, false>(p, c, st, &map);
@@ -601,6 +675,9 @@ int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const voi
   IgemmParams p{};
   p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out;
   fill_conv(p, d, 2);
+  CUtensorMap map;
+  if (use_tma() && make_im2col_map(&map, d, x, true))
+    return launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_CONV_F16, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream));
 }
 
