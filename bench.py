@@ -220,7 +220,7 @@ def run_unit(args):
         w = torch.randn((l.c_out // 16, cs // cb, l.k, l.k, cb // 4, 16, 4), device=dev, generator=gen)
         w = (w * 32.0).round_().clamp_(-128, 127).to(torch.int8)
         bias = torch.randint(-2 ** 15, 2 ** 15, (l.c_out,), dtype=torch.int32, device=dev, generator=gen)
-        packed = U.pack_conv_weights_int8(w)
+        packed = U.pack_conv_weights_int8(w, l.stride, l.pad)
         idxs = []
         for c in range(l.count):
             gen.manual_seed(R.layer_seed(5, li, 0) + 101 * c + 7919 * rank)

@@ -84,7 +84,8 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 
 /* Replaces: the reference hands its packed weight array straight to the
  * generated kernel (apps/cpu/kernel/conv2d.py:26,30).  Source layout
- * [c_out/16][c_in/c_block][kh][kw][c_block/4][16][4] s8. */
+ * [c_out/16][c_in/c_block][kh][kw][c_block/4][16][4] s8.  The packed form depends on
+ * c_in, c_block, c_out, kh, kw and, for c_block == 4, on the strides and padding too. */
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *desc);
 int unit_pack_weights_conv_i8(const unit_conv_desc *desc, const int8_t *d_w,
                               void *d_packed, void *stream);
@@ -107,12 +108,21 @@ int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *d_b,
 
 /* ---- contractions -------------------------------------------------------- */
 
+/* Scratch memory the int8 convolution can use for this geometry (0 for most).  A stride-2
+ * convolution on NCHW4c data (the 3-channel stem) is fastest when it may first fold 2 x 2
+ * pixel blocks into a 16-channel image of half the size in scratch memory; without scratch
+ * (d_workspace NULL or too small) the same call runs a slower in-place gather.  No
+ * counterpart in the reference, whose generated kernels use no scratch. */
+size_t unit_conv2d_workspace_bytes(const unit_conv_desc *desc);
+
 /* Replaces topi.nn.conv2d_NCHWc_int8(..., out_dtype='int32') scheduled with
  * INTRINSICS['vnni'] (apps/cpu/kernel/conv2d.py:50-54).  d_out is s32
- * [n][c_out/16][oh][ow][16]; d_bias (c_out s32) may be NULL. */
+ * [n][c_out/16][oh][ow][16]; d_bias (c_out s32) may be NULL.  d_workspace: device
+ * scratch of workspace_bytes (see unit_conv2d_workspace_bytes), may be NULL. */
 int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
                               const void *d_packed_w, const int32_t *d_bias,
-                              int32_t *d_out, void *stream);
+                              int32_t *d_out, void *d_workspace, size_t workspace_bytes,
+                              void *stream);
 
 /* Same contraction with the fused epilogue
  *   q = clamp((acc + bias[oc] + 2^(shift-1)) >> shift, 0, 255)  -> u8 NCHW16c.
@@ -120,7 +130,8 @@ int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
  * flow (apps/cpu/relay/conv2d.py:16-27).  1 <= shift <= 31. */
 int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
                                    const void *d_packed_w, const int32_t *d_bias,
-                                   int32_t shift, uint8_t *d_out, void *stream);
+                                   int32_t shift, uint8_t *d_out, void *d_workspace,
+                                   size_t workspace_bytes, void *stream);
 
 /* Replaces topi.x86.dense_dotprod(a, b_packed, None, 'int32')
  * (apps/cpu/kernel/int8-gemm.py:16).  A is u8 [m][k] with row pitch lda

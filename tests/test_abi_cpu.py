@@ -57,12 +57,19 @@ def test_packed_weight_sizes_are_pure_host_functions(L):
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=512, c_out=2048, kh=1, kw=1))) == 32 * 2048 * 16
     # stem: 7 kh x 2 groups of 4 kw taps = 14 columns, in two stages of 8 (the last one partial)
     assert L.unit_packed_weights_bytes_conv_i8(
-        ctypes.byref(desc(c_in=4, c_block=4, kh=7, kw=7, h=224, w=224, stride_h=2, stride_w=2, pad_h=3, pad_w=3))) == 16 * 64 * 16
+        ctypes.byref(desc(c_in=4, c_block=4, kh=7, kw=7, h=224, w=224, stride_h=2, stride_w=2, pad_h=3, pad_w=3))) == 16 * 64 * 16 + 16 * 64 * 16
     # odd column count (9 taps x 1 chunk) is padded to an even number of columns
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=16, c_out=16))) == 10 * 16 * 16
     assert L.unit_packed_weights_bytes_conv_f16(ctypes.byref(desc(c_in=256, c_out=256))) == 288 * 256 * 16
     assert L.unit_packed_weights_bytes_dense_i8(4096, 4096) == 4096 * 4096
     assert L.unit_packed_weights_bytes_gemm_f16(768, 3072) == 768 * 3072 * 2
+    # the same stem with stride 1 has no folded form; scratch is needed only for the folded form
+    stem = dict(c_in=4, c_block=4, kh=7, kw=7, h=224, w=224, pad_h=3, pad_w=3)
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(**stem))) == 16 * 64 * 16
+    assert L.unit_conv2d_workspace_bytes(ctypes.byref(desc(**stem))) == 0
+    assert L.unit_conv2d_workspace_bytes(ctypes.byref(desc(stride_h=2, stride_w=2, n=3, **stem))) == 3 * 112 * 112 * 16
+    assert L.unit_conv2d_workspace_bytes(ctypes.byref(desc(stride_h=2, stride_w=2, **dict(stem, h=223)))) == 0
+    assert L.unit_conv2d_workspace_bytes(ctypes.byref(desc())) == 0
     # unsupported geometries report size 0
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_out=20))) == 0
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_block=8))) == 0
@@ -77,14 +84,14 @@ def test_argument_checks_return_status_codes(L):
     p = ctypes.c_void_p(addr)
     mis = ctypes.c_void_p(addr + 4)
     d = desc()
-    assert L.unit_conv2d_u8s8s32_nchwc(None, p, p, None, p, None) == -1
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), None, p, None, p, None) == -1
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), mis, p, None, p, None) == -3
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(kh=0)), p, p, None, p, None) == -2
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(c_in=60)), p, p, None, p, None) == -4
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(h=1, w=1, pad_h=0, pad_w=0)), p, p, None, p, None) == -2
-    assert L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), p, p, None, 0, p, None) == -2
-    assert L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), p, p, None, 32, p, None) == -2
+    assert L.unit_conv2d_u8s8s32_nchwc(None, p, p, None, p, None, 0, None) == -1
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), None, p, None, p, None, 0, None) == -1
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), mis, p, None, p, None, 0, None) == -3
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(kh=0)), p, p, None, p, None, 0, None) == -2
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(c_in=60)), p, p, None, p, None, 0, None) == -4
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc(h=1, w=1, pad_h=0, pad_w=0)), p, p, None, p, None, 0, None) == -2
+    assert L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), p, p, None, 0, p, None, 0, None) == -2
+    assert L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), p, p, None, 32, p, None, 0, None) == -2
     assert L.unit_conv2d_f16f32_nchw16c(ctypes.byref(desc(c_block=4, c_in=4)), p, p, p, None) == -4
     assert L.unit_dense_u8s8s32(0, 64, 64, p, 64, p, p, 64, None) == -2
     assert L.unit_dense_u8s8s32(8, 60, 64, p, 64, p, p, 64, None) == -2
@@ -106,5 +113,5 @@ def test_valid_call_without_a_device_reports_arch_not_a_crash(L):
     addr = ctypes.addressof(buf)
     addr += (-addr) % 16
     p = ctypes.c_void_p(addr)
-    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc()), p, p, None, p, None) == -5
+    assert L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(desc()), p, p, None, p, None, 0, None) == -5
     assert L.unit_dense_u8s8s32(8, 64, 64, p, 64, p, p, 64, None) == -5

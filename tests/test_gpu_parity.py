@@ -157,6 +157,41 @@ def test_wide_layer_bias_beyond_staged_vector(U, oracle):
         assert np.array_equal(gots.cpu().numpy(), oracle.conv2d_u8s8(x, w, bias=b))
 
 
+@pytest.mark.parametrize('hw,k,p', [(32, 7, 3), (33, 7, 3), (30, 3, 1), (30, 5, 2), (18, 7, 0), (20, 4, 1), (26, 6, 2)])
+def test_stem_stride2_geometries(U, oracle, hw, k, p):
+    """Stride-2 NCHW4c convolutions: even images take the folded (scratch) path, odd ones the in-place gather."""
+    rng = np.random.default_rng(hw * 100 + k)
+    x = rng.integers(0, 256, (3, 1, hw, hw + 2 * (hw % 2 == 0), 4), dtype=np.uint8)
+    w = rng.integers(-128, 128, (2, 1, k, k, 1, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 15, 2 ** 15, 32, dtype=np.int32)
+    got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=2, padding=p)
+    gotq = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=2, padding=p, bias=dev(b), out_dtype='uint8')
+    U.device_status()
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, w, (2, 2), (p, p)))
+    assert np.array_equal(gotq.cpu().numpy(), oracle.conv2d_u8s8(x, w, (2, 2), (p, p), bias=b, requant_shift=8))
+
+
+def test_stem_without_workspace_through_the_c_abi(U, oracle):
+    """The same stem with d_workspace = NULL: the library falls back to the in-place gather."""
+    import ctypes
+    from unit_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(77)
+    x = rng.integers(0, 256, (2, 1, 32, 32, 4), dtype=np.uint8)
+    w = rng.integers(-128, 128, (4, 1, 7, 7, 1, 16, 4), dtype=np.int8)
+    xd, wd = dev(x), dev(w)
+    pw = U.pack_conv_weights_int8(wd, 2, 3)
+    d = _lib.ConvDesc(2, 4, 32, 32, 4, 64, 7, 7, 2, 2, 3, 3)
+    assert L.unit_conv2d_workspace_bytes(ctypes.byref(d)) == 2 * 16 * 16 * 16
+    out = torch.empty((2, 4, 16, 16, 16), dtype=torch.int32, device='cuda')
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), ctypes.c_void_p(xd.data_ptr()), ctypes.c_void_p(pw.buf.data_ptr()),
+                                     None, ctypes.c_void_p(out.data_ptr()), None, 0, stream)
+    assert rc == 0
+    U.device_status()
+    assert np.array_equal(out.cpu().numpy(), oracle.conv2d_u8s8(x, w, (2, 2), (3, 3)))
+
+
 def test_stem_nchw4c(U, oracle):
     rng = np.random.default_rng(4)
     for (n, hw) in ((2, 32), (1, 224)):

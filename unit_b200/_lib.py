@@ -44,8 +44,9 @@ SIGNATURES = {
     'unit_pack_weights_dense_i8': (_ci, [_ci, _ci, _ci, _vp, _vp, _vp]),
     'unit_packed_weights_bytes_gemm_f16': (_sz, [_ci, _ci]),
     'unit_pack_weights_gemm_f16': (_ci, [_ci, _ci, _vp, _vp, _vp]),
-    'unit_conv2d_u8s8s32_nchwc': (_ci, [_dp, _vp, _vp, _vp, _vp, _vp]),
-    'unit_conv2d_u8s8_requant_nchwc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp]),
+    'unit_conv2d_workspace_bytes': (_sz, [_dp]),
+    'unit_conv2d_u8s8s32_nchwc': (_ci, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'unit_conv2d_u8s8_requant_nchwc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp, _sz, _vp]),
     'unit_dense_u8s8s32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),
     'unit_conv2d_f16f32_nchw16c': (_ci, [_dp, _vp, _vp, _vp, _vp]),
     'unit_gemm_f16f32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),

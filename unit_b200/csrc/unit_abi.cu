@@ -129,13 +129,14 @@ static int sm_count() {
 // ---------------------------------------------------------------------------
 // weight packing: reference layouts -> [n_tile][k_stage][kc][bn][16 B] blocks
 // ---------------------------------------------------------------------------
-enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4 };
+enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4, PACK_STEM_S2D = 5 };
 
 struct PackParams {
   const uint8_t *src;
   uint4 *dst;
   int mode, n_total, bn, kc, cols, k_stages, n_tiles;
   int Cc, KH, KW, kwg;  // conv
+  int tw, sft_h, sft_w;  // PACK_STEM_S2D: taps per row of the 2x2-folded kernel, tap shifts
   int K, T;             // dense / gemm (K in elements)
 };
 
@@ -168,6 +169,17 @@ __global__ void pack_weights_kernel(const PackParams p) {
           if (kw < p.KW) {
             // [oc/16][ci][kh][kw][0][oc%16][r]
             const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 64 + (oc & 15) * 4;
+            w[q] = *reinterpret_cast<const uint32_t *>(s);
+          }
+        }
+      } else if (p.mode == PACK_STEM_S2D) {
+        // column = tap (ty, tx) of the folded kernel; the 16 bytes are (dy, dx, c) with
+        // kh = 2 ty + dy - sft_h, kw = 2 tx + dx - sft_w of the original kernel
+        const int ty = j / p.tw, tx = j % p.tw;
+        for (int q = 0; q < 4; ++q) {
+          const int kh = 2 * ty + (q >> 1) - p.sft_h, kw = 2 * tx + (q & 1) - p.sft_w;
+          if (kh >= 0 && kh < p.KH && kw >= 0 && kw < p.KW) {
+            const uint8_t *s = p.src + (((size_t)(oc >> 4) * p.KH + kh) * p.KW + kw) * 64 + (oc & 15) * 4;
             w[q] = *reinterpret_cast<const uint32_t *>(s);
           }
         }
@@ -290,6 +302,52 @@ static unsigned grid_for(long long total) {
   if (b > 148 * 32) b = 148 * 32;
   if (b < 1) b = 1;
   return (unsigned)b;
+}
+
+// ---------------------------------------------------------------------------
+// stride-2 stem on NCHW4c as a stride-1 convolution on 2x2-folded pixels
+// ---------------------------------------------------------------------------
+// A pixel of the folded image holds the 2 x 2 block (2y + dy, 2x + dx) of 4-channel pixels:
+// 16 bytes ordered (dy, dx, c), i.e. an ordinary NCHW16c image of half the height and width.
+// With pad_lo = ceil(pad / 2) and sft = 2 pad_lo - pad, tap (ty, tx) of the folded kernel
+// covers the original taps kh = 2 ty + dy - sft_h, kw = 2 tx + dx - sft_w (absent taps get
+// zero weights), and the convolution becomes stride 1 with low padding pad_lo; the high side
+// needs no explicit padding because the tensor copy zero-fills beyond the image.
+struct StemFold {
+  bool ok = false;
+  int h2 = 0, w2 = 0, pad_h = 0, pad_w = 0, sft_h = 0, sft_w = 0, th = 0, tw = 0;
+};
+static StemFold stem_fold(const unit_conv_desc *d, bool need_even_image) {
+  StemFold f;
+  if (d->c_block != 4 || d->c_in != 4 || d->stride_h != 2 || d->stride_w != 2) return f;
+  if (need_even_image && ((d->h & 1) || (d->w & 1))) return f;
+  f.pad_h = (d->pad_h + 1) / 2;
+  f.pad_w = (d->pad_w + 1) / 2;
+  f.sft_h = 2 * f.pad_h - d->pad_h;
+  f.sft_w = 2 * f.pad_w - d->pad_w;
+  f.th = (d->kh - 1 + f.sft_h) / 2 + 1;
+  f.tw = (d->kw - 1 + f.sft_w) / 2 + 1;
+  f.h2 = d->h / 2;
+  f.w2 = d->w / 2;
+  f.ok = true;
+  return f;
+}
+
+// [n][1][h][w][4] -> [n][1][h/2][w/2][16]; one thread per folded pixel: two 8-byte reads, one 16-byte write
+__global__ void fold2x2_kernel(const uint2 *__restrict__ src, uint4 *__restrict__ dst, int n, int h2, int w2) {
+  const long long total = (long long)n * h2 * w2;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int x = (int)(idx % w2);
+    const long long t = idx / w2;
+    const int y = (int)(t % h2);
+    const long long img = t / h2;
+    // source row 2y of image img starts at ((img * 2 h2 + 2 y) * 2 w2) pixels = that many / 2 uint2
+    const long long row0 = (img * 2 * h2 + 2 * y) * (long long)w2;  // in uint2 units (2 pixels each)
+    const uint2 a = src[row0 + x];
+    const uint2 b = src[row0 + w2 + x];
+    dst[idx] = make_uint4(a.x, a.y, b.x, b.y);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -420,7 +478,7 @@ static BoxGeom choose_box(int n, int oh, int ow) {
 // Tiled-mode tensor map over u8 NCHW16c activations seen as (8-byte units of a pixel row, image
 // row, channel chunk, image): one copy fetches box_n x box_h row segments of box_w pixels, and
 // out-of-range coordinates (the zero padding) are filled with zeros by the copy engine.
-static bool make_box_map(CUtensorMap *map, const unit_conv_desc *d, const void *x, const BoxGeom &g) {
+static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -433,10 +491,10 @@ static bool make_box_map(CUtensorMap *map, const unit_conv_desc *d, const void *
     return reinterpret_cast<EncodeFn>(fn);
   }();
   if (!encode) return false;
-  const cuuint64_t cc = (cuuint64_t)d->c_in / 16;
-  const cuuint64_t dims[4] = {(cuuint64_t)d->w * 2, (cuuint64_t)d->h, cc, (cuuint64_t)d->n};
-  const cuuint64_t row = (cuuint64_t)d->w * 16;
-  const cuuint64_t strides[3] = {row, row * d->h, row * d->h * cc};
+  const cuuint64_t cc = (cuuint64_t)c_in / 16;
+  const cuuint64_t dims[4] = {(cuuint64_t)w * 2, (cuuint64_t)h, cc, (cuuint64_t)n};
+  const cuuint64_t row = (cuuint64_t)w * 16;
+  const cuuint64_t strides[3] = {row, row * h, row * h * cc};
   const cuuint32_t box[4] = {(cuuint32_t)g.bw * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(x), dims, strides, box, estr,
@@ -468,12 +526,30 @@ static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
   p.cols_per_chunk = elem_bytes;
 }
 
+static void set_box(IgemmParams &p, const BoxGeom &g, int n) {
+  p.box_n = g.bn; p.box_h = g.bh; p.box_w = g.bw; p.blocks_h = g.blocks_h; p.blocks_w = g.blocks_w;
+  p.n_img = n;
+  p.sub_tiles = g.sub_tiles;
+  p.div_box_hw = make_fast_div((uint32_t)(g.bh * g.bw));
+  p.div_box_w = make_fast_div((uint32_t)g.bw);
+  p.div_blocks_w = make_fast_div((uint32_t)g.blocks_w);
+  p.div_blocks_h = make_fast_div((uint32_t)g.blocks_h);
+  p.m_total = g.sub_tiles * kTileM;  // rows of the padded tiling; the kernel masks the idle ones
+}
+
+static size_t stem_workspace_bytes(const unit_conv_desc *d) {
+  const StemFold f = stem_fold(d, true);
+  return f.ok ? (size_t)d->n * f.h2 * f.w2 * 16 : 0;
+}
+
 static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias, int shift,
-                   void *out, bool requant, cudaStream_t st) {
+                   void *out, bool requant, void *workspace, size_t workspace_bytes, cudaStream_t st) {
   int rc = check_conv(d, false);
   if (rc) return rc;
   if (!x || !pw || !out) return UNIT_ERR_NULL;
-  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (bias && !aligned16(bias))) return UNIT_ERR_ALIGN;
+  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (bias && !aligned16(bias)) ||
+      (workspace && !aligned16(workspace)))
+    return UNIT_ERR_ALIGN;
   if (requant && (shift < 1 || shift > 31)) return UNIT_ERR_SHAPE;
   if ((rc = check_arch())) return rc;
   const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
@@ -481,20 +557,13 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
   p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
   fill_conv(p, d, 1);
   p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
+  CUtensorMap map;
   if (d->c_block == 16) {
-    CUtensorMap map;
     if (use_tma() && d->stride_h == 1 && d->stride_w == 1) {
       // stride 1: whole pixel rows per copy
       const BoxGeom g = choose_box(d->n, p.OH, p.OW);
-      if (make_box_map(&map, d, x, g)) {
-        p.box_n = g.bn; p.box_h = g.bh; p.box_w = g.bw; p.blocks_h = g.blocks_h; p.blocks_w = g.blocks_w;
-        p.n_img = d->n;
-        p.sub_tiles = g.sub_tiles;
-        p.div_box_hw = make_fast_div((uint32_t)(g.bh * g.bw));
-        p.div_box_w = make_fast_div((uint32_t)g.bw);
-        p.div_blocks_w = make_fast_div((uint32_t)g.blocks_w);
-        p.div_blocks_h = make_fast_div((uint32_t)g.blocks_h);
-        p.m_total = g.sub_tiles * kTileM;  // rows of the padded tiling; the kernel masks the idle ones
+      if (make_box_map(&map, d->n, d->c_in, d->h, d->w, x, g)) {
+        set_box(p, g, d->n);
         return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(p, c, st, &map)
                        : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(p, c, st, &map);
       }
@@ -504,6 +573,30 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
                      : launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, false>(p, c, st, &map);
     return requant ? launch_igemm<A_CONV_I8, EPI_REQ_NCHWC, false>(p, c, st)
                    : launch_igemm<A_CONV_I8, EPI_RAW_NCHWC, false>(p, c, st);
+  }
+  // NCHW4c.  With scratch memory a stride-2 stem runs as a stride-1 convolution on 2x2-folded
+  // pixels (whole pixel rows per copy); otherwise the 4-byte gather does it in place.
+  const StemFold f = stem_fold(d, true);
+  const size_t need = stem_workspace_bytes(d);
+  if (use_tma() && f.ok && workspace != nullptr && workspace_bytes >= need) {
+    const long long total = (long long)d->n * f.h2 * f.w2;
+    fold2x2_kernel<<<grid_for(total), 256, 0, st>>>(reinterpret_cast<const uint2 *>(x),
+                                                    static_cast<uint4 *>(workspace), d->n, f.h2, f.w2);
+    g_launches.fetch_add(1);
+    if (cudaGetLastError() != cudaSuccess) return UNIT_ERR_LAUNCH;
+    const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
+    const size_t generic_bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+    IgemmParams q = p;  // OH, OW, output geometry and epilogue stay; the input side changes
+    q.a = static_cast<const uint8_t *>(workspace);
+    q.b = static_cast<const uint8_t *>(pw) + generic_bytes;
+    q.H = f.h2; q.W = f.w2; q.Cc = 1; q.KH = f.th; q.KW = f.tw; q.sh = q.sw = 1; q.ph = f.pad_h; q.pw = f.pad_w;
+    q.img_bytes = (long long)f.h2 * f.w2 * 16;
+    const BoxGeom g = choose_box(d->n, q.OH, q.OW);
+    if (make_box_map(&map, d->n, 16, f.h2, f.w2, workspace, g)) {
+      set_box(q, g, d->n);
+      return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(q, cf, st, &map)
+                     : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(q, cf, st, &map);
+    }
   }
   return requant ? launch_igemm<A_STEM_I8, EPI_REQ_NCHWC, false>(p, c, st)
                  : launch_igemm<A_STEM_I8, EPI_RAW_NCHWC, false>(p, c, st);
@@ -558,7 +651,18 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles) {
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
   if (check_conv(d, false)) return 0;
   const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
-  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+  size_t bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+  const StemFold f = stem_fold(d, false);
+  if (f.ok) {  // second copy for the folded stride-1 form of a stride-2 stem
+    const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
+    bytes += (size_t)cf.n_tiles * cf.k_stages * cf.b_stage_bytes;
+  }
+  return bytes;
+}
+
+size_t unit_conv2d_workspace_bytes(const unit_conv_desc *d) {
+  if (check_conv(d, false)) return 0;
+  return stem_workspace_bytes(d);
 }
 
 int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *packed, void *stream) {
@@ -573,7 +677,19 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
   pp.mode = d->c_block == 16 ? PACK_CONV_I8 : PACK_STEM_I8;
   pp.n_total = d->c_out; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
   pp.Cc = d->c_in / d->c_block; pp.KH = d->kh; pp.KW = d->kw; pp.kwg = (d->kw + 3) / 4;
-  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+  rc = launch_pack(pp, static_cast<cudaStream_t>(stream));
+  const StemFold f = stem_fold(d, false);
+  if (rc == UNIT_OK && f.ok) {
+    const size_t generic_bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+    const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
+    PackParams pf = pp;
+    pf.dst = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(packed) + generic_bytes);
+    pf.mode = PACK_STEM_S2D;
+    pf.bn = cf.bn; pf.kc = cf.kc; pf.cols = cf.cols; pf.k_stages = cf.k_stages; pf.n_tiles = cf.n_tiles;
+    pf.tw = f.tw; pf.sft_h = f.sft_h; pf.sft_w = f.sft_w;
+    rc = launch_pack(pf, static_cast<cudaStream_t>(stream));
+  }
+  return rc;
 }
 
 size_t unit_packed_weights_bytes_conv_f16(const unit_conv_desc *d) {
@@ -640,13 +756,14 @@ int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *b, void *packed
 
 // ---- contractions ------------------------------------------------------------
 int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
-                              int32_t *out, void *stream) {
-  return conv_i8(d, x, pw, bias, 0, out, false, static_cast<cudaStream_t>(stream));
+                              int32_t *out, void *workspace, size_t workspace_bytes, void *stream) {
+  return conv_i8(d, x, pw, bias, 0, out, false, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
-                                   int32_t shift, uint8_t *out, void *stream) {
-  return conv_i8(d, x, pw, bias, shift, out, true, static_cast<cudaStream_t>(stream));
+                                   int32_t shift, uint8_t *out, void *workspace, size_t workspace_bytes,
+                                   void *stream) {
+  return conv_i8(d, x, pw, bias, shift, out, true, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_t lda, const void *pw, int32_t *cmat,

@@ -112,18 +112,23 @@ def _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, pad) -> ConvDesc:
     return ConvDesc(n, c_in, h, w, cb, c_out, kh, kw, stride[0], stride[1], pad[0], pad[1])
 
 
-def pack_conv_weights_int8(kernel: torch.Tensor) -> PackedWeights:
-    """kernel: s8 ``[O/16][I/cb][KH][KW][cb/4][16][4]`` (apps/cpu/kernel/conv2d.py:26,30)."""
+def pack_conv_weights_int8(kernel: torch.Tensor, stride: IntPair = 1, padding: IntPair = 0) -> PackedWeights:
+    """kernel: s8 ``[O/16][I/cb][KH][KW][cb/4][16][4]`` (apps/cpu/kernel/conv2d.py:26,30).
+
+    For NCHW4c kernels (cb = 4) the packed form also depends on the stride and padding the
+    convolution will use; for NCHW16c kernels they are ignored.
+    """
     L = _require_cuda_lib()
     kernel = _to_device(kernel, torch.int8, 'kernel')
     if kernel.dim() != 7 or kernel.shape[5] != 16 or kernel.shape[6] != 4 or kernel.shape[4] not in (1, 4):
         raise ValueError(f'kernel must be [O/16][I/cb][KH][KW][cb/4][16][4], got {tuple(kernel.shape)}')
     oc, icc, kh, kw, c4 = (int(s) for s in kernel.shape[:5])
     cb = c4 * 4
-    key = ('conv_i8', oc * 16, icc * cb, cb, kh, kw)
+    stride, padding = (_pair(stride), _pair(padding)) if cb == 4 else ((1, 1), (0, 0))
+    key = ('conv_i8', oc * 16, icc * cb, cb, kh, kw, stride, padding)
 
     def make():
-        d = _conv_desc(1, icc * cb, kh, kw, cb, oc * 16, kh, kw, (1, 1), (0, 0))
+        d = _conv_desc(1, icc * cb, kh + 2 * 64, kw + 2 * 64, cb, oc * 16, kh, kw, stride, padding)
         nbytes = L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d))
         if nbytes == 0:
             raise ValueError('unsupported convolution weights')
@@ -203,6 +208,21 @@ def pack_gemm_weights_f16(b: torch.Tensor) -> PackedWeights:
 # --------------------------------------------------------------------------
 # int8 path
 # --------------------------------------------------------------------------
+_WORKSPACES: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch buffer per (device, stream), grown on demand; calls on one stream run in order,
+    so they can share it."""
+    key = (device.index, _stream())
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+
 def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: IntPair = 0, dilation: IntPair = 1,
                       layout: str = 'NCHW4c', out_layout: str = 'NCHW16c', out_dtype: str = 'int32', *,
                       bias: Optional[torch.Tensor] = None, requant_shift: Optional[int] = None,
@@ -231,12 +251,14 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
         raise ValueError(f'data must be [N][C/cb][H][W][cb] with cb in (4, 16), got {tuple(data.shape)}')
     n, cc, h, w, cb = (int(s) for s in data.shape)
     with torch.cuda.device(data.device):
-        pw = kernel if isinstance(kernel, PackedWeights) else pack_conv_weights_int8(kernel)
+        pw = kernel if isinstance(kernel, PackedWeights) else pack_conv_weights_int8(kernel, stride, padding)
         if pw.kind != 'conv_i8':
             raise ValueError('kernel was packed for a different operator')
-        _, c_out, c_in, pcb, kh, kw = pw.key
+        _, c_out, c_in, pcb, kh, kw, pstride, ppad = pw.key
         if c_in != cc * cb or pcb != cb:
             raise ValueError(f'channel mismatch: data has {cc}x{cb}, kernel expects {c_in} in blocks of {pcb}')
+        if cb == 4 and (pstride != stride or ppad != padding):
+            raise ValueError('NCHW4c weights were packed for a different stride / padding')
         requant = out_dtype == 'uint8' or requant_shift is not None
         shift = 8 if requant_shift is None else int(requant_shift)
         d = _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, padding)
@@ -258,12 +280,15 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
                 raise ValueError(f'out must be a contiguous CUDA {odt} tensor of shape {oshape}')
         if n == 0:
             return out_t.cpu() if (host and out is None) else out_t
+        ws_bytes = int(L.unit_conv2d_workspace_bytes(ctypes.byref(d)))
+        ws = _workspace(data.device, ws_bytes) if ws_bytes else None
         if requant:
             check(L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), shift,
-                                                   _ptr(out_t), _stream()), 'unit_conv2d_u8s8_requant_nchwc')
+                                                   _ptr(out_t), _ptr(ws), ws_bytes, _stream()),
+                  'unit_conv2d_u8s8_requant_nchwc')
         else:
             check(L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), _ptr(out_t),
-                                              _stream()), 'unit_conv2d_u8s8s32_nchwc')
+                                              _ptr(ws), ws_bytes, _stream()), 'unit_conv2d_u8s8s32_nchwc')
     return out_t.cpu() if (host and out is None) else out_t
 
 
