@@ -765,39 +765,47 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int g_end = min(g_begin + per, groups);
     const int dtid = threadIdx.x;  // 0..511 within the drain warps
     const bool static_wide = EPI == EPI_REQ_NCHWC && (p.shift > 23 || p.acc_bound >= (1ll << 30));
+    int staged_n0 = -1, staged_n1 = -1;              // column block whose bias each accumulator set holds
+    bool staged_wide0 = false, staged_wide1 = false;  // and whether those columns need the 64-bit path
     for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile % p.n_tiles;
       const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
       const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
       // Stage this tile's bias values (plus the rounding constant on the 32-bit requantise
-      // path).  Barrier A: every drain warp has left the previous tile, so bias[slot] is free;
-      // it also ORs the per-column "needs 64 bits" tests so that all threads take the same
-      // path.  Barrier B (after the wait for the accumulator): publishes the staged values and
-      // ORs the outcome of the bounded wait, so that the drain warps give up together.
-      bool wide = false;
+      // path) unless this accumulator set last served the same columns: a CTA's tiles keep or
+      // alternate their column block, so staging happens once or twice per kernel.
+      // Barrier A: every drain warp has left the previous tile, so bias[slot] is free; it also
+      // ORs the per-column "needs 64 bits" tests so that all threads take the same path.
+      // Barrier B (after the wait for the accumulator): publishes the staged values and ORs
+      // the outcome of the bounded wait, so that the drain warps give up together.
       const int32_t *tile_bias = &ps->bias[slot][0];
       if constexpr (EPI != EPI_RAW_ROWS) {
-        int32_t b = 0;
-        long long br = 0;
-        int need_wide = 0;
-        if (dtid < p.bn) {
-          const int col = n_tile * p.bn + dtid;
-          b = (p.bias != nullptr && col < p.n_total) ? __ldg(p.bias + col) : 0;
-          if constexpr (EPI == EPI_REQ_NCHWC) {
-            br = (long long)b + (1ll << (p.shift - 1));
-            const long long mag = br < 0 ? -br : br;
-            need_wide = (mag + p.acc_bound >= (1ll << 31)) ? 1 : 0;
+        if ((slot ? staged_n1 : staged_n0) != n_tile) {  // same decision in every drain thread
+          int32_t b = 0;
+          long long br = 0;
+          int need_wide = 0;
+          if (dtid < p.bn) {
+            const int col = n_tile * p.bn + dtid;
+            b = (p.bias != nullptr && col < p.n_total) ? __ldg(p.bias + col) : 0;
+            if constexpr (EPI == EPI_REQ_NCHWC) {
+              br = (long long)b + (1ll << (p.shift - 1));
+              const long long mag = br < 0 ? -br : br;
+              need_wide = (mag + p.acc_bound >= (1ll << 31)) ? 1 : 0;
+            }
           }
-        }
-        if constexpr (EPI == EPI_REQ_NCHWC) {
-          wide = drain_barrier_or(need_wide) || static_wide;
-          if (dtid < p.bn) ps->bias[slot][dtid] = wide ? b : (int32_t)br;
-        } else {
-          drain_barrier_or(0);
-          if (dtid < p.bn) ps->bias[slot][dtid] = b;
+          if constexpr (EPI == EPI_REQ_NCHWC) {
+            const bool w = drain_barrier_or(need_wide) || static_wide;
+            if (slot) staged_wide1 = w; else staged_wide0 = w;
+            if (dtid < p.bn) ps->bias[slot][dtid] = w ? b : (int32_t)br;
+          } else {
+            drain_barrier_or(0);
+            if (dtid < p.bn) ps->bias[slot][dtid] = b;
+          }
+          if (slot) staged_n1 = n_tile; else staged_n0 = n_tile;
         }
       }
+      const bool wide = slot ? staged_wide1 : staged_wide0;
       const bool got = mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull);
       if (drain_barrier_or(got ? 0 : 1)) {
         alive = false;
