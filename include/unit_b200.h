@@ -133,6 +133,30 @@ int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *desc, const uint8_t *d_
                                    int32_t shift, uint8_t *d_out, void *d_workspace,
                                    size_t workspace_bytes, void *stream);
 
+/* Requantising convolution for callers that may not allocate.  No counterpart in the
+ * reference.  It is unit_conv2d_u8s8_requant_nchwc with the scratch taken from a fixed array
+ * inside the library instead of a caller-provided workspace.  Some hosts of this library have
+ * no way to obtain device memory at call time: an operator invoked from a runtime whose buffers
+ * are all planned before execution (as the reference's graph runtime does) receives only its
+ * input and output tensors, and a serving loop that must never trigger the device-wide
+ * synchronisation of cudaMalloc / cudaFree cannot allocate either.  This entry point calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *   - Limit: the scratch a geometry needs (unit_conv2d_workspace_bytes) must not exceed
+ *     unit_noalloc_scratch_capacity() = 8 MiB, e.g. a 224 x 224 NCHW4c stem up to batch 41;
+ *     larger requests return UNIT_ERR_TOO_LARGE and nothing is launched.  Geometries that need
+ *     no scratch are simply forwarded.
+ *   - Every GPU that loads the library holds the 8 MiB until the process exits.
+ *   - The first call on each device looks up the array's device address (one runtime query,
+ *     no allocation); make that first call before any stream capture begins.
+ *   - All calls share the one array, which keeps whatever the last call wrote.  Nothing in it
+ *     has to start at zero: each call overwrites the part it reads.  Calls that can overlap on
+ *     the GPU (different streams, or one stream's call not yet finished when another begins
+ *     elsewhere) race on it; issue them on one stream or serialise them yourself. */
+size_t unit_noalloc_scratch_capacity(void);
+int unit_conv2d_u8s8_requant_nchwc_noalloc(const unit_conv_desc *desc, const uint8_t *d_x,
+                                           const void *d_packed_w, const int32_t *d_bias,
+                                           int32_t shift, uint8_t *d_out, void *stream);
+
 /* Replaces topi.x86.dense_dotprod(a, b_packed, None, 'int32')
  * (apps/cpu/kernel/int8-gemm.py:16).  A is u8 [m][k] with row pitch lda
  * bytes, C is s32 [m][n] with row pitch ldc elements. */

@@ -47,6 +47,8 @@ SIGNATURES = {
     'unit_conv2d_workspace_bytes': (_sz, [_dp]),
     'unit_conv2d_u8s8s32_nchwc': (_ci, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     'unit_conv2d_u8s8_requant_nchwc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp, _sz, _vp]),
+    'unit_noalloc_scratch_capacity': (_sz, []),
+    'unit_conv2d_u8s8_requant_nchwc_noalloc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp]),
     'unit_dense_u8s8s32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),
     'unit_conv2d_f16f32_nchw16c': (_ci, [_dp, _vp, _vp, _vp, _vp]),
     'unit_gemm_f16f32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),

@@ -15,6 +15,11 @@
 namespace unit {
 
 __device__ unsigned int g_error_word = 0;
+
+// Scratch for unit_conv2d_u8s8_requant_nchwc_noalloc: lives in the library image, so every
+// GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<unsigned long long *> g_trace{nullptr};
 static std::atomic<int> g_trace_cap{0};
@@ -602,6 +607,24 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
                  : launch_igemm<A_STEM_I8, EPI_RAW_NCHWC, false>(p, c, st);
 }
 
+// Device address of g_static_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is looked up
+// once per device (with that device current) and cached.
+static int static_scratch_address(void **out) {
+  static std::mutex mu;
+  static void *cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return UNIT_ERR_ARCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return UNIT_ERR_LAUNCH;
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return UNIT_OK;
+}
+
 }  // namespace unit
 
 using namespace unit;
@@ -764,6 +787,23 @@ int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *d, const uint8_t *x, co
                                    int32_t shift, uint8_t *out, void *workspace, size_t workspace_bytes,
                                    void *stream) {
   return conv_i8(d, x, pw, bias, shift, out, true, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+size_t unit_noalloc_scratch_capacity(void) { return kStaticScratchBytes; }
+
+int unit_conv2d_u8s8_requant_nchwc_noalloc(const unit_conv_desc *d, const uint8_t *x, const void *pw,
+                                           const int32_t *bias, int32_t shift, uint8_t *out, void *stream) {
+  const int rc = check_conv(d, false);
+  if (rc) return rc;
+  const size_t need = stem_workspace_bytes(d);
+  if (need > kStaticScratchBytes) return UNIT_ERR_TOO_LARGE;  // beyond the built-in scratch: use the workspace form
+  void *scratch = nullptr;
+  if (need > 0) {
+    const int rs = static_scratch_address(&scratch);
+    if (rs) return rs;
+  }
+  return conv_i8(d, x, pw, bias, shift, out, true, scratch, need ? kStaticScratchBytes : 0,
+                 static_cast<cudaStream_t>(stream));
 }
 
 int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_t lda, const void *pw, int32_t *cmat,
