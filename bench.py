@@ -105,6 +105,7 @@ def cpu_sweep(sample_batch: int, min_seconds: float, max_passes: int = 50):
     from oracle import c_oracle as co
     from unit_b200 import resnet50 as R
     vnni = co.host_has_vnni()
+    co.use_all_cores()
     data = []
     for i, l in enumerate(R.LAYERS):
         x, w, b = R.make_layer_inputs(l, i, sample_batch, config=5)
@@ -136,6 +137,7 @@ def run_reference(args):
     from oracle import c_oracle as co
     from unit_b200 import resnet50 as R
     vnni = co.host_has_vnni()
+    co.use_all_cores()
     data = [(l,) + R.make_layer_inputs(l, i, sample, config=5) for i, l in enumerate(R.LAYERS)]
 
     def step():
@@ -365,7 +367,7 @@ def run_unit(args):
                        'l2': 'every convolution instance has its own buffers; %.2f GB touched per step per GPU, '
                              'larger than L2' % (sum(l.bytes(batch) * l.count for l in layer_set) / 1e9)},
             'clocks': clocks,
-            'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+            'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d * world, 'd2h_bytes_per_step': d2h * world,
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': gpu_launches,
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',

@@ -50,6 +50,8 @@ def lib() -> ctypes.CDLL:
     vp, ci = ctypes.c_void_p, ctypes.c_int
     L.oracle_has_vnni.restype = ci
     L.oracle_max_threads.restype = ci
+    L.oracle_set_threads.argtypes = [ci]
+    L.oracle_set_threads.restype = None
     L.oracle_vnni_dot.argtypes = [vp, vp, vp]
     L.oracle_vnni_dot_hw.argtypes = [vp, vp, vp]
     L.oracle_vnni_dot_hw.restype = ci
@@ -66,6 +68,16 @@ def lib() -> ctypes.CDLL:
     L.oracle_gemm_f16f32.restype = None
     _LIB = L
     return L
+
+
+def use_all_cores() -> int:
+    """Let the OpenMP baseline use every core this process may run on; returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_threads(n)
+    return int(lib().oracle_max_threads())
 
 
 def _p(a):

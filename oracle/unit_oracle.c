@@ -52,6 +52,16 @@ typedef _Float16 f16;
 
 int oracle_has_vnni(void) { return UNIT_HAVE_VNNI; }
 
+/* Number of OpenMP threads the timed baseline may use (launchers such as torchrun export
+ * OMP_NUM_THREADS=1; the baseline is meant to use every core the process may run on). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
