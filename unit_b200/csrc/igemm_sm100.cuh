@@ -305,15 +305,6 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
   asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-// Waits for this thread's TMEM reads; the registers are operands so that the compiler keeps
-// every use of them behind the wait.
-__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&v)[16]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
-                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
-               :
-               : "memory");
-}
 // Named barrier 1 over the drain warps; returns the OR of `flag` over all of them.
 __device__ __forceinline__ bool drain_barrier_or(int flag) {
   uint32_t r;
@@ -850,18 +841,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t va[16], vb[16];
       if (g_begin < g_end) {
         tmem_ld16(t_row + (uint32_t)g_begin * 16u, va);
-        tmem_ld_wait16(va);
+        tmem_ld_wait();
       }
       for (int g = g_begin; g < g_end; g += 2) {
         const bool has_b = g + 1 < g_end;
         if (has_b) tmem_ld16(t_row + (uint32_t)(g + 1) * 16u, vb);
         if (mvalid && n_tile * p.bn + g * 16 < p.n_total)
           store_group16<EPI>(p, tile_bias + g * 16, wide, va, obase + g * gstride);
-        tmem_ld_wait16(vb);
+        tmem_ld_wait();
         if (g + 2 < g_end) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
         if (has_b && mvalid && n_tile * p.bn + (g + 1) * 16 < p.n_total)
           store_group16<EPI>(p, tile_bias + (g + 1) * 16, wide, vb, obase + (g + 1) * gstride);
-        tmem_ld_wait16(va);
+        tmem_ld_wait();
       }
       tc_fence_before();
       __syncwarp();
