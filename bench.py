@@ -169,6 +169,31 @@ def run_reference(args):
     return 0
 
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the two layers captured
+# with `ncu --set full` at batch 256 on one GPU; the summaries under profiles/ give the commands.
+NCU_TRAFFIC_B256 = {'s1_1x1_64_256': 51.46e6 + 147.64e6, 's3_3x3_256_256': 13.48e6 + 0.0}
+
+
+def roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak):
+    """Roofline objects of the captured layers: achieved from this run's per-layer timing."""
+    out = []
+    by_name = {r['layer']: r for r in layer_rows}
+    for l in layer_set:
+        if l.name not in NCU_TRAFFIC_B256 or l.name not in by_name:
+            continue
+        r = by_name[l.name]
+        us = r['us']
+        if r['bound'] == 'hbm':
+            achieved, peak, unit = l.bytes(batch) / us / 1e3, peaks['hbm_gbs'], 'GB/s'
+        else:
+            achieved, peak, unit = l.ops(batch) / us / 1e6, int8_peak, 'TOPS'
+        out.append({'layer': l.name, 'bound': r['bound'], 'achieved': achieved, 'peak': peak, 'unit': unit,
+                    'frac': achieved / peak,
+                    'traffic': NCU_TRAFFIC_B256[l.name] if batch == TOTAL_BATCH else None,
+                    'algorithmic_bytes': l.bytes(batch)})
+    return out
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -374,9 +399,13 @@ def run_unit(args):
                          'frac': kernel_tops / int8_peak, 'traffic': None,
                          'peak_source': f'2 x bf16_tflops_sustained of {peaks["source"]} peaks '
                                         '(dense int8 issues at twice the bf16 rate)',
-                         'kernel': 'igemm_kernel<A_CONV_I8, EPI_REQ_NCHWC> over the 53 launches of one step',
+                         'kernel': 'igemm_kernel<A_CONV_BOX|A_CONV_TMA, EPI_REQ_NCHWC, i8> over the contraction launches '
+                                   'of one step (2 x ops / summed per-layer launch time, CUDA events)',
+                         'traffic_note': 'the launches are 24 different layers; DRAM traffic from ncu is given per '
+                                         'captured layer in roofline_samples',
                          'mixed_bound_frac': (sum_roof_ms / sum_kernel_ms) if sum_roof_ms else None,
                          'hbm_peak_gbs': peaks['hbm_gbs']},
+            'roofline_samples': roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak),
             'layers': layer_rows,
             'cpu_baseline': cpu,
         }
