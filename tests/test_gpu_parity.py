@@ -143,6 +143,35 @@ def test_requant_rounding_and_bias_only_s32(U, oracle):
     U.device_status()
 
 
+def test_bias_through_the_tensor_core_and_through_the_drain(U, oracle):
+    """Biases small enough enter the accumulator as one more K step of the MMA; larger ones are
+    added by the drain.  Both edges of the first range, every digit pattern, and mixed blocks."""
+    rng = np.random.default_rng(77)
+    x = rng.integers(0, 256, (2, 3, 9, 9, 16), dtype=np.uint8)
+    w = rng.integers(-128, 128, (20, 3, 3, 3, 4, 16, 4), dtype=np.int8)   # 320 channels: two column blocks
+    lo, hi = -245760, 243967                                             # range of bias + rounding constant
+    cases = {
+        'edges_shift8': (8, np.resize(np.array([lo - 128, hi - 128, 0, -1, 1, -128, 127, lo - 127, hi - 129], np.int64), 320)),
+        'all_digits': (8, np.arange(320, dtype=np.int64) * 1531 - 244000),
+        'just_outside': (8, np.resize(np.array([hi - 127, 5, lo - 129, 7], np.int64), 320)),
+        'second_block_outside': (8, np.concatenate([rng.integers(-2 ** 15, 2 ** 15, 160), rng.integers(-2 ** 24, 2 ** 24, 160)])),
+        'shift1': (1, rng.integers(-2 ** 15, 2 ** 15, 320)),
+        'shift18': (18, rng.integers(-2 ** 16, 2 ** 16, 320)),
+        'shift19_rounding_too_large': (19, rng.integers(-2 ** 12, 2 ** 12, 320)),
+        'huge': (8, rng.integers(-2 ** 31, 2 ** 31, 320)),
+    }
+    for name, (shift, b) in cases.items():
+        b = np.asarray(b, np.int64).astype(np.int32)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(w), padding=1, bias=dev(b), requant_shift=shift).cpu().numpy()
+        gots = U.conv2d_NCHWc_int8(dev(x), dev(w), padding=1, bias=dev(b)).cpu().numpy()
+        U.device_status()
+        assert np.array_equal(got, oracle.conv2d_u8s8(x, w, (1, 1), (1, 1), bias=b, requant_shift=shift)), name
+        assert np.array_equal(gots, oracle.conv2d_u8s8(x, w, (1, 1), (1, 1), bias=b)), name
+    # requantisation without a bias: only the rounding constant goes in
+    got = U.conv2d_NCHWc_int8(dev(x), dev(w), padding=1, out_dtype='uint8').cpu().numpy()
+    assert np.array_equal(got, oracle.conv2d_u8s8(x, w, (1, 1), (1, 1), requant_shift=8))
+
+
 def test_wide_layer_bias_beyond_staged_vector(U, oracle):
     """More output channels than the kernel keeps in shared memory (2048), with ordinary and extreme biases."""
     rng = np.random.default_rng(21)

@@ -54,9 +54,11 @@ enum AMode : int {
   A_STEM_I8 = 2,   // u8 NCHW4c: one column = 4 consecutive kw taps x 4 channels
   A_DENSE = 3,     // plain row-major matrix, K contiguous
   A_CONV_TMA = 4,  // NCHW16c (u8 or fp16) fetched by im2col-mode TMA: one bulk tensor copy per K column
-  A_CONV_BOX = 5   // u8 NCHW16c, stride 1: each sub-tile is a box of (images x output rows x
+  A_CONV_BOX = 5,  // u8 NCHW16c, stride 1: each sub-tile is a box of (images x output rows x
                    // row segment) fetched by tiled-mode TMA, whole pixel rows at a time
+  A_DENSE_TMA = 6  // plain row-major matrix fetched by tiled-mode TMA: one copy = 128 rows x 16 bytes
 };
+__host__ __device__ constexpr bool a_mode_uses_tma(int m) { return m == A_CONV_TMA || m == A_CONV_BOX || m == A_DENSE_TMA; }
 enum EpiMode : int {
   EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
   EPI_REQ_NCHWC = 1,  // + bias, round-shift, clamp -> u8 [n][oc/16][oh][ow][16]
@@ -67,6 +69,8 @@ constexpr int kTileM = 128;
 constexpr int kMaxStages = 12;
 constexpr int kNumThreads = 704;
 constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21;
+constexpr uint32_t kFoldBBytes = 4096;  // one accumulator set's bias digits: 256 channels x 16 bytes
+constexpr uint32_t kFoldBytes = 2 * kFoldBBytes + 2 * 128 * 16;  // two sets + the constant A block (2 columns)
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
 constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
 
@@ -108,6 +112,7 @@ struct IgemmParams {
   long long sub_tiles;      // number of sub-tiles
   FastDiv div_box_hw, div_box_w, div_blocks_w, div_blocks_h;
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
+  int fold_bias;  // 0: the drain always adds the bias (comparison runs)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
 };
@@ -175,12 +180,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   atomicCAS(err, 0u, code);
   return false;
 }
-// Warp-collective form: lane 0 waits, the result is broadcast (32x fewer barrier probes).
+// Warp-collective form, called by all 32 lanes together.  Every lane probes the barrier (one
+// warp-wide instruction on one address) and the lanes agree by vote, so the warp stays converged.
+// Measured: a warp whose lane 0 polls while the other lanes are parked at a warp-level
+// synchronisation point runs that lane markedly slower (10-20 % on whole K-loop-bound layers).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                                unsigned int *err, uint32_t code) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, err, code) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  bool timed_out = true;
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, 400u) ? 1 : 0)) return true;
+    __nanosleep(32);
+    if ((it & 15u) == 15u) {
+      if (__any_sync(0xffffffffu, *abort_flag)) { timed_out = false; break; }
+      if (__any_sync(0xffffffffu, global_timer_ns() - t0 > 1000000000ull ? 1 : 0)) break;
+    }
+  }
+  if (timed_out && (threadIdx.x & 31) == 0) {
+    *abort_flag = 1;
+    atomicCAS(err, 0u, code);
+  }
+  return false;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
@@ -228,6 +249,14 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap *tma
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
       "%5}], [%6];" ::"r"(dst),
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+// tiled-mode tensor copy of one box of the 3-D tensor (8-byte half of a 16-byte column, column, row)
+__device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap *tmap, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
+      "[%5];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -305,17 +334,6 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
   asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-// Named barrier 1 over the drain warps; returns the OR of `flag` over all of them.
-__device__ __forceinline__ bool drain_barrier_or(int flag) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(r)
-      : "r"(flag), "n"(kDrainWarps * 32)
-      : "memory");
-  return r != 0;
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Tile trace: CTA 0 records when each role passes a point of tile `lt` (slot 0-7).
@@ -343,7 +361,8 @@ __device__ __forceinline__ uint32_t make_idesc(int bn) {
 }
 
 struct alignas(16) PipeShared {
-  int32_t bias[2][kBiasSmem];  // per accumulator set: bias (+ rounding constant) of the tile's columns
+  int32_t bias[2][2][kBiasSmem];  // [accumulator set][version]: bias (+ rounding constant) where the drain adds it
+  int bias_mma[2];                // per accumulator set: the bias goes in through one more MMA K step
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
   unsigned long long tfull[2];
@@ -359,12 +378,31 @@ struct alignas(16) PipeShared {
 // group's 16 staged bias values in shared memory (bias + rounding constant for the
 // requantising epilogue).
 template <int EPI>
-__device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, bool wide, const uint32_t *v,
-                                              long long o) {
-  if constexpr (EPI == EPI_RAW_ROWS) {
-    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+__device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, bool folded, bool wide,
+                                              const uint32_t *v, long long o) {
+  if (EPI == EPI_RAW_ROWS || folded) {
+    // the accumulator is final: bias and rounding constant, if any, came in through the MMA
+    if constexpr (EPI == EPI_REQ_NCHWC) {
+      uint32_t w[4];
+      if (p.shift == 8) {
+        // clamp to [0, 65535] while packing pairs, then keep the high byte of each half-word:
+        // min(max(x, 0), 65535) >> 8 == min(max(x >> 8, 0), 255)
 #pragma unroll
-    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        for (int q = 0; q < 4; ++q)
+          w[q] = __byte_perm(pack_sat_u16((int32_t)v[4 * q + 1], (int32_t)v[4 * q]),
+                             pack_sat_u16((int32_t)v[4 * q + 3], (int32_t)v[4 * q + 2]), 0x7531);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          w[q] = pack_sat_u8((int32_t)v[4 * q + 1] >> p.shift, (int32_t)v[4 * q] >> p.shift,
+                             pack_sat_u8((int32_t)v[4 * q + 3] >> p.shift, (int32_t)v[4 * q + 2] >> p.shift, 0u));
+      }
+      *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
   } else {
     int32_t bv[16];
     const int4 *bp = reinterpret_cast<const int4 *>(bias_s);
@@ -420,6 +458,74 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
   }
 }
 
+// Prepares the bias of one accumulator set's columns for the tile that will use the set next.
+// Called by each drain warp with all lanes; the warps work independently (no CTA barrier).
+//
+// Preferred form: bias (plus the rounding constant 2^(shift-1) when requantising) enters the
+// accumulator as one more K step of the MMA.  The A side of that step is a constant block whose
+// every row holds the bytes {1, 128, 128, ... 128} (second 16-byte column: zeros); the B side
+// holds, per output channel, sixteen s8 digits {d0, d1 ... d15} with
+//     d0 + 128 * (d1 + ... + d15) == value,   0 <= d0 < 128,  -128 <= dj <= 127,
+// which exists for -245760 <= value <= 243967.  The drain then stores the accumulator as it is.
+// If a value of the block does not fit (or the 64-bit requantisation is needed) the values go to
+// ps->bias[slot][version] as integers and the drain adds them.
+//
+// Every warp reads all of the block's values to reach the same verdict (folded / wide) by warp
+// votes; warp w then writes channels 16 w .. 16 w + 15.  The writes become visible to the MMA
+// warp through this warp's arrival on the set's "empty" barrier.
+template <int EPI>
+__device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps, uint8_t *fold_mem, uint32_t slot,
+                                           uint32_t version, int n_tile, int warp, int lane, bool &folded, bool &wide) {
+  constexpr bool kReq = EPI == EPI_REQ_NCHWC;
+  if (!kReq && p.bias == nullptr) {  // nothing to add at all: the accumulator is final without an extra step
+    folded = true;
+    wide = false;
+    if (warp == 0 && lane == 0) ps->bias_mma[slot] = 0;
+    return;
+  }
+  const bool static_wide = kReq && (p.shift > 23 || p.acc_bound >= (1ll << 30));
+  const long long rnd = kReq ? (1ll << (p.shift - 1)) : 0ll;
+  const int col0 = n_tile * p.bn;
+  bool fits = !static_wide && p.fold_bias != 0, need_wide = static_wide;
+#pragma unroll
+  for (int i = 0; i < kBiasSmem / 32; ++i) {
+    const int ch = lane + 32 * i;
+    const int32_t b = (ch < p.bn && p.bias != nullptr && col0 + ch < p.n_total) ? __ldg(p.bias + col0 + ch) : 0;
+    const long long v = (long long)b + rnd;
+    const long long hi = v >> 7;
+    fits = fits && hi >= -1920 && hi <= 1905;
+    if (kReq) {
+      const long long mag = v < 0 ? -v : v;
+      need_wide = need_wide || (mag + p.acc_bound >= (1ll << 31));
+    }
+  }
+  fits = __all_sync(0xffffffffu, fits ? 1 : 0) != 0;
+  need_wide = __any_sync(0xffffffffu, need_wide ? 1 : 0) != 0;
+  const int ch = warp * 16 + lane;
+  if (lane < 16 && ch < p.bn) {
+    const int32_t b = (p.bias != nullptr && col0 + ch < p.n_total) ? __ldg(p.bias + col0 + ch) : 0;
+    if (fits) {
+      const int v = b + (int)rnd;
+      const int hi = v >> 7, d0 = v & 127;
+      const int q = hi / 15, rem = hi - 15 * q;  // hi = 15 q + rem, |rem| < 15, rem has the sign of hi
+      const int extra = rem < 0 ? -rem : rem, step = rem < 0 ? -1 : 1;
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int d = j == 0 ? d0 : q + (j <= extra ? step : 0);
+        w[j >> 2] |= (uint32_t)(d & 0xff) << (8 * (j & 3));
+      }
+      *reinterpret_cast<uint4 *>(fold_mem + (size_t)slot * kFoldBBytes + (size_t)ch * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      ps->bias[slot][version][ch] = (kReq && !need_wide) ? (int32_t)((long long)b + rnd) : b;
+    }
+  }
+  if (warp == 0 && lane == 0) ps->bias_mma[slot] = fits ? 1 : 0;
+  fence_proxy_async();  // the digits are read by the tensor core (async proxy)
+  folded = fits;
+  wide = need_wide;
+}
+
 template <int AMODE, int EPI, bool F16, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
@@ -432,7 +538,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const uint32_t a_stage_bytes = (uint32_t)MT * a_sub_bytes;
   const uint32_t b_stage_bytes = (uint32_t)p.kc * (uint32_t)p.bn * 16u;
   const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
-  PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes);
+  PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes + kFoldBytes);
   const uint32_t smem_base = smem_u32(smem);
   volatile int *abort_flag = &ps->abort_flag;
   // accumulator sets that fit in the 512 TMEM columns (2 = drain overlaps the next main loop)
@@ -441,11 +547,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       // 128 A-producer threads + the B producer; with TMA-fed A only the thread that issues all copies
-      mbar_init(smem_u32(&ps->full[s]), (AMODE == A_CONV_TMA || AMODE == A_CONV_BOX) ? 2 : 128 + 1);
+      mbar_init(smem_u32(&ps->full[s]), a_mode_uses_tma(AMODE) ? 2 : 128 + 1);
       mbar_init(smem_u32(&ps->empty[s]), 1);       // one tcgen05.commit
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ps->tfull[i]), 1);             // one tcgen05.commit
+      mbar_init(smem_u32(&ps->tfull[i]), 2);             // the issuing thread's arrival + its tcgen05.commit
       mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps);  // the drain warps
     }
     ps->abort_flag = 0;
@@ -462,7 +568,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (AMODE != A_CONV_TMA && AMODE != A_CONV_BOX && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
+  if (!a_mode_uses_tma(AMODE) && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A producers =====================
     const int pw = warp - kFirstProducerWarp;
     uint32_t s = 0, ring_phase = 0;  // ring position and the number of wraps (mod 2)
@@ -588,8 +694,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 1);
     }
     cp_async_wait<0>();  // nothing of this thread is in flight when the CTA winds down
-  } else if ((AMODE == A_CONV_TMA || AMODE == A_CONV_BOX) && warp >= kFirstProducerWarp &&
-             warp < kFirstProducerWarp + 4) {
+  } else if (a_mode_uses_tma(AMODE) && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A copies by TMA =====================
     // One tensor copy brings one K column of one sub-tile (2 KB at most).  Measured: a thread
     // needs ~330 cycles per copy and a warp ~70, so the copies of a stage (column x sub-tile)
@@ -607,7 +712,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // origin of this lane's sub-tile
       int c0 = 0, c1 = 0, c2 = 0;  // BOX: x (8-byte units), y, first image; TMA: w, h, image
       bool sub_ok = true;
-      if constexpr (AMODE == A_CONV_BOX) {
+      if constexpr (AMODE == A_DENSE_TMA) {
+        c0 = (m_tile * MT + t) * kTileM;  // first row of this lane's sub-tile; rows past the end are zero-filled
+      } else if constexpr (AMODE == A_CONV_BOX) {
         long long st = (long long)m_tile * MT + t;
         sub_ok = st < p.sub_tiles;
         if (!sub_ok) st = 0;
@@ -641,9 +748,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const int cpc = (AMODE == A_CONV_BOX) ? 1 : p.cols_per_chunk;
       const int half = jj % cpc;
       int q0 = jj / cpc;  // chunk index along K
-      int kh = q0 / (p.Cc * p.KW);
-      int kw = (q0 / p.Cc) % p.KW;
-      int ci = q0 % p.Cc;
+      int kh = 0, kw = 0, ci = 0;
+      if constexpr (AMODE != A_DENSE_TMA) {
+        kh = q0 / (p.Cc * p.KW);
+        kw = (q0 / p.Cc) % p.KW;
+        ci = q0 % p.Cc;
+      }
       const int chunk_step = p.kc / cpc;
       for (int ks = 0; ks < p.k_stages; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
@@ -657,14 +767,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         __syncwarp();
         if (lane_active && jj < real && (AMODE != A_CONV_BOX || sub_ok)) {
           const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes;
-          if constexpr (AMODE == A_CONV_BOX)
+          if constexpr (AMODE == A_DENSE_TMA)
+            tma_tile_3d(dst, &tmap, 0, ks * p.kc + jj, c0, bar);
+          else if constexpr (AMODE == A_CONV_BOX)
             tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2, bar);
           else
             tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, bar);
         }
         // advance this lane's column by one stage
-        ci += chunk_step;
-        while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; ++kh; } }
+        if constexpr (AMODE != A_DENSE_TMA) {
+          ci += chunk_step;
+          while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; ++kh; } }
+        }
         if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
       }
       if (tx_poster) trace_mark(p, lt, 1);
@@ -694,6 +808,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
   } else if (warp == kMmaWarp) {
     // ===================== MMA issuer =====================
+    // One thread issues; the other lanes of the warp go straight to the final CTA barrier.
+    // (Measured: keeping them parked at a warp-level synchronisation point instead slows the
+    // issuing lane's polling and costs 10-20 % on K-loop-bound layers.)
+    constexpr bool kCanFold = !F16 && EPI != EPI_RAW_ROWS;
+    const uint32_t fold_base = smem_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
+    if constexpr (kCanFold) {
+      uint4 *ac = reinterpret_cast<uint4 *>(smem + (size_t)p.stages * stage_bytes + 2 * kFoldBBytes);
+      for (int i = lane; i < 2 * kTileM; i += 32)  // column 0: bytes {1, 128 x 15} in every row; column 1: zeros
+        ac[i] = i < kTileM ? make_uint4(0x80808001u, 0x80808080u, 0x80808080u, 0x80808080u) : make_uint4(0u, 0u, 0u, 0u);
+      fence_proxy_async();
+      __syncwarp();
+    }
     if (lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn);
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
@@ -707,13 +833,24 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
         const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
         const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
-        if (!mbar_wait(smem_u32(&ps->tempty[slot]), (use & 1u) ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
+        // the drain warps arrive once before the set's first use (bias prepared) and once after every drain
+        if (!mbar_wait(smem_u32(&ps->tempty[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
           alive = false;
           break;
         }
         tc_fence_after();
         trace_mark(p, lt, 3);
         const uint32_t d_tmem = tmem_base + slot * (uint32_t)MT * (uint32_t)p.bn;
+        uint32_t started = 0u;
+        if constexpr (kCanFold) {
+          if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0) {
+            const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
+            const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
+#pragma unroll
+            for (int t = 0; t < MT; ++t) tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, 0u);
+            started = 1u;
+          }
+        }
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, abort_flag, p.err, kErrWaitFull)) {
             alive = false;
@@ -730,20 +867,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
               const uint64_t adesc = a_desc0 | (uint64_t)(a_enc + (uint32_t)t * a_sub_enc + (uint32_t)k * a_step);
-              tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, (ks | k) != 0 ? 1u : 0u);
+              tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, started);
             }
+            started = 1u;
           }
           tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
-        if (alive) tc_commit(smem_u32(&ps->tfull[slot]));  // accumulators complete
+        if (alive) {
+          // Two arrivals complete "accumulators ready": this thread's own (a release that
+          // passes the drain warps' bias integers on to whichever warp reads them) and the commit.
+          mbar_arrive(smem_u32(&ps->tfull[slot]));
+          tc_commit(smem_u32(&ps->tfull[slot]));
+        }
         trace_mark(p, lt, 5);
       }
     }
   } else if (warp < kDrainWarps) {
     // ===================== drain (warps 0-15) =====================
+    constexpr bool kCanFold = !F16 && EPI != EPI_RAW_ROWS;
+    uint8_t *fold_mem = smem + (size_t)p.stages * stage_bytes;
     uint32_t lt = 0;
-    bool alive = true;
     const int ohw = p.OH * p.OW;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
     const int part = warp >> 2;  // 0-3: which sub-tile / share of the column groups
@@ -754,77 +898,56 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int per = (groups + nparts - 1) / nparts;
     const int g_begin = min(cpart * per, groups);
     const int g_end = min(g_begin + per, groups);
-    const int dtid = threadIdx.x;  // 0..511 within the drain warps
-    const bool static_wide = EPI == EPI_REQ_NCHWC && (p.shift > 23 || p.acc_bound >= (1ll << 30));
-    int staged_n0 = -1, staged_n1 = -1;              // column block whose bias each accumulator set holds
-    bool staged_wide0 = false, staged_wide1 = false;  // and whether those columns need the 64-bit path
-    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+    const uint32_t r = (uint32_t)(quad * 32 + lane);  // this thread's row of the sub-tile
+    // box mode: where the row sits inside its box (the same for every tile)
+    uint32_t dn = 0, dh = 0, dw = 0;
+    if constexpr (AMODE == A_CONV_BOX) {
+      dn = fast_div(r, p.div_box_hw);
+      const uint32_t rr = r - dn * (uint32_t)(p.box_h * p.box_w);
+      dh = fast_div(rr, p.div_box_w);
+      dw = rr - dh * (uint32_t)p.box_w;
+    }
+    const long long gstride = (EPI == EPI_RAW_ROWS) ? 16 : (long long)ohw * 16;  // between 16-column groups
+    // Per accumulator set: the column block its bias is prepared for, the verdict, and which of
+    // the two integer buffers holds the values (it flips at every preparation, so that a warp
+    // preparing the next tile never overwrites what a slower warp still reads for this one).
+    int staged_n0 = -1, staged_n1 = -1;
+    bool folded0 = true, folded1 = true, wide0 = false, wide1 = false;
+    uint32_t ver0 = 0, ver1 = 0;
+    // before the first use of each set: prepare its bias, then hand the set to the MMA warp
+    for (uint32_t sl = 0; sl < nslots; ++sl) {
+      const int first = blockIdx.x + (int)sl * (int)gridDim.x;
+      if constexpr (kCanFold) {
+        if (first < total_tiles) {
+          const int nt = first % p.n_tiles;
+          bool f, w;
+          stage_bias<EPI>(p, ps, fold_mem, sl, 0u, nt, warp, lane, f, w);
+          if (sl) { folded1 = f; wide1 = w; staged_n1 = nt; } else { folded0 = f; wide0 = w; staged_n0 = nt; }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[sl]));
+    }
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile % p.n_tiles;
       const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
       const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
-      // Stage this tile's bias values (plus the rounding constant on the 32-bit requantise
-      // path) unless this accumulator set last served the same columns: a CTA's tiles keep or
-      // alternate their column block, so staging happens once or twice per kernel.
-      // Barrier A: every drain warp has left the previous tile, so bias[slot] is free; it also
-      // ORs the per-column "needs 64 bits" tests so that all threads take the same path.
-      // Barrier B (after the wait for the accumulator): publishes the staged values and ORs
-      // the outcome of the bounded wait, so that the drain warps give up together.
-      const int32_t *tile_bias = &ps->bias[slot][0];
-      if constexpr (EPI != EPI_RAW_ROWS) {
-        if ((slot ? staged_n1 : staged_n0) != n_tile) {  // same decision in every drain thread
-          int32_t b = 0;
-          long long br = 0;
-          int need_wide = 0;
-          if (dtid < p.bn) {
-            const int col = n_tile * p.bn + dtid;
-            b = (p.bias != nullptr && col < p.n_total) ? __ldg(p.bias + col) : 0;
-            if constexpr (EPI == EPI_REQ_NCHWC) {
-              br = (long long)b + (1ll << (p.shift - 1));
-              const long long mag = br < 0 ? -br : br;
-              need_wide = (mag + p.acc_bound >= (1ll << 31)) ? 1 : 0;
-            }
-          }
-          if constexpr (EPI == EPI_REQ_NCHWC) {
-            const bool w = drain_barrier_or(need_wide) || static_wide;
-            if (slot) staged_wide1 = w; else staged_wide0 = w;
-            if (dtid < p.bn) ps->bias[slot][dtid] = w ? b : (int32_t)br;
-          } else {
-            drain_barrier_or(0);
-            if (dtid < p.bn) ps->bias[slot][dtid] = b;
-          }
-          if (slot) staged_n1 = n_tile; else staged_n0 = n_tile;
-        }
-      }
-      const bool wide = slot ? staged_wide1 : staged_wide0;
-      const bool got = mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull);
-      if (drain_barrier_or(got ? 0 : 1)) {
-        alive = false;
-        break;
-      }
-      tc_fence_after();
-      if (threadIdx.x == 0) trace_mark(p, lt, 6);
-      const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + quad * 32 + lane;
+      // this row's first stored element (needs nothing of the accumulator, so it comes before the wait)
+      const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + r;
       bool mvalid = m < p.m_total;
-      long long obase = 0;     // element offset of this row's first stored value
-      long long gstride = 16;  // element distance between consecutive 16-column groups
+      long long obase = 0;
       if constexpr (AMODE == A_CONV_BOX) {
-        // sub-tile -> (image block, row block, column block); row -> (image, row, column) inside the box
+        // sub-tile -> (image block, row block, column block)
         const long long st = (long long)m_tile * MT + sub;
-        const uint32_t r = (uint32_t)(quad * 32 + lane);
         const uint32_t stc = st < p.sub_tiles ? (uint32_t)st : 0u;
         const uint32_t q = fast_div(stc, p.div_blocks_w);
         const uint32_t wb = stc - q * (uint32_t)p.blocks_w;
         const uint32_t nb = fast_div(q, p.div_blocks_h);
         const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
-        const uint32_t dn = fast_div(r, p.div_box_hw);
-        const uint32_t rr = r - dn * (uint32_t)(p.box_h * p.box_w);
-        const uint32_t dh = fast_div(rr, p.div_box_w);
-        const uint32_t dw = rr - dh * (uint32_t)p.box_w;
         const int n_i = (int)nb * p.box_n + (int)dn, oh = (int)hb * p.box_h + (int)dh, ow = (int)wb * p.box_w + (int)dw;
         mvalid = st < p.sub_tiles && (int)dn < p.box_n && n_i < p.n_img && oh < p.OH && ow < p.OW;
         obase = (((long long)n_i * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + (long long)oh * p.OW + ow) * 16;
-        gstride = (long long)ohw * 16;
       } else if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
       } else {
@@ -833,26 +956,43 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const long long rem = (long long)mm - n_img * ohw;
         // [n][oc/16][ohw][16]: column group g of this tile adds g * ohw * 16
         obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
-        gstride = (long long)ohw * 16;
       }
+      const bool folded = slot ? folded1 : folded0;
+      const bool wide = slot ? wide1 : wide0;
+      const int32_t *tile_bias = &ps->bias[slot][slot ? ver1 : ver0][0];
+      if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull)) break;
+      tc_fence_after();
+      if (threadIdx.x == 0) trace_mark(p, lt, 6);
       const uint32_t t_row =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
+      const int g_stop = min(g_end, (p.n_total - n_tile * p.bn + 15) >> 4);  // groups that hold real columns
       // software pipeline: the read of group g + 1 is in flight while group g is processed
       uint32_t va[16], vb[16];
-      if (g_begin < g_end) {
+      if (g_begin < g_stop) {
         tmem_ld16(t_row + (uint32_t)g_begin * 16u, va);
         tmem_ld_wait();
       }
-      for (int g = g_begin; g < g_end; g += 2) {
-        const bool has_b = g + 1 < g_end;
+      for (int g = g_begin; g < g_stop; g += 2) {
+        const bool has_b = g + 1 < g_stop;
         if (has_b) tmem_ld16(t_row + (uint32_t)(g + 1) * 16u, vb);
-        if (mvalid && n_tile * p.bn + g * 16 < p.n_total)
-          store_group16<EPI>(p, tile_bias + g * 16, wide, va, obase + g * gstride);
+        if (mvalid) store_group16<EPI>(p, tile_bias + g * 16, folded, wide, va, obase + g * gstride);
         tmem_ld_wait();
-        if (g + 2 < g_end) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
-        if (has_b && mvalid && n_tile * p.bn + (g + 1) * 16 < p.n_total)
-          store_group16<EPI>(p, tile_bias + (g + 1) * 16, wide, vb, obase + (g + 1) * gstride);
+        if (g + 2 < g_stop) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
+        if (has_b && mvalid) store_group16<EPI>(p, tile_bias + (g + 1) * 16, folded, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait();
+      }
+      // prepare the set for the tile that uses it next, unless that tile has the same column block
+      if constexpr (kCanFold) {
+        const int next = tile + (int)nslots * (int)gridDim.x;
+        if (next < total_tiles) {
+          const int nt = next % p.n_tiles;
+          if (nt != (slot ? staged_n1 : staged_n0)) {
+            const uint32_t ver = (slot ? ver1 : ver0) ^ 1u;
+            bool f, w;
+            stage_bias<EPI>(p, ps, fold_mem, slot, ver, nt, warp, lane, f, w);
+            if (slot) { folded1 = f; wide1 = w; staged_n1 = nt; ver1 = ver; } else { folded0 = f; wide0 = w; staged_n0 = nt; ver0 = ver; }
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();

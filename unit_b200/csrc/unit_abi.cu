@@ -77,7 +77,7 @@ static int stages_for(const TileCfg &c, int mt, size_t *smem_bytes) {
   int s = (int)(kSmemBudget / stage);
   if (s > kMaxStages) s = kMaxStages;
   if (s < 2) s = 2;
-  *smem_bytes = (size_t)s * stage + sizeof(PipeShared) + 128;
+  *smem_bytes = (size_t)s * stage + kFoldBytes + sizeof(PipeShared) + 128;
   return s;
 }
 
@@ -358,6 +358,15 @@ __global__ void fold2x2_kernel(const uint2 *__restrict__ src, uint4 *__restrict_
 // ---------------------------------------------------------------------------
 // launches of the contraction kernel
 // ---------------------------------------------------------------------------
+// UNIT_B200_FOLD=0 makes the drain add every bias (for comparison runs); the default lets the tensor core do it.
+static bool use_fold() {
+  static const int v = [] {
+    const char *e = getenv("UNIT_B200_FOLD");
+    return e ? atoi(e) : 1;
+  }();
+  return v != 0;
+}
+
 template <int AMODE, int EPI, bool F16, int MT>
 static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, int sms, const CUtensorMap &tmap) {
   static std::once_flag once[64];
@@ -392,6 +401,7 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const
   void *err_ptr = nullptr;
   if (cudaGetSymbolAddress(&err_ptr, g_error_word) != cudaSuccess) return UNIT_ERR_LAUNCH;
   p.err = static_cast<unsigned int *>(err_ptr);
+  p.fold_bias = use_fold() ? 1 : 0;
   p.trace = g_trace.load();
   p.trace_cap = g_trace_cap.load();
   const int sms = sm_count();
@@ -503,6 +513,33 @@ static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const 
   const cuuint32_t box[4] = {(cuuint32_t)g.bw * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Tiled-mode tensor map over a row-major matrix of `row_bytes` used bytes per row and `ld` bytes
+// between rows, seen as (8-byte half of a K column, K column, row): one copy fetches one 16-byte K
+// column of 128 consecutive rows, which lands in shared memory as that column's core matrices.
+// Rows past the end of the matrix are filled with zeros by the copy engine.
+static bool make_dense_map(CUtensorMap *map, const void *a, long long rows, long long row_bytes, long long ld) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode || ld >= (1ll << 40) || rows > 0x7fffffffll - 512) return false;
+  const cuuint64_t dims[3] = {2, (cuuint64_t)(row_bytes / 16), (cuuint64_t)rows};
+  const cuuint64_t strides[2] = {16, (cuuint64_t)ld};
+  const cuuint32_t box[3] = {2, 1, 128};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(a), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -819,6 +856,9 @@ int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_
   p.a = a; p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
   p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
   p.OH = p.OW = 1;
+  CUtensorMap map;
+  if (use_tma() && make_dense_map(&map, a, m, k, lda))
+    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_DENSE, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream));
 }
 
@@ -851,6 +891,9 @@ int unit_gemm_f16f32(int32_t m, int32_t n, int32_t k, const void *a, int64_t lda
   p.a = static_cast<const uint8_t *>(a); p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
   p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
   p.OH = p.OW = 1;
+  CUtensorMap map;
+  if (use_tma() && make_dense_map(&map, a, m, 2ll * k, lda))
+    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_DENSE, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream));
 }
 
