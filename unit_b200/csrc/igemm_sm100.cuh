@@ -111,6 +111,7 @@ struct IgemmParams {
   int box_n, box_h, box_w, blocks_h, blocks_w, n_img;
   long long sub_tiles;      // number of sub-tiles
   FastDiv div_box_hw, div_box_w, div_blocks_w, div_blocks_h;
+  FastDiv div_n_tiles;      // tile index -> (row block, column block)
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
   int fold_bias;  // 0: the drain always adds the bias (comparison runs)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
@@ -575,7 +576,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t lt = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
-      const int m_tile = tile / p.n_tiles;
+      const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       const long long m0 = (long long)m_tile * (kTileM * MT);
 
       // rows this lane feeds (per sub-tile) and their decoded positions
@@ -708,7 +709,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t lt = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
-      const int m_tile = tile / p.n_tiles;
+      const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       // origin of this lane's sub-tile
       int c0 = 0, c1 = 0, c2 = 0;  // BOX: x (8-byte units), y, first image; TMA: w, h, image
       bool sub_ok = true;
@@ -790,7 +791,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t lt = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
-        const int n_tile = tile % p.n_tiles;
+        const int n_tile = tile - (int)fast_div((uint32_t)tile, p.div_n_tiles) * p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
@@ -919,7 +920,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const int first = blockIdx.x + (int)sl * (int)gridDim.x;
       if constexpr (kCanFold) {
         if (first < total_tiles) {
-          const int nt = first % p.n_tiles;
+          const int nt = first - (int)fast_div((uint32_t)first, p.div_n_tiles) * p.n_tiles;
           bool f, w;
           stage_bias<EPI>(p, ps, fold_mem, sl, 0u, nt, warp, lane, f, w);
           if (sl) { folded1 = f; wide1 = w; staged_n1 = nt; } else { folded0 = f; wide0 = w; staged_n0 = nt; }
@@ -929,8 +930,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[sl]));
     }
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
-      const int m_tile = tile / p.n_tiles;
-      const int n_tile = tile % p.n_tiles;
+      const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
+      const int n_tile = tile - m_tile * p.n_tiles;
       const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
       const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
       // this row's first stored element (needs nothing of the accumulator, so it comes before the wait)
@@ -985,7 +986,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if constexpr (kCanFold) {
         const int next = tile + (int)nslots * (int)gridDim.x;
         if (next < total_tiles) {
-          const int nt = next % p.n_tiles;
+          const int nt = next - (int)fast_div((uint32_t)next, p.div_n_tiles) * p.n_tiles;
           if (nt != (slot ? staged_n1 : staged_n0)) {
             const uint32_t ver = (slot ? ver1 : ver0) ^ 1u;
             bool f, w;

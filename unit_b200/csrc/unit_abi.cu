@@ -388,6 +388,8 @@ static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, in
   return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
 }
 
+static FastDiv make_fast_div(uint32_t d);
+
 template <int AMODE, int EPI, bool F16>
 static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const CUtensorMap *tmap_in = nullptr) {
   static const CUtensorMap no_map{};
@@ -398,6 +400,7 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const
   p.k_stages = c.k_stages;
   p.last_ksteps = c.last_ksteps;
   p.n_tiles = c.n_tiles;
+  p.div_n_tiles = make_fast_div((uint32_t)c.n_tiles);
   void *err_ptr = nullptr;
   if (cudaGetSymbolAddress(&err_ptr, g_error_word) != cudaSuccess) return UNIT_ERR_LAUNCH;
   p.err = static_cast<unsigned int *>(err_ptr);
