@@ -460,7 +460,8 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
 }
 
 // Prepares the bias of one accumulator set's columns for the tile that will use the set next.
-// Called by each drain warp with all lanes; the warps work independently (no CTA barrier).
+// Called with all lanes by each of the `gw` drain warps that serve the set (wl = 0 .. gw-1); the
+// warps work independently (no CTA barrier).
 //
 // Preferred form: bias (plus the rounding constant 2^(shift-1) when requantising) enters the
 // accumulator as one more K step of the MMA.  The A side of that step is a constant block whose
@@ -472,16 +473,17 @@ __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_
 // ps->bias[slot][version] as integers and the drain adds them.
 //
 // Every warp reads all of the block's values to reach the same verdict (folded / wide) by warp
-// votes; warp w then writes channels 16 w .. 16 w + 15.  The writes become visible to the MMA
+// votes; warp wl then writes its 256 / gw channels.  The writes become visible to the MMA
 // warp through this warp's arrival on the set's "empty" barrier.
 template <int EPI>
 __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps, uint8_t *fold_mem, uint32_t slot,
-                                           uint32_t version, int n_tile, int warp, int lane, bool &folded, bool &wide) {
+                                           uint32_t version, int n_tile, int wl, int gw, int lane, bool &folded,
+                                           bool &wide) {
   constexpr bool kReq = EPI == EPI_REQ_NCHWC;
   if (!kReq && p.bias == nullptr) {  // nothing to add at all: the accumulator is final without an extra step
     folded = true;
     wide = false;
-    if (warp == 0 && lane == 0) ps->bias_mma[slot] = 0;
+    if (wl == 0 && lane == 0) ps->bias_mma[slot] = 0;
     return;
   }
   const bool static_wide = kReq && (p.shift > 23 || p.acc_bound >= (1ll << 30));
@@ -502,8 +504,9 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
   }
   fits = __all_sync(0xffffffffu, fits ? 1 : 0) != 0;
   need_wide = __any_sync(0xffffffffu, need_wide ? 1 : 0) != 0;
-  const int ch = warp * 16 + lane;
-  if (lane < 16 && ch < p.bn) {
+  const int per_warp = kBiasSmem / gw;  // 16 or 32 channels
+  const int ch = wl * per_warp + lane;
+  if (lane < per_warp && ch < p.bn) {
     const int32_t b = (p.bias != nullptr && col0 + ch < p.n_total) ? __ldg(p.bias + col0 + ch) : 0;
     if (fits) {
       const int v = b + (int)rnd;
@@ -521,7 +524,7 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
       ps->bias[slot][version][ch] = (kReq && !need_wide) ? (int32_t)((long long)b + rnd) : b;
     }
   }
-  if (warp == 0 && lane == 0) ps->bias_mma[slot] = fits ? 1 : 0;
+  if (wl == 0 && lane == 0) ps->bias_mma[slot] = fits ? 1 : 0;
   fence_proxy_async();  // the digits are read by the tensor core (async proxy)
   folded = fits;
   wide = need_wide;
@@ -553,7 +556,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ps->tfull[i]), 2);             // the issuing thread's arrival + its tcgen05.commit
-      mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps);  // the drain warps
+      mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps / nslots);  // the drain warps that serve the set
     }
     ps->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -886,16 +889,22 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
   } else if (warp < kDrainWarps) {
     // ===================== drain (warps 0-15) =====================
+    // With two accumulator sets the warps split into two groups of eight, one per set: group 0
+    // drains the CTA's even tiles, group 1 the odd ones, each at its own pace, so that one
+    // group's stores overlap the other's per-tile bookkeeping and waiting.  With one set all
+    // sixteen warps drain every tile.
     constexpr bool kCanFold = !F16 && EPI != EPI_RAW_ROWS;
     uint8_t *fold_mem = smem + (size_t)p.stages * stage_bytes;
-    uint32_t lt = 0;
+    const int gw = kDrainWarps / (int)nslots;      // warps per group
+    const uint32_t slot = (uint32_t)(warp / gw);   // the group's accumulator set
+    const int wl = warp % gw;                      // warp within the group
     const int ohw = p.OH * p.OW;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
-    const int part = warp >> 2;  // 0-3: which sub-tile / share of the column groups
+    const int part = wl >> 2;    // which sub-tile / share of the column groups
     const int groups = p.bn >> 4;
-    const int sub = (MT == 2) ? (part >> 1) : 0;
-    const int nparts = (MT == 2) ? 2 : 4;
-    const int cpart = (MT == 2) ? (part & 1) : part;
+    const int nparts = (gw >> 2) / MT;  // warps that share one sub-tile's column groups
+    const int sub = part / nparts;
+    const int cpart = part - sub * nparts;
     const int per = (groups + nparts - 1) / nparts;
     const int g_begin = min(cpart * per, groups);
     const int g_end = min(g_begin + per, groups);
@@ -909,31 +918,28 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       dw = rr - dh * (uint32_t)p.box_w;
     }
     const long long gstride = (EPI == EPI_RAW_ROWS) ? 16 : (long long)ohw * 16;  // between 16-column groups
-    // Per accumulator set: the column block its bias is prepared for, the verdict, and which of
-    // the two integer buffers holds the values (it flips at every preparation, so that a warp
-    // preparing the next tile never overwrites what a slower warp still reads for this one).
-    int staged_n0 = -1, staged_n1 = -1;
-    bool folded0 = true, folded1 = true, wide0 = false, wide1 = false;
-    uint32_t ver0 = 0, ver1 = 0;
-    // before the first use of each set: prepare its bias, then hand the set to the MMA warp
-    for (uint32_t sl = 0; sl < nslots; ++sl) {
-      const int first = blockIdx.x + (int)sl * (int)gridDim.x;
-      if constexpr (kCanFold) {
-        if (first < total_tiles) {
-          const int nt = first - (int)fast_div((uint32_t)first, p.div_n_tiles) * p.n_tiles;
-          bool f, w;
-          stage_bias<EPI>(p, ps, fold_mem, sl, 0u, nt, warp, lane, f, w);
-          if (sl) { folded1 = f; wide1 = w; staged_n1 = nt; } else { folded0 = f; wide0 = w; staged_n0 = nt; }
-        }
+    const int tile_step = (int)nslots * (int)gridDim.x;  // from one tile of this group to its next
+    // The set's bias: the column block it is prepared for, the verdict, and which of the two
+    // integer buffers holds the values (it flips at every preparation, so that a warp preparing
+    // the next tile never overwrites what a slower warp still reads for this one).
+    int staged_n = -1;
+    bool folded = true, wide = false;
+    uint32_t ver = 0;
+    const int first_tile = blockIdx.x + (int)slot * (int)gridDim.x;
+    // before the set's first use: prepare its bias, then hand the set to the MMA warp
+    if constexpr (kCanFold) {
+      if (first_tile < total_tiles) {
+        staged_n = first_tile - (int)fast_div((uint32_t)first_tile, p.div_n_tiles) * p.n_tiles;
+        stage_bias<EPI>(p, ps, fold_mem, slot, ver, staged_n, wl, gw, lane, folded, wide);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[sl]));
     }
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
+    uint32_t use = 0;  // how many tiles this group has drained
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++use) {
+      const uint32_t lt = use * nslots + slot;  // the CTA's tile counter, for the trace
       const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       const int n_tile = tile - m_tile * p.n_tiles;
-      const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
-      const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
       // this row's first stored element (needs nothing of the accumulator, so it comes before the wait)
       const long long m = (long long)m_tile * (kTileM * MT) + sub * kTileM + r;
       bool mvalid = m < p.m_total;
@@ -958,12 +964,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         // [n][oc/16][ohw][16]: column group g of this tile adds g * ohw * 16
         obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
       }
-      const bool folded = slot ? folded1 : folded0;
-      const bool wide = slot ? wide1 : wide0;
-      const int32_t *tile_bias = &ps->bias[slot][slot ? ver1 : ver0][0];
+      const int32_t *tile_bias = &ps->bias[slot][ver][0];
       if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull)) break;
       tc_fence_after();
-      if (threadIdx.x == 0) trace_mark(p, lt, 6);
+      if (wl == 0 && lane == 0) trace_mark(p, lt, 6);
       const uint32_t t_row =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
       const int g_stop = min(g_end, (p.n_total - n_tile * p.bn + 15) >> 4);  // groups that hold real columns
@@ -982,22 +986,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (has_b && mvalid) store_group16<EPI>(p, tile_bias + (g + 1) * 16, folded, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait();
       }
-      // prepare the set for the tile that uses it next, unless that tile has the same column block
+      // prepare the set for the group's next tile, unless that tile has the same column block
       if constexpr (kCanFold) {
-        const int next = tile + (int)nslots * (int)gridDim.x;
+        const int next = tile + tile_step;
         if (next < total_tiles) {
           const int nt = next - (int)fast_div((uint32_t)next, p.div_n_tiles) * p.n_tiles;
-          if (nt != (slot ? staged_n1 : staged_n0)) {
-            const uint32_t ver = (slot ? ver1 : ver0) ^ 1u;
-            bool f, w;
-            stage_bias<EPI>(p, ps, fold_mem, slot, ver, nt, warp, lane, f, w);
-            if (slot) { folded1 = f; wide1 = w; staged_n1 = nt; ver1 = ver; } else { folded0 = f; wide0 = w; staged_n0 = nt; ver0 = ver; }
+          if (nt != staged_n) {
+            ver ^= 1u;
+            stage_bias<EPI>(p, ps, fold_mem, slot, ver, nt, wl, gw, lane, folded, wide);
+            staged_n = nt;
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (threadIdx.x == 0) trace_mark(p, lt, 7);
+      if (wl == 0 && lane == 0) trace_mark(p, lt, 7);
       if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
     }
   }
