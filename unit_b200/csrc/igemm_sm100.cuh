@@ -337,13 +337,9 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Tile trace: CTA 0 records when each role passes a point of tile `lt` (slots 0-7), and how
-// long the MMA thread (slot 8) and the first A producer warp (slot 9) waited for the ring.
+// Tile trace: CTA 0 records when each role passes a point of tile `lt` (slot 0-7).
 __device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, int slot) {
   if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 16u + slot] = (unsigned long long)clock64();
-}
-__device__ __forceinline__ void trace_value(const IgemmParams &p, uint32_t lt, int slot, unsigned long long v) {
-  if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 16u + slot] = v;
 }
 
 // Shared-memory matrix descriptor, K-major, no swizzle.
@@ -763,14 +759,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         ci = q0 % p.Cc;
       }
       const int chunk_step = p.kc / cpc;
-      unsigned long long waited = 0;  // cycles spent waiting for free stages (trace only)
       for (int ks = 0; ks < p.k_stages; ++ks) {
-        const long long w0 = p.trace != nullptr ? clock64() : 0;
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
           alive = false;
           break;
         }
-        if (p.trace != nullptr) waited += (unsigned long long)(clock64() - w0);
         const uint32_t bar = smem_u32(&ps->full[s]);
         int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
         real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
@@ -792,7 +785,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         }
         if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
       }
-      if (tx_poster) { trace_mark(p, lt, 1); trace_value(p, lt, 9, waited); }
+      if (tx_poster) trace_mark(p, lt, 1);
     }
   } else if (warp == kBWarp) {
     // ===================== B producer =====================
@@ -862,14 +855,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             started = 1u;
           }
         }
-        unsigned long long waited = 0;  // cycles spent waiting for operands (trace only)
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          const long long w0 = p.trace != nullptr ? clock64() : 0;
           if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, abort_flag, p.err, kErrWaitFull)) {
             alive = false;
             break;
           }
-          if (p.trace != nullptr) waited += (unsigned long long)(clock64() - w0);
           tc_fence_after();
           if (ks == 0) trace_mark(p, lt, 4);
           // descriptors differ only in the start-address field (address >> 4, 14 bits)
@@ -895,7 +885,6 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           tc_commit(smem_u32(&ps->tfull[slot]));
         }
         trace_mark(p, lt, 5);
-        trace_value(p, lt, 8, waited);
       }
     }
   } else if (warp < kDrainWarps) {
