@@ -200,6 +200,21 @@ def test_stem_stride2_geometries(U, oracle, hw, k, p):
     assert np.array_equal(gotq.cpu().numpy(), oracle.conv2d_u8s8(x, w, (2, 2), (p, p), bias=b, requant_shift=8))
 
 
+@pytest.mark.parametrize('h,w,k,p', [(12, 224, 7, 3), (10, 250, 7, 3), (14, 132, 3, 1), (8, 200, 4, 1), (6, 248, 8, 3)])
+def test_stem_wide_rows_one_copy_per_kernel_row(U, oracle, h, w, k, p):
+    """Folded stride-2 convolutions whose output rows fill a 128-row sub-tile on their own: the taps
+    of a kernel row are fetched with one copy and addressed as shifted windows."""
+    rng = np.random.default_rng(h * 1000 + w + k)
+    x = rng.integers(0, 256, (2, 1, h, w, 4), dtype=np.uint8)
+    wt = rng.integers(-128, 128, (4, 1, k, k, 1, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 15, 2 ** 15, 64, dtype=np.int32)
+    got = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=2, padding=p)
+    gotq = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=2, padding=p, bias=dev(b), out_dtype='uint8')
+    U.device_status()
+    assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (2, 2), (p, p)))
+    assert np.array_equal(gotq.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (2, 2), (p, p), bias=b, requant_shift=8))
+
+
 def test_stem_without_workspace_through_the_c_abi(U, oracle):
     """The same stem with d_workspace = NULL: the library falls back to the in-place gather."""
     import ctypes

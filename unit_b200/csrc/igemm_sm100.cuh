@@ -24,7 +24,7 @@
 // A CTA tile is MT x 128 rows by BN columns (MT = 1 or 2): with MT = 2 one B
 // stage feeds two accumulators, which halves the weight bytes fetched per MAC.
 //
-// Warp roles (704 threads):
+// Warp roles (736 threads):
 //   warps 0-15  drain: tcgen05.ld the finished accumulator (warp w may touch
 //               TMEM lanes 32(w%4)..+31 = tile rows), apply the epilogue, store;
 //               the four warps of a lane quadrant split the sub-tiles and the
@@ -34,7 +34,9 @@
 //               thread's copies arrive on the stage barrier by themselves
 //               (cp.async.mbarrier.arrive.noinc), so no producer waits for data
 //   warp  20    B producer: one lane issues the bulk copies
-//   warp  21    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit
+//   warp  21    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit for sub-tile 0
+//   warp  22    (MT = 2) one lane issues them for sub-tile 1: a single thread cannot issue
+//               MMAs fast enough to keep the tensor core busy on narrow column blocks
 // When two accumulator sets fit in the 512 TMEM columns, the drain of tile i
 // overlaps the main loop of tile i+1.
 //
@@ -67,8 +69,8 @@ enum EpiMode : int {
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 12;
-constexpr int kNumThreads = 704;
-constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21;
+constexpr int kNumThreads = 736;
+constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21, kMmaWarp2 = 22;
 constexpr uint32_t kFoldBBytes = 4096;  // one accumulator set's bias digits: 256 channels x 16 bytes
 constexpr uint32_t kFoldBytes = 2 * kFoldBBytes + 2 * 128 * 16;  // two sets + the constant A block (2 columns)
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
@@ -111,6 +113,13 @@ struct IgemmParams {
   int box_n, box_h, box_w, blocks_h, blocks_w, n_img;
   long long sub_tiles;      // number of sub-tiles
   FastDiv div_box_hw, div_box_w, div_blocks_w, div_blocks_h;
+  // Row form of A_CONV_BOX (row_kw > 0): a sub-tile is one row segment of one image and one
+  // channel chunk, so the KW taps of a kernel row are the same pixels shifted by 16 bytes each.
+  // One copy of box_w + KW - 1 pixels then serves all KW columns of that kernel row: the MMA
+  // reads column (kh, kw) at the row buffer's address + 16 kw, and the two columns of a K step
+  // are 16 bytes apart (overlapping core matrices).
+  int row_kw;     // 0, or KW (even) when the row form is in use
+  int row_bytes;  // bytes one row copy delivers: (box_w + KW - 1) * 16
   FastDiv div_n_tiles;      // tile index -> (row block, column block)
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
   int fold_bias;  // 0: the drain always adds the bias (comparison runs)
@@ -552,10 +561,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     for (int s = 0; s < p.stages; ++s) {
       // 128 A-producer threads + the B producer; with TMA-fed A only the thread that issues all copies
       mbar_init(smem_u32(&ps->full[s]), a_mode_uses_tma(AMODE) ? 2 : 128 + 1);
-      mbar_init(smem_u32(&ps->empty[s]), 1);       // one tcgen05.commit
+      mbar_init(smem_u32(&ps->empty[s]), MT);      // one tcgen05.commit per MMA-issuing thread
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ps->tfull[i]), 2);             // the issuing thread's arrival + its tcgen05.commit
+      mbar_init(smem_u32(&ps->tfull[i]), 1 + MT);        // the first issuing thread's arrival + one commit per issuer
       mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps / nslots);  // the drain warps that serve the set
     }
     ps->abort_flag = 0;
@@ -564,6 +573,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&ps->tmem_base), 512);
     tmem_relinquish();
+    if constexpr (!F16 && EPI != EPI_RAW_ROWS) {
+      // the constant A block of the bias step: column 0 = bytes {1, 128 x 15} in every row, column 1 = zeros
+      uint4 *ac = reinterpret_cast<uint4 *>(smem + (size_t)p.stages * stage_bytes + 2 * kFoldBBytes);
+      for (int i = lane; i < 2 * kTileM; i += 32)
+        ac[i] = i < kTileM ? make_uint4(0x80808001u, 0x80808080u, 0x80808080u, 0x80808080u) : make_uint4(0u, 0u, 0u, 0u);
+      fence_proxy_async();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -759,6 +775,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         ci = q0 % p.Cc;
       }
       const int chunk_step = p.kc / cpc;
+      // row form: jj counts kernel rows of the stage, each copied once into the slot of its first column
+      const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
+      const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
       for (int ks = 0; ks < p.k_stages; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
           alive = false;
@@ -767,16 +786,26 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t bar = smem_u32(&ps->full[s]);
         int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
         real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
-        if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(real * nsub) * copy_bytes);
-        __syncwarp();
-        if (lane_active && jj < real && (AMODE != A_CONV_BOX || sub_ok)) {
-          const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes;
-          if constexpr (AMODE == A_DENSE_TMA)
-            tma_tile_3d(dst, &tmap, 0, ks * p.kc + jj, c0, bar);
-          else if constexpr (AMODE == A_CONV_BOX)
-            tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2, bar);
-          else
-            tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, bar);
+        if (row_form) {
+          if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(rows_per_stage * nsub) * (uint32_t)p.row_bytes);
+          __syncwarp();
+          if (jj < rows_per_stage && sub_ok) {
+            const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes +
+                                 (uint32_t)(jj * p.row_kw) * kSubBytes;
+            tma_tile_4d(dst, &tmap, c0, c1 + ks * rows_per_stage + jj, 0, c2, bar);
+          }
+        } else {
+          if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(real * nsub) * copy_bytes);
+          __syncwarp();
+          if (lane_active && jj < real && (AMODE != A_CONV_BOX || sub_ok)) {
+            const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes;
+            if constexpr (AMODE == A_DENSE_TMA)
+              tma_tile_3d(dst, &tmap, 0, ks * p.kc + jj, c0, bar);
+            else if constexpr (AMODE == A_CONV_BOX)
+              tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2, bar);
+            else
+              tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, bar);
+          }
         }
         // advance this lane's column by one stage
         if constexpr (AMODE != A_DENSE_TMA) {
@@ -810,23 +839,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         trace_mark(p, lt, 2);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ===================== MMA issuer =====================
-    // One thread issues; the other lanes of the warp go straight to the final CTA barrier.
+  } else if (warp == kMmaWarp || (MT == 2 && warp == kMmaWarp2)) {
+    // ===================== MMA issuers =====================
+    // One thread per sub-tile issues that sub-tile's MMAs (measured: a thread cannot issue
+    // tcgen05.mma faster than one per ~80 cycles, which starves the tensor core on narrow column
+    // blocks: a 128 x 64 x 32 MMA is 32 cycles of math; two threads in different warps issue
+    // independently).  The other lanes of these warps go straight to the final CTA barrier.
     // (Measured: keeping them parked at a warp-level synchronisation point instead slows the
     // issuing lane's polling and costs 10-20 % on K-loop-bound layers.)
     constexpr bool kCanFold = !F16 && EPI != EPI_RAW_ROWS;
     const uint32_t fold_base = smem_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
-    if constexpr (kCanFold) {
-      uint4 *ac = reinterpret_cast<uint4 *>(smem + (size_t)p.stages * stage_bytes + 2 * kFoldBBytes);
-      for (int i = lane; i < 2 * kTileM; i += 32)  // column 0: bytes {1, 128 x 15} in every row; column 1: zeros
-        ac[i] = i < kTileM ? make_uint4(0x80808001u, 0x80808080u, 0x80808080u, 0x80808080u) : make_uint4(0u, 0u, 0u, 0u);
-      fence_proxy_async();
-      __syncwarp();
-    }
+    const uint32_t my_t = warp == kMmaWarp ? 0u : 1u;  // the sub-tile this thread issues for
     if (lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn);
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
+      const uint64_t a_desc_row = make_smem_desc(0u, 16u, 128u);  // row form: K columns 16 bytes apart
       const uint64_t b_desc0 = make_smem_desc(0u, (uint32_t)p.bn * 16u, 128u);
       const uint32_t a_step = (2u * kSubBytes) >> 4;               // one MMA K-step = two 16-byte columns
       const uint32_t b_step = (2u * (uint32_t)p.bn * 16u) >> 4;
@@ -843,15 +870,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           break;
         }
         tc_fence_after();
-        trace_mark(p, lt, 3);
-        const uint32_t d_tmem = tmem_base + slot * (uint32_t)MT * (uint32_t)p.bn;
+        if (my_t == 0u) trace_mark(p, lt, 3);
+        const uint32_t d_tmem = tmem_base + (slot * (uint32_t)MT + my_t) * (uint32_t)p.bn;  // this thread's accumulator
         uint32_t started = 0u;
         if constexpr (kCanFold) {
           if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0) {
             const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
             const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
-#pragma unroll
-            for (int t = 0; t < MT; ++t) tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, 0u);
+            tc_mma<F16>(d_tmem, adesc, bdesc, idesc, 0u);
             started = 1u;
           }
         }
@@ -861,30 +887,41 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             break;
           }
           tc_fence_after();
-          if (ks == 0) trace_mark(p, lt, 4);
+          if (ks == 0 && my_t == 0u) trace_mark(p, lt, 4);
           // descriptors differ only in the start-address field (address >> 4, 14 bits)
-          const uint32_t a_enc = (smem_base + s * stage_bytes) >> 4;
-          const uint32_t b_enc = a_enc + (a_stage_bytes >> 4);
+          const uint32_t stage_enc = (smem_base + s * stage_bytes) >> 4;
+          const uint32_t a_enc = stage_enc + my_t * a_sub_enc;  // this thread's sub-tile of the stage
+          const uint32_t b_enc = stage_enc + (a_stage_bytes >> 4);
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
-          for (int k = 0; k < nk; ++k) {
-            const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
-#pragma unroll
-            for (int t = 0; t < MT; ++t) {
-              const uint64_t adesc = a_desc0 | (uint64_t)(a_enc + (uint32_t)t * a_sub_enc + (uint32_t)k * a_step);
-              tc_mma<F16>(d_tmem + (uint32_t)t * (uint32_t)p.bn, adesc, bdesc, idesc, started);
+          if (AMODE == A_CONV_BOX && p.row_kw > 0) {
+            // row form: the columns of a kernel row share one row buffer, 16 bytes apart
+            uint32_t a_row = a_enc;  // row buffer of the current kernel row (encoded address)
+            int pr = 0;              // pair of columns within the row
+            for (int k = 0; k < nk; ++k) {
+              const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
+              const uint64_t adesc = a_desc_row | (uint64_t)(a_row + (uint32_t)pr * 2u);
+              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              started = 1u;
+              if (++pr == (p.row_kw >> 1)) { pr = 0; a_row += ((uint32_t)p.row_kw * kSubBytes) >> 4; }
             }
-            started = 1u;
+          } else {
+            for (int k = 0; k < nk; ++k) {
+              const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
+              const uint64_t adesc = a_desc0 | (uint64_t)(a_enc + (uint32_t)k * a_step);
+              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              started = 1u;
+            }
           }
           tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
         if (alive) {
-          // Two arrivals complete "accumulators ready": this thread's own (a release that
-          // passes the drain warps' bias integers on to whichever warp reads them) and the commit.
-          mbar_arrive(smem_u32(&ps->tfull[slot]));
+          // "accumulators ready" completes with every issuer's commit plus one plain arrival (a
+          // release that passes the drain warps' bias integers on to whichever warp reads them)
+          if (my_t == 0u) mbar_arrive(smem_u32(&ps->tfull[slot]));
           tc_commit(smem_u32(&ps->tfull[slot]));
         }
-        trace_mark(p, lt, 5);
+        if (my_t == 0u) trace_mark(p, lt, 5);
       }
     }
   } else if (warp < kDrainWarps) {

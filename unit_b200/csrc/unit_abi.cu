@@ -358,6 +358,15 @@ __global__ void fold2x2_kernel(const uint2 *__restrict__ src, uint4 *__restrict_
 // ---------------------------------------------------------------------------
 // launches of the contraction kernel
 // ---------------------------------------------------------------------------
+// UNIT_B200_ROW=0 keeps one copy per tap for the folded stem (for comparison runs).
+static bool use_row_form() {
+  static const int v = [] {
+    const char *e = getenv("UNIT_B200_ROW");
+    return e ? atoi(e) : 1;
+  }();
+  return v != 0;
+}
+
 // UNIT_B200_FOLD=0 makes the drain add every bias (for comparison runs); the default lets the tensor core do it.
 static bool use_fold() {
   static const int v = [] {
@@ -496,7 +505,8 @@ static BoxGeom choose_box(int n, int oh, int ow) {
 // Tiled-mode tensor map over u8 NCHW16c activations seen as (8-byte units of a pixel row, image
 // row, channel chunk, image): one copy fetches box_n x box_h row segments of box_w pixels, and
 // out-of-range coordinates (the zero padding) are filled with zeros by the copy engine.
-static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g) {
+static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g,
+                         int extra_w = 0) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -513,7 +523,7 @@ static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const 
   const cuuint64_t dims[4] = {(cuuint64_t)w * 2, (cuuint64_t)h, cc, (cuuint64_t)n};
   const cuuint64_t row = (cuuint64_t)w * 16;
   const cuuint64_t strides[3] = {row, row * h, row * h * cc};
-  const cuuint32_t box[4] = {(cuuint32_t)g.bw * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
+  const cuuint32_t box[4] = {(cuuint32_t)(g.bw + extra_w) * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(x), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -637,8 +647,15 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
     q.H = f.h2; q.W = f.w2; q.Cc = 1; q.KH = f.th; q.KW = f.tw; q.sh = q.sw = 1; q.ph = f.pad_h; q.pw = f.pad_w;
     q.img_bytes = (long long)f.h2 * f.w2 * 16;
     const BoxGeom g = choose_box(d->n, q.OH, q.OW);
-    if (make_box_map(&map, d->n, 16, f.h2, f.w2, workspace, g)) {
+    // row form (one copy per kernel row instead of one per tap) when a sub-tile is a single row
+    // segment, the kernel width is even (column pairs stay inside a kernel row) and the stages
+    // hold whole kernel rows
+    const bool row_form = use_row_form() && g.bn == 1 && g.bh == 1 && f.tw % 2 == 0 && cf.kc % f.tw == 0 &&
+                          cf.cols % cf.kc == 0 && (g.bw + f.tw - 1) * 2 <= 256;
+    if (make_box_map(&map, d->n, 16, f.h2, f.w2, workspace, g, row_form ? f.tw - 1 : 0)) {
       set_box(q, g, d->n);
+      q.row_kw = row_form ? f.tw : 0;
+      q.row_bytes = (g.bw + f.tw - 1) * 16;
       return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(q, cf, st, &map)
                      : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(q, cf, st, &map);
     }
