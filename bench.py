@@ -169,17 +169,54 @@ def run_reference(args):
     return 0
 
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the two layers captured
-# with `ncu --set full` at batch 256 on one GPU; the summaries under profiles/ give the commands.
-NCU_TRAFFIC_B256 = {'s1_1x1_64_256': 51.46e6 + 147.64e6, 's3_3x3_256_256': 13.48e6 + 0.0}
+# DRAM traffic per launch, (dram__bytes_read.sum, dram__bytes_write.sum), of every layer shape at
+# batch 256 on one GPU: one `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum,gpu__time_duration.sum
+# --clock-control none -k regex:igemm -s <3 x count> -c 1 python bench.py --layer <name> --steps 1
+# --warmup 3 --kernels-only` per layer (profiles/igemm_resnet50_dram_traffic_b256.md).  Writes still
+# in L2 when the kernel ends are not in the write figure.
+NCU_DRAM_B256 = {
+    'stem_7x7s2_3_64': (51.48e6, 147.61e6),
+    's1_1x1_64_64': (51.44e6, 8.61e6),
+    's1_1x1_256_64': (205.61e6, 31.44e6),
+    's1_3x3_64_64': (51.48e6, 10.88e6),
+    's1_1x1_64_256': (51.46e6, 144.63e6),
+    's1_proj_64_256': (51.46e6, 144.88e6),
+    's2_1x1_256_128': (205.62e6, 65.81e6),
+    's2_3x3s2_128_128': (102.97e6, 9.61e6),
+    's2_1x1_512_128': (102.89e6, 6.13e6),
+    's2_3x3_128_128': (25.90e6, 0.0),
+    's2_1x1_128_512': (25.82e6, 42.98e6),
+    's2_proj_s2_256_512': (102.95e6, 53.64e6),
+    's3_1x1_512_256': (102.95e6, 21.19e6),
+    's3_3x3s2_256_256': (52.03e6, 0.33e6),
+    's3_1x1_1024_256': (51.70e6, 0.36e6),
+    's3_3x3_256_256': (13.49e6, 0.0),
+    's3_1x1_256_1024': (13.17e6, 1.00e6),
+    's3_proj_s2_512_1024': (59.31e6, 11.33e6),
+    's4_1x1_1024_512': (51.97e6, 1.43e6),
+    's4_3x3s2_512_512': (28.11e6, 0.0),
+    's4_1x1_2048_512': (26.80e6, 0.0),
+    's4_3x3_512_512': (8.84e6, 0.0),
+    's4_1x1_512_2048': (7.54e6, 0.0),
+    's4_proj_s2_1024_2048': (38.86e6, 0.50e6),
+}
+ROOFLINE_SAMPLE_LAYERS = ('s1_1x1_64_256', 's3_3x3_256_256')  # the two layers with full ncu captures
+
+
+def ncu_traffic(name, batch):
+    """DRAM bytes of one launch from the ncu capture (only valid at the captured batch)."""
+    if batch != TOTAL_BATCH or name not in NCU_DRAM_B256:
+        return None
+    r, w = NCU_DRAM_B256[name]
+    return r + w
 
 
 def roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak):
-    """Roofline objects of the captured layers: achieved from this run's per-layer timing."""
+    """Roofline objects of the fully captured layers: achieved from this run's per-layer timing."""
     out = []
     by_name = {r['layer']: r for r in layer_rows}
     for l in layer_set:
-        if l.name not in NCU_TRAFFIC_B256 or l.name not in by_name:
+        if l.name not in ROOFLINE_SAMPLE_LAYERS or l.name not in by_name:
             continue
         r = by_name[l.name]
         us = r['us']
@@ -188,10 +225,27 @@ def roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak):
         else:
             achieved, peak, unit = l.ops(batch) / us / 1e6, int8_peak, 'TOPS'
         out.append({'layer': l.name, 'bound': r['bound'], 'achieved': achieved, 'peak': peak, 'unit': unit,
-                    'frac': achieved / peak,
-                    'traffic': NCU_TRAFFIC_B256[l.name] if batch == TOTAL_BATCH else None,
+                    'frac': achieved / peak, 'traffic': ncu_traffic(l.name, batch),
                     'algorithmic_bytes': l.bytes(batch)})
     return out
+
+
+def write_only_bandwidth(torch, dev):
+    """GB/s of a plain fill of 1 GiB, measured live: the ceiling for the share of a layer's bytes that are
+    writes (a copy, the roofline's denominator, moves half its bytes each way)."""
+    buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        buf.fill_(1)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(10):
+        buf.fill_(2)
+    b.record()
+    torch.cuda.synchronize()
+    gbs = buf.numel() * 10 / (a.elapsed_time(b) * 1e-3) / 1e9
+    del buf
+    return gbs
 
 
 # ---------------------------------------------------------------------------
@@ -303,6 +357,7 @@ def run_unit(args):
     # ---- per-layer timing (explains the number; not part of `value`)
     peaks = _peaks()
     int8_peak = 2.0 * peaks['bf16_sustained']
+    write_gbs = write_only_bandwidth(torch, dev) if not args.kernels_only else float(peaks['hbm_gbs'])
     layer_rows = []
     sum_kernel_ms = 0.0
     sum_roof_ms = 0.0
@@ -326,9 +381,12 @@ def run_unit(args):
         roof = max(t_tensor, t_hbm)
         sum_kernel_ms += ms * len(idxs)
         sum_roof_ms += roof * len(idxs)
+        out_bytes = float(batch) * l.c_out * l.out_hw * l.out_hw
+        t_write = out_bytes / (write_gbs * 1e9) * 1e3  # the output alone, at the measured write-only rate
         layer_rows.append({'layer': l.name, 'count': l.count, 'us': round(ms * 1e3, 2),
                            'tops': round(ops / ms / 1e9, 1), 'gbs': round(byts / ms / 1e6, 1), 'bound': bound,
-                           'frac': round(roof / ms, 3)})
+                           'frac': round(roof / ms, 3), 'frac_with_write_floor': round(max(roof, t_write) / ms, 3),
+                           'traffic': ncu_traffic(l.name, batch), 'algorithmic_bytes': byts})
     if args.kernels_only:
         sum_kernel_ms, sum_roof_ms = ms_step, None
     kernel_tops = total_ops / world / (sum_kernel_ms * 1e-3) / 1e12
@@ -396,13 +454,17 @@ def run_unit(args):
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': gpu_launches,
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
-                         'frac': kernel_tops / int8_peak, 'traffic': None,
+                         'frac': kernel_tops / int8_peak,
+                         'traffic': (sum(ncu_traffic(l.name, batch) * l.count for l in layer_set) / sum(l.count for l in layer_set))
+                         if batch == TOTAL_BATCH else None,
                          'peak_source': f'2 x bf16_tflops_sustained of {peaks["source"]} peaks '
                                         '(dense int8 issues at twice the bf16 rate)',
                          'kernel': 'igemm_kernel<A_CONV_BOX|A_CONV_TMA, EPI_REQ_NCHWC, i8> over the contraction launches '
                                    'of one step (2 x ops / summed per-layer launch time, CUDA events)',
-                         'traffic_note': 'the launches are 24 different layers; DRAM traffic from ncu is given per '
-                                         'captured layer in roofline_samples',
+                         'traffic_note': 'mean DRAM bytes per launch over the 53 launches of a step (ncu, one capture per '
+                                         'layer shape at batch 256; per layer in `layers`); algorithmic mean %.1f MB'
+                                         % (sum(l.bytes(batch) * l.count for l in layer_set) / sum(l.count for l in layer_set) / 1e6),
+                         'hbm_write_only_gbs': write_gbs,
                          'mixed_bound_frac': (sum_roof_ms / sum_kernel_ms) if sum_roof_ms else None,
                          'hbm_peak_gbs': peaks['hbm_gbs']},
             'roofline_samples': roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak),
