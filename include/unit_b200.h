@@ -85,7 +85,9 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 /* Replaces: the reference hands its packed weight array straight to the
  * generated kernel (apps/cpu/kernel/conv2d.py:26,30).  Source layout
  * [c_out/16][c_in/c_block][kh][kw][c_block/4][16][4] s8.  The packed form depends on
- * c_in, c_block, c_out, kh, kw and, for c_block == 4, on the strides and padding too. */
+ * c_in, c_block, c_out, kh, kw and the strides (the column-block width is chosen per stride) and,
+ * for c_block == 4, on the padding too: pack with the descriptor fields the convolution will use
+ * (n, h and w may differ). */
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *desc);
 int unit_pack_weights_conv_i8(const unit_conv_desc *desc, const int8_t *d_w,
                               void *d_packed, void *stream);

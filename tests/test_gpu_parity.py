@@ -402,7 +402,7 @@ def test_batch_split_equals_whole_batch(U):
     l = R.LAYERS[9]
     x, w, b = R.make_layer_inputs(l, 9, 24, config=5)
     xd, bd = dev(x), dev(b)
-    pw = U.pack_conv_weights_int8(dev(w))
+    pw = U.pack_conv_weights_int8(dev(w), l.stride, l.pad)
     whole = U.conv2d_NCHWc_int8(xd, pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
     for world in (2, 8):
         parts = [U.conv2d_NCHWc_int8(shard(xd, r, world), pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
@@ -418,7 +418,7 @@ def test_large_batch_property_config5(U, oracle):
         l = R.LAYERS[li]
         x, w, b = R.make_layer_inputs(l, li, 256, config=5)
         xd, bd = dev(x), dev(b)
-        pw = U.pack_conv_weights_int8(dev(w))
+        pw = U.pack_conv_weights_int8(dev(w), l.stride, l.pad)
         got = U.conv2d_NCHWc_int8(xd, pw, stride=l.stride, padding=l.pad, bias=bd, out_dtype='uint8')
         U.device_status()
         sample = [0, 100, 255]

@@ -39,11 +39,25 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // Depends on the weight tensor only (never on the batch), so packed weights stay valid
 // for every input size.  kc is chosen so that four stages of the larger (two sub-tile)
 // CTA tile fit in shared memory.
-static TileCfg make_cfg(int n_total, int cols) {
+static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
   TileCfg c;
   c.cols = cols;
   c.cols_pad = round_up(cols, 2);
-  c.n_tiles = (n_total + 255) / 256;
+  // Widest column block.  256 columns x two sub-tiles fill TMEM with one accumulator set, so
+  // each tile's drain (about 2.7 k cycles) is exposed; that is paid back by the halved weight
+  // traffic only when the reduction is long.  Measured at batch 256: reductions of 256..1024
+  // bytes (16..64 columns) run 8-13 % faster with 128-wide blocks (two sets, drain overlapped),
+  // longer ones 15-50 % slower.  UNIT_B200_BN overrides (experiments).
+  static const int forced_bn = [] {
+    const char *e = getenv("UNIT_B200_BN");
+    const int v = e ? atoi(e) : 0;
+    return (v >= 16 && v <= 256 && v % 16 == 0) ? v : 0;
+  }();
+  // (cheap_a = false: the A operand comes through the slower im2col copies, where fetching it
+  // once more per extra column block costs more than the overlap gains: stride-2 layers lost 35-45 %)
+  const int bn_max = forced_bn ? forced_bn
+                               : ((cheap_a && n_total >= 256 && c.cols_pad >= 16 && c.cols_pad <= 64) ? 128 : 256);
+  c.n_tiles = (n_total + bn_max - 1) / bn_max;
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
   const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
   static const int cand[] = {8, 6, 4, 12, 10, 14, 16};
@@ -85,6 +99,8 @@ static int conv_cols_i8(const unit_conv_desc *d) {
   if (d->c_block == 16) return d->kh * d->kw * (d->c_in / 16);
   return (d->c_in / 4) * d->kh * ((d->kw + 3) / 4);
 }
+// stride-1 NCHW16c int8 convolutions fetch A with whole-row box copies
+static bool conv_a_is_cheap(const unit_conv_desc *d) { return d->c_block == 16 && d->stride_h == 1 && d->stride_w == 1; }
 static int conv_cols_f16(const unit_conv_desc *d) { return d->kh * d->kw * (d->c_in / 16) * 2; }
 
 static int check_conv(const unit_conv_desc *d, bool f16) {
@@ -607,7 +623,7 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
     return UNIT_ERR_ALIGN;
   if (requant && (shift < 1 || shift > 31)) return UNIT_ERR_SHAPE;
   if ((rc = check_arch())) return rc;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
   IgemmParams p{};
   p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
   fill_conv(p, d, 1);
@@ -730,7 +746,7 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles) {
 // ---- packed weights --------------------------------------------------------
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
   if (check_conv(d, false)) return 0;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
   size_t bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
   const StemFold f = stem_fold(d, false);
   if (f.ok) {  // second copy for the folded stride-1 form of a stride-2 stem
@@ -750,7 +766,7 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
   if (rc) return rc;
   if (!w || !packed) return UNIT_ERR_NULL;
   if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
   PackParams pp{};
   pp.src = reinterpret_cast<const uint8_t *>(w);
   pp.dst = static_cast<uint4 *>(packed);
@@ -774,7 +790,7 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
 
 size_t unit_packed_weights_bytes_conv_f16(const unit_conv_desc *d) {
   if (check_conv(d, true)) return 0;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d), false);
   return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
 }
 
@@ -783,7 +799,7 @@ int unit_pack_weights_conv_f16(const unit_conv_desc *d, const void *w, void *pac
   if (rc) return rc;
   if (!w || !packed) return UNIT_ERR_NULL;
   if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d), false);
   PackParams pp{};
   pp.src = static_cast<const uint8_t *>(w);
   pp.dst = static_cast<uint4 *>(packed);
@@ -888,7 +904,7 @@ int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const voi
   if (!x || !pw || !out) return UNIT_ERR_NULL;
   if (!aligned16(x) || !aligned16(pw) || !aligned16(out)) return UNIT_ERR_ALIGN;
   if ((rc = check_arch())) return rc;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d));
+  const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d), false);
   IgemmParams p{};
   p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out;
   fill_conv(p, d, 2);

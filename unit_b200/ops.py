@@ -115,8 +115,8 @@ def _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, pad) -> ConvDesc:
 def pack_conv_weights_int8(kernel: torch.Tensor, stride: IntPair = 1, padding: IntPair = 0) -> PackedWeights:
     """kernel: s8 ``[O/16][I/cb][KH][KW][cb/4][16][4]`` (apps/cpu/kernel/conv2d.py:26,30).
 
-    For NCHW4c kernels (cb = 4) the packed form also depends on the stride and padding the
-    convolution will use; for NCHW16c kernels they are ignored.
+    The packed form depends on the stride the convolution will use (the column-block width is
+    chosen per stride) and, for NCHW4c kernels (cb = 4), on the padding as well.
     """
     L = _require_cuda_lib()
     kernel = _to_device(kernel, torch.int8, 'kernel')
@@ -124,7 +124,8 @@ def pack_conv_weights_int8(kernel: torch.Tensor, stride: IntPair = 1, padding: I
         raise ValueError(f'kernel must be [O/16][I/cb][KH][KW][cb/4][16][4], got {tuple(kernel.shape)}')
     oc, icc, kh, kw, c4 = (int(s) for s in kernel.shape[:5])
     cb = c4 * 4
-    stride, padding = (_pair(stride), _pair(padding)) if cb == 4 else ((1, 1), (0, 0))
+    stride = _pair(stride)
+    padding = _pair(padding) if cb == 4 else (0, 0)
     key = ('conv_i8', oc * 16, icc * cb, cb, kh, kw, stride, padding)
 
     def make():
@@ -257,8 +258,8 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
         _, c_out, c_in, pcb, kh, kw, pstride, ppad = pw.key
         if c_in != cc * cb or pcb != cb:
             raise ValueError(f'channel mismatch: data has {cc}x{cb}, kernel expects {c_in} in blocks of {pcb}')
-        if cb == 4 and (pstride != stride or ppad != padding):
-            raise ValueError('NCHW4c weights were packed for a different stride / padding')
+        if pstride != stride or (cb == 4 and ppad != padding):
+            raise ValueError('weights were packed for a different stride (or, NCHW4c, padding)')
         requant = out_dtype == 'uint8' or requant_shift is not None
         shift = 8 if requant_shift is None else int(requant_shift)
         d = _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, padding)
