@@ -45,8 +45,8 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
   c.cols_pad = round_up(cols, 2);
   // Widest column block.  256 columns x two sub-tiles fill TMEM with one accumulator set, so
   // each tile's drain (about 2.7 k cycles) is exposed; that is paid back by the halved weight
-  // traffic only when the reduction is long.  Measured at batch 256: reductions of 256..1024
-  // bytes (16..64 columns) run 8-13 % faster with 128-wide blocks (two sets, drain overlapped),
+  // traffic only when the reduction is long.  Measured at batch 256: reductions of 128..1024
+  // bytes (8..64 columns) run 8-13 % faster with 128-wide blocks (two sets, drain overlapped),
   // longer ones 15-50 % slower.  UNIT_B200_BN overrides (experiments).
   static const int forced_bn = [] {
     const char *e = getenv("UNIT_B200_BN");
@@ -56,7 +56,7 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
   // (cheap_a = false: the A operand comes through the slower im2col copies, where fetching it
   // once more per extra column block costs more than the overlap gains: stride-2 layers lost 35-45 %)
   const int bn_max = forced_bn ? forced_bn
-                               : ((cheap_a && n_total >= 256 && c.cols_pad >= 16 && c.cols_pad <= 64) ? 128 : 256);
+                               : ((cheap_a && n_total >= 256 && c.cols_pad >= 8 && c.cols_pad <= 64) ? 128 : 256);
   c.n_tiles = (n_total + bn_max - 1) / bn_max;
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
   const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
@@ -76,14 +76,27 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
 // Rows per CTA tile: two 128-row sub-tiles share each weight stage when the larger tiles
 // still occupy at least half of the SMs and the reduction is long enough for the weight
 // traffic to matter (measured: fewer weight bytes per MAC outweighs a partly idle GPU).
-static int choose_mt(const TileCfg &c, long long m_total, int sms) {
+// Sub-tiles per CTA tile.  Two (one B stage feeds two accumulators, one MMA-issuing thread each)
+// unless the grid would be under-filled, or the reduction is so short that a second accumulator
+// set in TMEM is worth more (wide blocks only: with MT x BN <= 256 both sets fit anyway).  When
+// the A operand is the bottleneck (im2col copies: slow_a) a single sub-tile costs nothing extra,
+// so it is taken when it fills the last round of tiles markedly better.  Measured at batch 256.
+static int choose_mt(const TileCfg &c, long long m_total, int sms, bool slow_a) {
   static const int forced = [] {
     const char *e = getenv("UNIT_B200_MT");
     return e ? atoi(e) : 0;
   }();
   if (forced == 1 || forced == 2) return forced;
   const long long tiles2 = (m_total + 2 * kTileM - 1) / (2 * kTileM) * c.n_tiles;
-  return (2 * tiles2 >= sms && c.cols_pad >= 16) ? 2 : 1;
+  const long long tiles1 = (m_total + kTileM - 1) / kTileM * c.n_tiles;
+  if (2 * tiles2 < sms) return 1;
+  if (c.cols_pad < 16 && c.bn > 128) return 1;
+  if (slow_a) {
+    const double eff2 = (double)tiles2 / (double)((tiles2 + sms - 1) / sms * sms);
+    const double eff1 = (double)tiles1 / (double)((tiles1 + sms - 1) / sms * sms);
+    if (eff1 > 1.25 * eff2) return 1;
+  }
+  return 2;
 }
 
 static int stages_for(const TileCfg &c, int mt, size_t *smem_bytes) {
@@ -433,7 +446,7 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const
   p.trace = g_trace.load();
   p.trace_cap = g_trace_cap.load();
   const int sms = sm_count();
-  if (choose_mt(c, p.m_total, sms) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms, tmap);
+  if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms, tmap);
   return launch_igemm_mt<AMODE, EPI, F16, 1>(p, c, st, sms, tmap);
 }
 
