@@ -329,22 +329,53 @@ def run_unit(args):
     for _ in range(args.warmup):
         step()
     barrier()
+    # One step = 53 launches of a few tens of microseconds: replay them as a CUDA graph so that
+    # the host's per-call work (Python, ctypes, tensor-map encoding) is not what is measured.
+    graph = None
+    launches_per_step = None
+    if not args.no_graph and not args.kernels_only:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()  # the operators keep their scratch per stream: create it before the capture
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            c0 = U.launch_count()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+            launches_per_step = U.launch_count() - c0
+            for _ in range(args.warmup):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:  # keep measuring, say how
+            print(f'[bench] CUDA graph capture failed ({exc!r}); timing eager launches', file=sys.stderr)
+            graph = None
+
+    def timed_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    barrier()
     n0 = U.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as cs_:
         e0.record()
         for _ in range(args.steps):
-            step()
+            timed_step()
         e1.record()
         barrier()
-        launches = U.launch_count() - n0
+        launches = (launches_per_step * args.steps) if graph is not None else (U.launch_count() - n0)
         # nvidia-smi needs ~0.1 s per sample: when the timed region was shorter than a few
         # samples, keep the same load running (untimed) until the sampler has seen it
         t_end = time.time() + 1.5
         extended = False
         while len(cs_.rows) < 6 and time.time() < t_end:
             extended = True
-            step()
+            timed_step()
             torch.cuda.synchronize()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     U.device_status()
@@ -453,6 +484,8 @@ def run_unit(args):
             'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d * world, 'd2h_bytes_per_step': d2h * world,
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': gpu_launches,
+            'launch_mode': ('cuda graph: one captured step (%d kernel launches) replayed per timed step' % launches_per_step)
+            if graph is not None else 'eager launches through the Python operator',
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
                          'frac': kernel_tops / int8_peak,
                          'traffic': (sum(ncu_traffic(l.name, batch) * l.count for l in layer_set) / sum(l.count for l in layer_set))
@@ -485,6 +518,7 @@ def main():
     ap.add_argument('--impl', default='unit', choices=['unit', 'reference'])
     ap.add_argument('--e2e-steps', type=int, default=2)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-graph', action='store_true', help='time eager launches instead of replaying a captured step')
     ap.add_argument('--layer', action='append', default=None,
                     help='restrict the sweep to the named layer(s) of unit_b200.resnet50.LAYERS (diagnostic runs; '
                          'the JSON line then describes that subset)')

@@ -61,9 +61,15 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
   const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
   static const int cand[] = {8, 6, 4, 12, 10, 14, 16};
+  static const int forced_kc = [] {  // UNIT_B200_KC: preferred stage depth in columns (experiments)
+    const char *e = getenv("UNIT_B200_KC");
+    const int v = e ? atoi(e) : 0;
+    return (v >= 2 && v <= 16 && v % 2 == 0) ? v : 0;
+  }();
   c.kc = 0;
+  if (forced_kc && forced_kc <= kc_max && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
   for (int kc : cand)
-    if (kc <= kc_max && c.cols_pad % kc == 0) { c.kc = kc; break; }
+    if (c.kc == 0 && kc <= kc_max && c.cols_pad % kc == 0) { c.kc = kc; break; }
   if (c.kc == 0) c.kc = kc_max >= 8 ? 8 : (kc_max & ~1);  // last stage is partial
   if (c.cols_pad < c.kc) c.kc = c.cols_pad;
   c.k_stages = (c.cols_pad + c.kc - 1) / c.kc;
@@ -428,6 +434,22 @@ static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, in
 
 static FastDiv make_fast_div(uint32_t d);
 
+// Device address of the error word on the current device, looked up once per device (a launch
+// then makes no runtime call besides the kernel launch itself, so it can be captured in a graph).
+static unsigned int *error_word_address() {
+  static std::mutex mu;
+  static unsigned int *cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_error_word) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<unsigned int *>(ptr);
+  }
+  return cached[dev];
+}
+
 template <int AMODE, int EPI, bool F16>
 static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const CUtensorMap *tmap_in = nullptr) {
   static const CUtensorMap no_map{};
@@ -439,9 +461,8 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const
   p.last_ksteps = c.last_ksteps;
   p.n_tiles = c.n_tiles;
   p.div_n_tiles = make_fast_div((uint32_t)c.n_tiles);
-  void *err_ptr = nullptr;
-  if (cudaGetSymbolAddress(&err_ptr, g_error_word) != cudaSuccess) return UNIT_ERR_LAUNCH;
-  p.err = static_cast<unsigned int *>(err_ptr);
+  p.err = error_word_address();
+  if (p.err == nullptr) return UNIT_ERR_LAUNCH;
   p.fold_bias = use_fold() ? 1 : 0;
   p.trace = g_trace.load();
   p.trace_cap = g_trace_cap.load();
