@@ -543,6 +543,8 @@ template <int AMODE, int EPI, bool F16, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(128) uint8_t smem[];
+  // let the next kernel of the stream start its own prologue as soon as SMs become free
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -585,6 +587,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ps->tmem_base;
+  // Programmatic dependent launch: everything above touched only this CTA's shared memory and
+  // TMEM, so it may run while the previous kernel in the stream is still finishing; from here
+  // on global memory is read and written, which has to wait for that kernel's completion.
+  // (A no-op when the kernel was launched without the attribute.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 

@@ -402,6 +402,15 @@ static bool use_row_form() {
   return v != 0;
 }
 
+// UNIT_B200_PDL=0 launches the contraction kernels fully serialised (for comparison runs).
+static bool use_pdl() {
+  static const int v = [] {
+    const char *e = getenv("UNIT_B200_PDL");
+    return e ? atoi(e) : 1;
+  }();
+  return v != 0;
+}
+
 // UNIT_B200_FOLD=0 makes the drain add every bias (for comparison runs); the default lets the tensor core do it.
 static bool use_fold() {
   static const int v = [] {
@@ -427,9 +436,22 @@ static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, in
   p.m_tiles = (int)((p.m_total + kTileM * MT - 1) / (kTileM * MT));
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kern<<<grid, kNumThreads, smem_bytes, st>>>(p, tmap);
+  // launched with programmatic stream serialisation: the kernel's prologue (barrier set-up,
+  // TMEM allocation) may overlap the tail of the previous kernel in the stream; the kernel waits
+  // for that kernel's completion (griddepcontrol.wait) before it touches global memory
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = use_pdl() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p, tmap);
   g_launches.fetch_add(1);
-  return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
+  return (le == cudaSuccess && cudaGetLastError() == cudaSuccess) ? UNIT_OK : UNIT_ERR_LAUNCH;
 }
 
 static FastDiv make_fast_div(uint32_t d);
