@@ -73,6 +73,10 @@ constexpr int kNumThreads = 736;
 constexpr int kDrainWarps = 16, kFirstProducerWarp = 16, kBWarp = 20, kMmaWarp = 21, kMmaWarp2 = 22;
 constexpr uint32_t kFoldBBytes = 4096;  // one accumulator set's bias digits: 256 channels x 16 bytes
 constexpr uint32_t kFoldBytes = 2 * kFoldBBytes + 2 * 128 * 16;  // two sets + the constant A block (2 columns)
+#ifndef UNIT_WAIT_HINT_NS
+#define UNIT_WAIT_HINT_NS 100
+#endif
+constexpr uint32_t kWaitHintNs = UNIT_WAIT_HINT_NS;  // longest suspension of one mbarrier probe
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
 constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
 
@@ -179,7 +183,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t it = 0; it < (1u << 26); ++it) {
-    if (mbar_try_wait_hint(bar, parity, 400u)) return true;
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
     __nanosleep(32);
     if ((it & 15u) == 15u) {
       if (*abort_flag) return false;
@@ -200,7 +204,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   const unsigned long long t0 = global_timer_ns();
   bool timed_out = true;
   for (uint32_t it = 0; it < (1u << 26); ++it) {
-    if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, 400u) ? 1 : 0)) return true;
+    if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, kWaitHintNs) ? 1 : 0)) return true;
     __nanosleep(32);
     if ((it & 15u) == 15u) {
       if (__any_sync(0xffffffffu, *abort_flag)) { timed_out = false; break; }
