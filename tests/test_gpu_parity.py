@@ -430,6 +430,29 @@ def test_large_batch_property_config5(U, oracle):
             assert torch.equal(part, got[s0:s0 + 32])
 
 
+def test_dependent_convolutions_back_to_back(U, oracle):
+    """Each convolution's prologue may overlap the previous kernel's tail (programmatic dependent
+    launch); a chain in which every layer reads the previous layer's output, launched without any
+    host synchronisation in between, must still equal the oracle's chain."""
+    rng = np.random.default_rng(4242)
+    x = rng.integers(0, 256, (4, 4, 28, 28, 16), dtype=np.uint8)
+    ws = [rng.integers(-8, 9, (4, 4, k, k, 4, 16, 4), dtype=np.int8) for k in (1, 3, 1, 3)]
+    bs = [rng.integers(-2 ** 10, 2 ** 10, 64, dtype=np.int32) for _ in ws]
+    ref = x
+    for w, b in zip(ws, bs):
+        k = w.shape[2]
+        ref = oracle.conv2d_u8s8(ref, w, (1, 1), (k // 2, k // 2), bias=b, requant_shift=8)
+    xd = dev(x)
+    pws = [U.pack_conv_weights_int8(dev(w), 1, w.shape[2] // 2) for w in ws]
+    bds = [dev(b) for b in bs]
+    for rep in range(10):
+        cur = xd
+        for w, pw, bd in zip(ws, pws, bds):
+            cur = U.conv2d_NCHWc_int8(cur, pw, stride=1, padding=w.shape[2] // 2, bias=bd, out_dtype='uint8')
+        assert np.array_equal(cur.cpu().numpy(), ref), f'repetition {rep}'
+    U.device_status()
+
+
 def test_error_behaviour(U):
     x = torch.zeros((1, 4, 8, 8, 16), dtype=torch.uint8, device='cuda')
     w = torch.zeros((4, 4, 3, 3, 4, 16, 4), dtype=torch.int8, device='cuda')
