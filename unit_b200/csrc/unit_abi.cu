@@ -67,7 +67,12 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
     return (v >= 2 && v <= 16 && v % 2 == 0) ? v : 0;
   }();
   c.kc = 0;
-  if (forced_kc && forced_kc <= kc_max && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
+  const int kc_max2 = (int)(kSmemBudget / 2 / (16 * (2 * kTileM + c.bn)));  // two stages still fit
+  if (forced_kc && forced_kc <= kc_max2 && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
+  // Narrow column blocks with a reduction of at most 16 columns (the folded stem): the whole
+  // reduction in one stage.  Such tiles are bound by the per-stage work of the MMA-issuing
+  // threads (wait, commit), not by bytes in flight (measured: stem 182 -> 156 us; wider blocks lose).
+  if (c.kc == 0 && c.bn <= 64 && c.cols_pad > 8 && c.cols_pad <= 16 && c.cols_pad <= kc_max2) c.kc = c.cols_pad;
   for (int kc : cand)
     if (c.kc == 0 && kc <= kc_max && c.cols_pad % kc == 0) { c.kc = kc; break; }
   if (c.kc == 0) c.kc = kc_max >= 8 ? 8 : (kc_max & ~1);  // last stage is partial
