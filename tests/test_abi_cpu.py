@@ -55,9 +55,9 @@ def test_packed_weight_sizes_are_pure_host_functions(L):
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc())) == 36 * 64 * 16
     # 1x1 512->2048: 32 columns, 8 N tiles of 256
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=512, c_out=2048, kh=1, kw=1))) == 32 * 2048 * 16
-    # stem: 7 kh x 2 groups of 4 kw taps = 14 columns, in two stages of 8 (the last one partial)
+    # stem: 7 kh x 2 groups of 4 kw taps = 14 columns in one stage, plus the 16 columns of the folded form
     assert L.unit_packed_weights_bytes_conv_i8(
-        ctypes.byref(desc(c_in=4, c_block=4, kh=7, kw=7, h=224, w=224, stride_h=2, stride_w=2, pad_h=3, pad_w=3))) == 16 * 64 * 16 + 16 * 64 * 16
+        ctypes.byref(desc(c_in=4, c_block=4, kh=7, kw=7, h=224, w=224, stride_h=2, stride_w=2, pad_h=3, pad_w=3))) == 14 * 64 * 16 + 16 * 64 * 16
     # odd column count (9 taps x 1 chunk) is padded to an even number of columns
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=16, c_out=16))) == 10 * 16 * 16
     assert L.unit_packed_weights_bytes_conv_f16(ctypes.byref(desc(c_in=256, c_out=256))) == 288 * 256 * 16
