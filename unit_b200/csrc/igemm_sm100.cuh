@@ -16,9 +16,11 @@
 //   stride between adjacent K columns (LBO) = R * 16 bytes.
 // NCHW16c activations fit this format natively: 16 channels of one u8 pixel
 // are one 16-byte core-matrix row and consecutive pixels of an image row are
-// consecutive rows, so the A tile is gathered by 16-byte cp.async copies with
-// zero fill for padding taps and rows past the end.  Weights are repacked once
-// on the device into ready-made [KC][BN][16 B] stage blocks and arrive with a
+// consecutive rows.  The A tile is filled by tensor copies (TMA): whole-row
+// boxes for stride 1, im2col-mode copies for other strides, column copies for
+// plain matrices; 16-byte cp.async gathers with zero fill remain as the path
+// for small tensors and NCHW4c without scratch.  Weights are repacked once on
+// the device into ready-made [KC][BN][16 B] stage blocks and arrive with a
 // single bulk copy (cp.async.bulk, no tensor map, no multicast) per stage.
 //
 // A CTA tile is MT x 128 rows by BN columns (MT = 1 or 2): with MT = 2 one B
@@ -26,19 +28,26 @@
 //
 // Warp roles (736 threads):
 //   warps 0-15  drain: tcgen05.ld the finished accumulator (warp w may touch
-//               TMEM lanes 32(w%4)..+31 = tile rows), apply the epilogue, store;
-//               the four warps of a lane quadrant split the sub-tiles and the
-//               columns.  The drain is plain integer code whose speed comes from
-//               warp-level parallelism, hence the many warps
-//   warps 16-19 A producers: 128 threads gather A columns with cp.async; each
-//               thread's copies arrive on the stage barrier by themselves
-//               (cp.async.mbarrier.arrive.noinc), so no producer waits for data
+//               TMEM lanes 32(w%4)..+31 = tile rows), requantise or copy, store.
+//               With two accumulator sets in TMEM the warps form two groups of
+//               eight, one per set, that drain alternate tiles independently.
+//               They also prepare the bias of the tile that will use their set
+//               next: as s8 digits that one extra MMA K step adds to the
+//               accumulator (so the drain itself only shifts, clamps and stores),
+//               or as integers to add where the values do not fit that form
+//   warps 16-19 A producers: lanes issue the tensor copies of a stage (or 128
+//               threads gather columns with cp.async, whose copies arrive on the
+//               stage barrier by themselves)
 //   warp  20    B producer: one lane issues the bulk copies
 //   warp  21    TMEM allocation; one lane issues tcgen05.mma / tcgen05.commit for sub-tile 0
 //   warp  22    (MT = 2) one lane issues them for sub-tile 1: a single thread cannot issue
 //               MMAs fast enough to keep the tensor core busy on narrow column blocks
 // When two accumulator sets fit in the 512 TMEM columns, the drain of tile i
 // overlaps the main loop of tile i+1.
+//
+// The kernel is launched with programmatic stream serialisation: barrier set-up
+// and TMEM allocation may overlap the previous kernel's tail; griddepcontrol.wait
+// precedes the first access to global memory.
 //
 // Every wait on an mbarrier is bounded in time.  A wait that runs out sets a
 // CTA-wide abort flag and a global error word; all roles then leave their
@@ -335,11 +344,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 __device__ __forceinline__ uint32_t pack_sat_u16(int32_t a, int32_t b) {
   uint32_t d;
   asm("cvt.pack.sat.u16.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ int32_t add_sat(int32_t a, int32_t b) {
-  int32_t d;
-  asm("add.sat.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
 // d = (c << 16) | (sat_u8(a) << 8) | sat_u8(b)
