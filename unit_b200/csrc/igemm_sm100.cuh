@@ -131,6 +131,7 @@ struct IgemmParams {
   // One copy of box_w + KW - 1 pixels then serves all KW columns of that kernel row: the MMA
   // reads column (kh, kw) at the row buffer's address + 16 kw, and the two columns of a K step
   // are 16 bytes apart (overlapping core matrices).
+  int a_sw128;    // A_DENSE_TMA: 1 = the A tile lies in the 128-byte-swizzled K-major layout (rows of 128 bytes)
   int row_kw;     // 0, or KW (even) when the row form is in use
   int row_bytes;  // bytes one row copy delivers: (box_w + KW - 1) * 16
   FastDiv div_n_tiles;      // tile index -> (row block, column block)
@@ -274,6 +275,13 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap *tma
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
       : "memory");
 }
+// tiled-mode tensor copy of one box of the 2-D tensor (byte of a row, row)
+__device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
 // tiled-mode tensor copy of one box of the 3-D tensor (8-byte half of a 16-byte column, column, row)
 __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap *tmap, int x, int y, int z, uint32_t bar) {
   asm volatile(
@@ -366,6 +374,13 @@ __device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, in
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: a row is 128 bytes of K, eight rows
+// form a 1 KB atom whose 16-byte chunks are XOR-permuted by the row number (the layout the copy
+// engine writes with CU_TENSOR_MAP_SWIZZLE_128B); consecutive atoms along M are 1 KB apart (SBO).
+// A K step of 32 bytes inside the atom is addressed by advancing the start address by 32 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor: D format bits 4-5 (1 = f32, 2 = s32), A format bits 7-9,
 // B format bits 10-12 (i8 kinds: 0 = u8, 1 = s8; f16 kind: 0 = fp16), both operands
@@ -550,7 +565,7 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
 template <int AMODE, int EPI, bool F16, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];  // (1 KB: a swizzled operand atom is 8 rows x 128 bytes)
   // let the next kernel of the stream start its own prologue as soon as SMs become free
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
@@ -801,7 +816,16 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t bar = smem_u32(&ps->full[s]);
         int real = p.cols - ks * p.kc;  // columns of this stage that exist (the rest only meets zero weights)
         real = real < 0 ? 0 : (real > p.kc ? p.kc : real);
-        if (row_form) {
+        if (AMODE == A_DENSE_TMA && p.a_sw128 != 0) {
+          // one copy = 128 rows x 128 bytes of K (8 columns) of one sub-tile, written swizzled
+          const int atoms = p.kc >> 3;
+          if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(atoms * nsub) * 16384u);
+          __syncwarp();
+          if (jj < atoms) {
+            const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * 16384u;
+            tma_tile_2d(dst, &tmap, (ks * p.kc + jj * 8) * 16, c0, bar);
+          }
+        } else if (row_form) {
           if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(rows_per_stage * nsub) * (uint32_t)p.row_bytes);
           __syncwarp();
           if (jj < rows_per_stage && sub_ok) {
@@ -869,6 +893,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const uint32_t idesc = make_idesc<F16>(p.bn);
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
       const uint64_t a_desc_row = make_smem_desc(0u, 16u, 128u);  // row form: K columns 16 bytes apart
+      const uint64_t a_desc_sw = make_smem_desc_sw128(0u);         // dense matrices in the swizzled layout
       const uint64_t b_desc0 = make_smem_desc(0u, (uint32_t)p.bn * 16u, 128u);
       const uint32_t a_step = (2u * kSubBytes) >> 4;               // one MMA K-step = two 16-byte columns
       const uint32_t b_step = (2u * (uint32_t)p.bn * 16u) >> 4;
@@ -908,7 +933,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint32_t a_enc = stage_enc + my_t * a_sub_enc;  // this thread's sub-tile of the stage
           const uint32_t b_enc = stage_enc + (a_stage_bytes >> 4);
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
-          if (AMODE == A_CONV_BOX && p.row_kw > 0) {
+          if (AMODE == A_DENSE_TMA && p.a_sw128 != 0) {
+            // swizzled A: K step k is 32 bytes further inside its 128-byte atom; atoms are 16 KB apart
+            for (int k = 0; k < nk; ++k) {
+              const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
+              const uint64_t adesc = a_desc_sw | (uint64_t)(a_enc + (uint32_t)(k >> 2) * (16384u >> 4) + (uint32_t)(k & 3) * 2u);
+              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              started = 1u;
+            }
+          } else if (AMODE == A_CONV_BOX && p.row_kw > 0) {
             // row form: the columns of a kernel row share one row buffer, 16 bytes apart
             uint32_t a_row = a_enc;  // row buffer of the current kernel row (encoded address)
             int pr = 0;              // pair of columns within the row

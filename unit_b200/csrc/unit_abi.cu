@@ -39,7 +39,7 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // Depends on the weight tensor only (never on the batch), so packed weights stay valid
 // for every input size.  kc is chosen so that four stages of the larger (two sub-tile)
 // CTA tile fit in shared memory.
-static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
+static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense = false) {
   TileCfg c;
   c.cols = cols;
   c.cols_pad = round_up(cols, 2);
@@ -69,6 +69,9 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false) {
   c.kc = 0;
   const int kc_max2 = (int)(kSmemBudget / 2 / (16 * (2 * kTileM + c.bn)));  // two stages still fit
   if (forced_kc && forced_kc <= kc_max2 && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
+  // plain matrices: stages of 8 columns = 128 bytes of K per row, the width of a swizzled operand
+  // row, which lets the A tile arrive as full cache lines (three stages still fit)
+  if (c.kc == 0 && dense && c.cols_pad % 8 == 0 && 8 <= (int)(kSmemBudget / 3 / (16 * (2 * kTileM + c.bn)))) c.kc = 8;
   // Narrow column blocks with a reduction of at most 16 columns (the folded stem): the whole
   // reduction in one stage.  Such tiles are bound by the per-stage work of the MMA-issuing
   // threads (wait, commit), not by bytes in flight (measured: stem 182 -> 156 us; wider blocks lose).
@@ -635,6 +638,42 @@ static bool make_dense_map(CUtensorMap *map, const void *a, long long rows, long
   return r == CUDA_SUCCESS;
 }
 
+// Tiled-mode tensor map over a row-major byte matrix for the 128-byte-swizzled operand layout:
+// one copy fetches 128 bytes of K of 128 consecutive rows (full cache lines) and writes them as
+// 1 KB atoms of 8 rows with the 16-byte chunks permuted by the row number.  Bytes and rows past
+// the end of the matrix are filled with zeros.
+static bool make_dense_map_sw128(CUtensorMap *map, const void *a, long long rows, long long row_bytes, long long ld) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode || ld >= (1ll << 40) || rows > 0x7fffffffll - 512 || row_bytes >= (1ll << 31)) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(a), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// UNIT_B200_SW128=0 keeps the column copies for plain matrices (for comparison runs).
+static bool use_sw128() {
+  static const int v = [] {
+    const char *e = getenv("UNIT_B200_SW128");
+    return e ? atoi(e) : 1;
+  }();
+  return v != 0;
+}
+
 // The im2col TMA path is the default; UNIT_B200_TMA=0 selects the cp.async gather (for comparison runs).
 static bool use_tma() {
   static const int v = [] {
@@ -872,7 +911,7 @@ int unit_pack_weights_conv_f16(const unit_conv_desc *d, const void *w, void *pac
 
 size_t unit_packed_weights_bytes_dense_i8(int32_t n, int32_t k) {
   if (n < 16 || n % 16 || k < 16 || k % 16) return 0;
-  const TileCfg c = make_cfg(n, k / 16);
+  const TileCfg c = make_cfg(n, k / 16, false, true);
   return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
 }
 
@@ -881,7 +920,7 @@ int unit_pack_weights_dense_i8(int32_t n, int32_t k, int32_t tile, const int8_t 
   if (tile < 1 || n % tile) return UNIT_ERR_LAYOUT;
   if (!b || !packed) return UNIT_ERR_NULL;
   if (!aligned16(b) || !aligned16(packed)) return UNIT_ERR_ALIGN;
-  const TileCfg c = make_cfg(n, k / 16);
+  const TileCfg c = make_cfg(n, k / 16, false, true);
   PackParams pp{};
   pp.src = reinterpret_cast<const uint8_t *>(b);
   pp.dst = static_cast<uint4 *>(packed);
@@ -893,7 +932,7 @@ int unit_pack_weights_dense_i8(int32_t n, int32_t k, int32_t tile, const int8_t 
 
 size_t unit_packed_weights_bytes_gemm_f16(int32_t n, int32_t k) {
   if (n < 16 || n % 16 || k < 8 || k % 8) return 0;
-  const TileCfg c = make_cfg(n, k / 8);
+  const TileCfg c = make_cfg(n, k / 8, false, true);
   return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
 }
 
@@ -901,7 +940,7 @@ int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *b, void *packed
   if (n < 16 || n % 16 || k < 8 || k % 8) return UNIT_ERR_SHAPE;
   if (!b || !packed) return UNIT_ERR_NULL;
   if (!aligned16(b) || !aligned16(packed)) return UNIT_ERR_ALIGN;
-  const TileCfg c = make_cfg(n, k / 8);
+  const TileCfg c = make_cfg(n, k / 8, false, true);
   PackParams pp{};
   pp.src = static_cast<const uint8_t *>(b);
   pp.dst = static_cast<uint4 *>(packed);
@@ -948,12 +987,16 @@ int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_
     return UNIT_ERR_ALIGN;
   int rc = check_arch();
   if (rc) return rc;
-  const TileCfg c = make_cfg(n, k / 16);
+  const TileCfg c = make_cfg(n, k / 16, false, true);
   IgemmParams p{};
   p.a = a; p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
   p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
   p.OH = p.OW = 1;
   CUtensorMap map;
+  if (use_tma() && use_sw128() && c.kc % 8 == 0 && make_dense_map_sw128(&map, a, m, k, lda)) {
+    p.a_sw128 = 1;
+    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream), &map);
+  }
   if (use_tma() && make_dense_map(&map, a, m, k, lda))
     return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_DENSE, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream));
@@ -983,12 +1026,16 @@ int unit_gemm_f16f32(int32_t m, int32_t n, int32_t k, const void *a, int64_t lda
     return UNIT_ERR_ALIGN;
   int rc = check_arch();
   if (rc) return rc;
-  const TileCfg c = make_cfg(n, k / 8);
+  const TileCfg c = make_cfg(n, k / 8, false, true);
   IgemmParams p{};
   p.a = static_cast<const uint8_t *>(a); p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
   p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
   p.OH = p.OW = 1;
   CUtensorMap map;
+  if (use_tma() && use_sw128() && c.kc % 8 == 0 && make_dense_map_sw128(&map, a, m, 2ll * k, lda)) {
+    p.a_sw128 = 1;
+    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream), &map);
+  }
   if (use_tma() && make_dense_map(&map, a, m, 2ll * k, lda))
     return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_DENSE, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream));
