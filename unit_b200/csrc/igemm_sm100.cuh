@@ -131,6 +131,7 @@ struct IgemmParams {
   // One copy of box_w + KW - 1 pixels then serves all KW columns of that kernel row: the MMA
   // reads column (kh, kw) at the row buffer's address + 16 kw, and the two columns of a K step
   // are 16 bytes apart (overlapping core matrices).
+  int a_sw32;     // A_CONV_BOX on fp16: pixels (32 bytes = one K step) as 32-byte-swizzled rows, one box copy per K step
   int a_sw128;    // A_DENSE_TMA: 1 = the A tile lies in the 128-byte-swizzled K-major layout (rows of 128 bytes)
   int row_kw;     // 0, or KW (even) when the row form is in use
   int row_bytes;  // bytes one row copy delivers: (box_w + KW - 1) * 16
@@ -275,6 +276,15 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap *tma
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
       : "memory");
 }
+// tiled-mode tensor copy of one box of a 5-D tensor
+__device__ __forceinline__ void tma_tile_5d(uint32_t dst, const CUtensorMap *tmap, int c0, int c1, int c2, int c3, int c4,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], "
+      "[%7];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
 // tiled-mode tensor copy of one box of the 2-D tensor (byte of a row, row)
 __device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar) {
   asm volatile(
@@ -381,6 +391,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 // A K step of 32 bytes inside the atom is addressed by advancing the start address by 32 bytes.
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t addr) {
   return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// The same with 32-byte rows (32-byte swizzle): eight rows form a 256-byte atom; one row is one
+// K step (a 32-byte fp16 pixel chunk).
+__device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(256u >> 4) << 32) | (1ull << 46) | (6ull << 61);
 }
 // Instruction descriptor: D format bits 4-5 (1 = f32, 2 = s32), A format bits 7-9,
 // B format bits 10-12 (i8 kinds: 0 = u8, 1 = s8; f16 kind: 0 = fp16), both operands
@@ -772,7 +787,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t wb = (uint32_t)st - q * (uint32_t)p.blocks_w;
         const uint32_t nb = fast_div(q, p.div_blocks_h);
         const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
-        c0 = ((int)wb * p.box_w - p.pw) * 2;
+        c0 = ((int)wb * p.box_w - p.pw) * (F16 ? 1 : 2);  // u8: 8-byte units of a pixel row; fp16: pixels
         c1 = (int)hb * p.box_h - p.ph;
         c2 = (int)nb * p.box_n;
       } else {
@@ -795,6 +810,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         copy_bytes = (uint32_t)(p.box_n * p.box_h * p.box_w) * 16u;
       }
       // this lane's K column: chunk position (ci, kw, kh) and, for fp16, which 16-byte half
+      // (box mode: jj counts chunks, which for fp16 are whole K steps of two columns)
       const int cpc = (AMODE == A_CONV_BOX) ? 1 : p.cols_per_chunk;
       const int half = jj % cpc;
       int q0 = jj / cpc;  // chunk index along K
@@ -804,7 +820,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         kw = (q0 / p.Cc) % p.KW;
         ci = q0 % p.Cc;
       }
-      const int chunk_step = p.kc / cpc;
+      const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
       // row form: jj counts kernel rows of the stage, each copied once into the slot of its first column
       const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
       const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
@@ -824,6 +840,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (jj < atoms) {
             const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * 16384u;
             tma_tile_2d(dst, &tmap, (ks * p.kc + jj * 8) * 16, c0, bar);
+          }
+        } else if (AMODE == A_CONV_BOX && F16) {
+          // fp16 pixels: one copy per K step (chunk of 16 channels = 32 bytes per pixel), written swizzled
+          const int steps = real >> 1;
+          if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(steps * nsub) * copy_bytes * 2u);
+          __syncwarp();
+          if (jj < steps && sub_ok) {
+            const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * 2u * kSubBytes;
+            tma_tile_5d(dst, &tmap, 0, c0 + kw, c1 + kh, ci, c2, bar);
           }
         } else if (row_form) {
           if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(rows_per_stage * nsub) * (uint32_t)p.row_bytes);
@@ -894,6 +919,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
       const uint64_t a_desc_row = make_smem_desc(0u, 16u, 128u);  // row form: K columns 16 bytes apart
       const uint64_t a_desc_sw = make_smem_desc_sw128(0u);         // dense matrices in the swizzled layout
+      // the ordinary loop: column-by-column layout, or fp16 pixel boxes as 32-byte-swizzled rows
+      const uint64_t a_desc_std = (AMODE == A_CONV_BOX && F16) ? make_smem_desc_sw32(0u) : a_desc0;
       const uint64_t b_desc0 = make_smem_desc(0u, (uint32_t)p.bn * 16u, 128u);
       const uint32_t a_step = (2u * kSubBytes) >> 4;               // one MMA K-step = two 16-byte columns
       const uint32_t b_step = (2u * (uint32_t)p.bn * 16u) >> 4;
@@ -955,7 +982,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           } else {
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
-              const uint64_t adesc = a_desc0 | (uint64_t)(a_enc + (uint32_t)k * a_step);
+              const uint64_t adesc = a_desc_std | (uint64_t)(a_enc + (uint32_t)k * a_step);
               tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
               started = 1u;
             }

@@ -638,6 +638,35 @@ static bool make_dense_map(CUtensorMap *map, const void *a, long long rows, long
   return r == CUDA_SUCCESS;
 }
 
+// Tiled-mode tensor map over fp16 NCHW16c activations seen as (8-byte quarter of a pixel's 32
+// bytes, image column, image row, channel chunk, image), written with the 32-byte swizzle: one
+// copy fetches box_n x box_h row segments of box_w pixels of one chunk; a pixel lands as one
+// 32-byte operand row = one K step.  Out-of-range coordinates (the zero padding) read as zeros.
+static bool make_box_map_f16(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  const cuuint64_t cc = (cuuint64_t)c_in / 16;
+  const cuuint64_t dims[5] = {4, (cuuint64_t)w, (cuuint64_t)h, cc, (cuuint64_t)n};
+  const cuuint64_t row = (cuuint64_t)w * 32;
+  const cuuint64_t strides[4] = {32, row, row * h, row * h * cc};
+  const cuuint32_t box[5] = {4, (cuuint32_t)g.bw, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 5, const_cast<void *>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // Tiled-mode tensor map over a row-major byte matrix for the 128-byte-swizzled operand layout:
 // one copy fetches 128 bytes of K of 128 consecutive rows (full cache lines) and writes them as
 // 1 KB atoms of 8 rows with the 16-byte chunks permuted by the row number.  Bytes and rows past
@@ -1013,6 +1042,15 @@ int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const voi
   p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out;
   fill_conv(p, d, 2);
   CUtensorMap map;
+  if (use_tma() && use_sw128() && d->stride_h == 1 && d->stride_w == 1 && c.kc % 2 == 0) {
+    // stride 1: whole pixel rows per copy, one copy per K step
+    const BoxGeom g = choose_box(d->n, p.OH, p.OW);
+    if (make_box_map_f16(&map, d->n, d->c_in, d->h, d->w, x, g)) {
+      set_box(p, g, d->n);
+      p.a_sw32 = 1;
+      return launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream), &map);
+    }
+  }
   if (use_tma() && make_im2col_map(&map, d, x, true))
     return launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream), &map);
   return launch_igemm<A_CONV_F16, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream));
