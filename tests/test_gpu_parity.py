@@ -274,6 +274,8 @@ def test_resnet50_sweep_config3(U, oracle, batch):
 @pytest.mark.parametrize('m,n,k,t', [
     (1, 16, 16, 16), (128, 3072, 768, 128), (100, 128, 128, 128), (300, 512, 1024, 128), (129, 48, 80, 16),
     (1024, 1024, 1024, 16),
+    # swizzled A rows (K a multiple of 128 bytes) with ragged M and N, and K just off that grid (column copies)
+    (257, 272, 384, 16), (5, 16, 128, 16), (700, 528, 2048, 16), (130, 64, 144, 16),
 ])
 def test_dense_int8_bit_exact(U, oracle, m, n, k, t):
     rng = np.random.default_rng(m * 7 + n + k)
@@ -354,7 +356,7 @@ def test_conv_fp16_accepts_nchw_and_oihw_like_the_reference(U, oracle):
     assert isinstance(out, list) and torch.equal(out[0], got)
 
 
-@pytest.mark.parametrize('m,n,k', [(128, 768, 3072), (64, 192, 1024), (1, 16, 8), (130, 48, 72)])
+@pytest.mark.parametrize('m,n,k', [(128, 768, 3072), (64, 192, 1024), (1, 16, 8), (130, 48, 72), (300, 272, 192), (70, 64, 64)])
 def test_gemm_fp16(U, oracle, m, n, k):
     rng = np.random.default_rng(m + n + k)
     a = rng.standard_normal((m, k)).astype(np.float16)

@@ -23,6 +23,10 @@
 // the device into ready-made [KC][BN][16 B] stage blocks and arrive with a
 // single bulk copy (cp.async.bulk, no tensor map, no multicast) per stage.
 //
+// Two operands have K contiguous in memory in runs longer than 16 bytes and use the tensor
+// core's swizzled K-major layouts instead, written directly by the copy engine: plain matrices
+// (rows of 128 bytes, SWIZZLE_128B) and fp16 pixels (rows of 32 bytes = one K step, SWIZZLE_32B).
+//
 // A CTA tile is MT x 128 rows by BN columns (MT = 1 or 2): with MT = 2 one B
 // stage feeds two accumulators, which halves the weight bytes fetched per MAC.
 //
