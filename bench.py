@@ -529,8 +529,68 @@ def run_unit(args):
     return 0
 
 
+def run_side_config(args):
+    """Other BASELINE configurations, one JSON line each (diagnostic; not the headline metric):
+    `gemm` = int8 GEMM 4096^3 (config 2), `fp16conv` = fp16 3x3 256->256 @14^2, N = 256 (config 4),
+    `fp16gemm` = fp16 GEMM 4096^3."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the unit_b200 operators have no CPU fallback')
+    import unit_b200 as U
+    dev = torch.device('cuda', 0)
+    torch.manual_seed(0)
+    peaks = _peaks()
+    if args.config == 'gemm':
+        a = torch.randint(0, 256, (4096, 4096), dtype=torch.uint8, device=dev)
+        w = torch.randint(-128, 128, (32, 1024, 128, 4), dtype=torch.int8, device=dev)
+        pw = U.pack_dense_weights_int8(w)
+        out = torch.empty((4096, 4096), dtype=torch.int32, device=dev)
+        fn = lambda: U.dense_dotprod(a, pw, out=out)
+        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TOPS', 2.0 * peaks['bf16_sustained'], 'int8 GEMM 4096^3 (u8 x s8 -> s32)'
+    elif args.config == 'fp16gemm':
+        a = torch.randn((4096, 4096), dtype=torch.float16, device=dev)
+        b = torch.randn((4096, 4096), dtype=torch.float16, device=dev) * 0.05
+        pw = U.pack_gemm_weights_f16(b)
+        out = torch.empty((4096, 4096), dtype=torch.float32, device=dev)
+        fn = lambda: U.gemm_f16f32(a, pw, out=out)
+        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TFLOP/s', peaks['bf16_sustained'], 'fp16 GEMM 4096^3 (fp32 accumulate)'
+    else:
+        x = torch.randn((256, 16, 14, 14, 16), dtype=torch.float16, device=dev)
+        w = torch.randn((16, 16, 3, 3, 16, 16), dtype=torch.float16, device=dev) * 0.05
+        pw = U.pack_conv_weights_f16(w)
+        out = U.conv2d_NCHW16c_OHWI16o(x, pw, 1, 1, padding=1)
+        fn = lambda: U.conv2d_NCHW16c_OHWI16o(x, pw, 1, 1, padding=1, out=out)
+        ops, unit, peak, what = 2.0 * 256 * 14 * 14 * 256 * 256 * 9, 'TFLOP/s', peaks['bf16_sustained'], \
+            'fp16 conv2d 3x3 256->256 @14^2, N = 256 (fp32 accumulate)'
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+    for _ in range(max(3, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(args.steps):
+        if not args.kernels_only:
+            flush.zero_()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        fn()
+        a1.record()
+        torch.cuda.synchronize()
+        total += a0.elapsed_time(a1)
+    U.device_status()
+    ms = total / args.steps
+    value = ops / (ms * 1e-3) / 1e12
+    print(json.dumps({'metric': what, 'value': value, 'unit': unit, 'n_gpus': 1, 'steps': args.steps, 'warmup': max(3, args.warmup),
+                      'ms_per_step': ms, 'higher_is_better': True, 'data': 'synthetic',
+                      'config': {'workload': args.config, 'l2': 'a 256 MiB buffer is rewritten before every timed call'},
+                      'roofline': {'bound': 'tensor', 'achieved': value, 'peak': peak, 'unit': unit, 'frac': value / peak,
+                                   'peak_source': f'{peaks["source"]} sustained bf16 figure (doubled for int8)'}}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument('--config', default=None, choices=['gemm', 'fp16gemm', 'fp16conv'],
+                    help='time one of the other BASELINE configurations instead of the conv sweep (single GPU)')
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
@@ -549,6 +609,8 @@ def main():
         args.warmup = 3
     if args.impl == 'reference':
         return run_reference(args)
+    if args.config:
+        return run_side_config(args)
     return run_unit(args)
 
 
