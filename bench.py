@@ -283,9 +283,9 @@ def run_unit(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if TOTAL_BATCH % world:
-        raise SystemExit('--gpus must divide 256')
-    batch = TOTAL_BATCH // world
+    if args.total_batch % world:
+        raise SystemExit('--gpus must divide the batch')
+    batch = args.total_batch // world
     gen = torch.Generator(device=dev)
 
     # ---- build the 53 instances: packed weights shared per shape, own activations/outputs per instance
@@ -379,7 +379,7 @@ def run_unit(args):
             torch.cuda.synchronize()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     U.device_status()
-    total_ops = sum(l.ops(TOTAL_BATCH) * l.count for l in layer_set)
+    total_ops = sum(l.ops(args.total_batch) * l.count for l in layer_set)
     value = total_ops / (ms_step * 1e-3) / 1e12
     clocks = cs_.summary()
     clocks['sampled'] = 'timed region plus the same load continued untimed' if extended else 'timed region'
@@ -494,7 +494,7 @@ def run_unit(args):
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
             'config': {'workload': 'resnet50-int8-conv-sweep' + ('' if not args.layer else ':' + '+'.join(args.layer)),
-                       'global_batch': TOTAL_BATCH, 'per_gpu_batch': batch,
+                       'global_batch': args.total_batch, 'per_gpu_batch': batch,
                        'convolutions': sum(l.count for l in layer_set), 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
                        'parallelism': f'batch-split x{world}, weights replicated, no collective',
                        'l2': 'every convolution instance has its own buffers; %.2f GB touched per step per GPU, '
@@ -596,6 +596,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='unit', choices=['unit', 'reference'])
     ap.add_argument('--e2e-steps', type=int, default=2)
+    ap.add_argument('--total-batch', type=int, default=TOTAL_BATCH,
+                    help='global batch (diagnostic runs; the metric is quoted on 256)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-graph', action='store_true', help='time eager launches instead of replaying a captured step')
     ap.add_argument('--layer', action='append', default=None,

@@ -7,6 +7,9 @@
  *   - every pointer named d_* is a DEVICE pointer, 16-byte aligned;
  *   - the caller owns every buffer; the library reads inputs and writes only
  *     the output (and, for the pack calls, the destination);
+ *   - the first contraction call on a device, and the first use of each kernel variant, make
+ *     one-off runtime queries (a symbol address, a kernel attribute): make a warm-up call of each
+ *     shape before capturing calls into a CUDA graph;
  *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it;
  *   - every function returns a unit_status; nothing throws, aborts or prints;
  *   - weights are consumed in a tensor-core-ready copy ("packed weights") that
@@ -59,6 +62,47 @@ typedef struct unit_conv_desc {
   int32_t pad_h, pad_w;
 } unit_conv_desc;
 
+/* The int8 convolution's epilogue, applied to the s32 accumulator acc of every output element:
+ *     t = acc + d_bias[oc]            (wrapping s32; d_bias may be NULL)
+ *     t = t * mul                     (wrapping s32)
+ *   out_u8 == 0:  the s32 output is t.  With mul = 11 this is the fused operator of the
+ *                 reference's graph flow, multiply(add(conv, bias), 11)
+ *                 (apps/cpu/relay/conv2d.py:21-23, fused as apps/cpu/relay/result.log:35).
+ *                 shift must be 0 and d_residual NULL.
+ *   out_u8 != 0:  q = (t + 2^(shift-1)) >> shift  (arithmetic shift, 1 <= shift <= 31),
+ *                 q = q + d_residual[same index as the output]   (u8, may be NULL),
+ *                 output = clamp(q, 0, 255) as u8.  mul must be 1.  The clamp at 0 is the ReLU of
+ *                 a residual block, so a bottleneck block chains u8 NCHW16c -> u8 NCHW16c with no
+ *                 repack.  The reference fixes no rounding rule for this form; this is the
+ *                 library's own requantisation.
+ * x_signed != 0: the activations are s8 instead of u8.  The reference converts s8 activations to
+ *                 u8 by adding 128 and subtracts 128 * sum(weights) per output channel afterwards
+ *                 (apps/cpu/relay/result.log:4-6,15-21) because its instruction multiplies
+ *                 u8 x s8; the tensor core multiplies s8 x s8 directly, which gives the same
+ *                 numbers, and padding is s8 zero. */
+typedef struct unit_epilogue {
+  const int32_t *d_bias;
+  int32_t mul;
+  int32_t shift;
+  int32_t out_u8;
+  const uint8_t *d_residual;
+  int32_t x_signed;
+} unit_epilogue;
+
+/* A prepared launch (see unit_conv2d_plan_int8): plain bytes owned by the caller, valid in this
+ * process for the device that was current when it was made, until the buffers it names are freed.
+ * May be copied; holds no resource. */
+typedef struct unit_conv_plan {
+  uint64_t opaque[128];
+} unit_conv_plan;
+
+/* Keys of unit_debug_set. */
+enum {
+  UNIT_DEBUG_WAIT_LIMIT_NS = 1,       /* bound of every device-side wait, nanoseconds (default 1e9) */
+  UNIT_DEBUG_STALL_WEIGHT_COPIES = 2  /* non-zero: contraction kernels issue no weight copies, so
+                                         their waits run out and they report UNIT_ERR_DEVICE_WAIT */
+};
+
 /* Library version, major*10000 + minor*100 + patch. */
 int unit_version(void);
 /* Static string for a unit_status value. */
@@ -79,6 +123,21 @@ uint64_t unit_launch_count(void);
  * (clock64) of the SM that runs that block.  d_buf: capacity_tiles * 128 bytes of device
  * memory owned by the caller; NULL detaches.  Not for use while kernels are running. */
 int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
+
+/* Which kernel variant ran: the contraction kernel exists in one compiled variant per (operand
+ * path, epilogue, data type, sub-tiles per tile).  unit_variant_count() is the size of the index
+ * space; unit_variant_name(i) is NULL for indices without a compiled variant, otherwise a static
+ * string such as "igemm_kernel<A_CONV_BOX, EPI_REQ_NCHWC, i8, MT=2>"; unit_variant_launches(i)
+ * counts this process's launches of it.  The counterpart of the schedule index the reference logs
+ * per shape (cpu-tune.log, python/tensorizer/tune.py:20-51). */
+int unit_variant_count(void);
+const char *unit_variant_name(int index);
+uint64_t unit_variant_launches(int index);
+/* Diagnostics for testing the error path without faulting the device (no counterpart in the
+ * reference).  Every device-side wait is bounded; a kernel whose wait runs out stops, frees what
+ * it holds and sets the error word that unit_device_status reports.  Process-wide; applies to
+ * launches made afterwards. */
+int unit_debug_set(int key, long long value);
 
 /* ---- packed weights ------------------------------------------------------ */
 
@@ -128,12 +187,30 @@ int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
 
 /* Same contraction with the fused epilogue
  *   q = clamp((acc + bias[oc] + 2^(shift-1)) >> shift, 0, 255)  -> u8 NCHW16c.
- * Replaces the fused conv + bias + scale operator of the reference's graph
- * flow (apps/cpu/relay/conv2d.py:16-27).  1 <= shift <= 31. */
+ * This is the library's own requantisation (the reference's graph flow fuses bias and an s32
+ * multiply instead, apps/cpu/relay/conv2d.py:21-23: see unit_epilogue).  1 <= shift <= 31. */
 int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *desc, const uint8_t *d_x,
                                    const void *d_packed_w, const int32_t *d_bias,
                                    int32_t shift, uint8_t *d_out, void *d_workspace,
                                    size_t workspace_bytes, void *stream);
+
+/* The general int8 convolution: u8 or s8 activations and the whole epilogue family of
+ * unit_epilogue.  d_out is s32 (out_u8 == 0) or u8 NCHW16c.  The two entry points above are
+ * this one with {bias, 1, 0, 0, NULL, 0} and {bias, 1, shift, 1, NULL, 0}.  Replaces the fused
+ * conv2d_NCHWc + subtract + add + multiply operator of apps/cpu/relay/result.log:21-24,35. */
+int unit_conv2d_int8_nchwc(const unit_conv_desc *desc, const void *d_x, const void *d_packed_w,
+                           const unit_epilogue *epilogue, void *d_out, void *d_workspace,
+                           size_t workspace_bytes, void *stream);
+
+/* The same call split in two, the way the reference builds a module once and then calls it
+ * (poc/vnni/vnni_dense.py:40-66: tvm.build, then module(a, b, c) under time_evaluator).
+ * unit_conv2d_plan_int8 checks the arguments, selects the kernel variant and tile shape and
+ * encodes the tensor map into *plan; unit_conv2d_run launches it on `stream` (one kernel; two
+ * for a folded stem) with no further host work.  The plan names the buffers it was made for. */
+int unit_conv2d_plan_int8(const unit_conv_desc *desc, const void *d_x, const void *d_packed_w,
+                          const unit_epilogue *epilogue, void *d_out, void *d_workspace,
+                          size_t workspace_bytes, unit_conv_plan *plan);
+int unit_conv2d_run(const unit_conv_plan *plan, void *stream);
 
 /* Requantising convolution for callers that may not allocate.  No counterpart in the
  * reference.  It is unit_conv2d_u8s8_requant_nchwc with the scratch taken from a fixed array

@@ -59,6 +59,8 @@ def lib() -> ctypes.CDLL:
     for fn in (L.oracle_conv2d_u8s8, L.vnni_conv2d_u8s8):
         fn.argtypes = conv_args
         fn.restype = ci
+    L.oracle_conv2d_i8_ex.argtypes = [vp, ci, vp, vp, ci, vp, vp, vp, ci] + [ci] * 12
+    L.oracle_conv2d_i8_ex.restype = ci
     for fn in (L.oracle_dense_u8s8s32, L.vnni_dense_u8s8s32):
         fn.argtypes = [vp, vp, vp, ci, ci, ci, ci]
         fn.restype = ci
@@ -124,6 +126,55 @@ def conv2d_u8s8(x, w, stride=(1, 1), pad=(0, 0), bias=None, requant_shift=None, 
     if rc == 1:
         raise OverflowError('oracle: an accumulator left the s32 range')
     return out
+
+
+def conv2d_i8_ex(x, w, stride=(1, 1), pad=(0, 0), bias=None, mul=1, requant_shift=None, residual=None):
+    """The wider epilogue family: x u8 or s8 (by dtype), ``t = (acc + bias) * mul`` wrapping in s32
+    (apps/cpu/relay/conv2d.py:21-23); s32 out, or with ``requant_shift`` the u8 result
+    ``clamp(((t + 2^(shift-1)) >> shift) + residual, 0, 255)``."""
+    x = np.ascontiguousarray(x)
+    assert x.dtype in (np.uint8, np.int8)
+    w = _c(w, np.int8)
+    n, cc, h, wd, cb = x.shape
+    oc, cc2, kh, kw, c4, l16, r4 = w.shape
+    assert cc2 == cc and c4 * 4 == cb and l16 == 16 and r4 == 4
+    oh, ow = out_hw(h, wd, kh, kw, stride, pad)
+    if bias is not None:
+        bias = _c(bias, np.int32)
+        assert bias.size == oc * 16
+    if residual is not None:
+        residual = _c(residual, np.uint8)
+        assert residual.shape == (n, oc, oh, ow, 16) and requant_shift is not None
+    if requant_shift is None:
+        out = np.empty((n, oc, oh, ow, 16), np.int32)
+        o32, o8, sh = out, None, 0
+    else:
+        out = np.empty((n, oc, oh, ow, 16), np.uint8)
+        o32, o8, sh = None, out, int(requant_shift)
+    lib().oracle_conv2d_i8_ex(_p(x), int(x.dtype == np.int8), _p(w), _p(bias), int(mul), _p(residual), _p(o32), _p(o8),
+                              sh, n, cc, h, wd, cb, oc, kh, kw, stride[0], stride[1], pad[0], pad[1])
+    return out
+
+
+def conv2d_s8s8_relay_flow(x_s8, w, stride=(1, 1), pad=(0, 0), bias=None, mul=1):
+    """The reference's graph for signed activations, step by step (apps/cpu/relay/result.log):
+    cast to s32, add 128, cast to u8 (:4-6); u8 x s8 convolution (:14); 128 * sum of each output
+    channel's weights (:15-19) subtracted (:21); bias added (:23) and the s32 product with a
+    constant (:24, apps/cpu/relay/conv2d.py:21-23).  The reference runs it without padding; with
+    padding the shifted tensor is padded with 128 (the image of s8 zero) before a valid convolution."""
+    x_s8 = np.ascontiguousarray(x_s8)
+    assert x_s8.dtype == np.int8
+    w = _c(w, np.int8)
+    xu = (x_s8.astype(np.int32) + 128).astype(np.uint8)
+    if pad != (0, 0):
+        xu = np.pad(xu, ((0, 0), (0, 0), (pad[0], pad[0]), (pad[1], pad[1]), (0, 0)), constant_values=128)
+    conv = conv2d_u8s8(xu, w, stride, (0, 0), vnni=host_has_vnni()).astype(np.int64)
+    comp = 128 * w.astype(np.int64).sum(axis=(1, 2, 3, 4, 6))        # [Oc][16]: every input channel and tap
+    t = conv - comp[None, :, None, None, :]
+    if bias is not None:
+        t = t + np.asarray(bias, np.int64).reshape(1, -1, 1, 1, 16)
+    t = (t * int(mul)) & 0xFFFFFFFF
+    return t.astype(np.uint32).view(np.int32)   # wrapping s32, as the reference's int32 arithmetic
 
 
 def dense_u8s8s32(a, bp, vnni=False):

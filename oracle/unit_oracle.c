@@ -155,6 +155,69 @@ int oracle_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
   return overflow;
 }
 
+/*
+ * The same convolution with the wider epilogue family the library offers.
+ *   x_signed != 0: activations are s8 (the tensor core takes s8 x s8 natively; the reference
+ *                  reaches the same numbers by shifting to u8 and subtracting 128 * sum(w),
+ *                  apps/cpu/relay/result.log:4-6,15-21 -- that flow is restated separately in
+ *                  oracle/c_oracle.py: conv2d_s8s8_relay_flow -- so padding is s8 zero)
+ *   t = wrap32(acc + bias[oc]);  t = wrap32(t * mul)      (apps/cpu/relay/conv2d.py:21-23: add, then
+ *                                                         multiply by an s32 constant, both wrapping)
+ *   out_s32:  t
+ *   out_u8:   q = (t + 2^(shift-1)) >> shift;  q += residual (u8, same layout as the output), if any;
+ *             clamp to [0, 255]               (the clamp at 0 is the ReLU of a residual block)
+ * The requantising and residual forms have no test in the reference: PARITY UNPINNED for them.
+ */
+int oracle_conv2d_i8_ex(const void *xv, int x_signed, const int8_t *w, const int32_t *bias, int32_t mul,
+                        const uint8_t *residual, int32_t *out_s32, uint8_t *out_u8, int shift,
+                        int N, int Cc, int H, int W, int cb, int Oc,
+                        int KH, int KW, int sh, int sw, int ph, int pw) {
+  const int OH = (H + 2 * ph - KH) / sh + 1;
+  const int OW = (W + 2 * pw - KW) / sw + 1;
+  const int c4 = cb / 4;
+  const uint8_t *xu = (const uint8_t *)xv;
+  const int8_t *xs = (const int8_t *)xv;
+  int overflow = 0;
+#pragma omp parallel for collapse(2) reduction(| : overflow) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oc = 0; oc < Oc; ++oc)
+      for (int oh = 0; oh < OH; ++oh)
+        for (int ow = 0; ow < OW; ++ow) {
+          int64_t acc[16];
+          for (int l = 0; l < 16; ++l) acc[l] = 0;
+          for (int ic = 0; ic < Cc; ++ic)
+            for (int kh = 0; kh < KH; ++kh) {
+              const int ih = oh * sh + kh - ph;
+              if (ih < 0 || ih >= H) continue;
+              for (int kw = 0; kw < KW; ++kw) {
+                const int iw = ow * sw + kw - pw;
+                if (iw < 0 || iw >= W) continue;
+                const size_t xo = ((((size_t)n * Cc + ic) * H + ih) * W + iw) * cb;
+                const int8_t *wp = w + ((((size_t)oc * Cc + ic) * KH + kh) * KW + kw) * (size_t)(c4 * 64);
+                for (int m = 0; m < c4; ++m)
+                  for (int r = 0; r < 4; ++r) {
+                    const int32_t a = x_signed ? (int32_t)xs[xo + m * 4 + r] : (int32_t)xu[xo + m * 4 + r];
+                    for (int l = 0; l < 16; ++l) acc[l] += a * (int32_t)wp[(m * 16 + l) * 4 + r];
+                  }
+              }
+            }
+          const size_t o = ((((size_t)n * Oc + oc) * OH + oh) * OW + ow) * 16;
+          for (int l = 0; l < 16; ++l) {
+            if (acc[l] > INT32_MAX || acc[l] < INT32_MIN) overflow |= 1;
+            uint32_t t = (uint32_t)(uint64_t)acc[l] + (uint32_t)(bias ? bias[oc * 16 + l] : 0);
+            t *= (uint32_t)mul;
+            if (out_u8) {
+              int64_t q = ((int64_t)(int32_t)t + ((int64_t)1 << (shift - 1))) >> shift;
+              if (residual) q += residual[o + l];
+              out_u8[o + l] = (uint8_t)(q < 0 ? 0 : (q > 255 ? 255 : q));
+            } else {
+              out_s32[o + l] = (int32_t)t;
+            }
+          }
+        }
+  return overflow;
+}
+
 /* Scalar int8 dense: C[i][j] = sum_k A[i][k] * Bp[j/T][k/4][j%T][k%4]. */
 int oracle_dense_u8s8s32(const uint8_t *A, const int8_t *Bp, int32_t *C,
                          int M, int N, int K, int T) {

@@ -100,6 +100,16 @@ def test_vnni_known_answer_through_the_gpu(U):
     (1, 2048, 7, 7, 512, 1, 1, 1, 0),     # deepest 1x1 reduction
     (1, 512, 7, 7, 512, 3, 3, 1, 1),      # deepest 3x3 reduction (4608)
     (1, 16, 40, 40, 16, 3, 3, 1, 0),      # valid convolution (no padding), as the reference calls it
+    # tensors of 128 KB and more (tensor-copy fed), ragged in every direction
+    (9, 32, 23, 21, 48, 3, 3, 1, 1),      # box copies: 21-pixel rows, tiles straddle images, N tile of 48
+    (5, 48, 29, 31, 320, 3, 3, 1, 1),     # box copies, three chunks, two N tiles of 160
+    (3, 64, 27, 33, 64, 5, 5, 1, 2),      # 5x5 taps, 25 x 4 = 100 K columns
+    (7, 16, 37, 35, 16, 1, 7, 1, 0),      # 1x7 / 7x1 on box copies
+    (7, 16, 37, 35, 16, 7, 1, 1, 3),
+    (2, 16, 70, 150, 32, 3, 3, 1, 1),     # rows wider than a 128-row sub-tile
+    (6, 32, 31, 29, 80, 3, 3, 2, 1),      # im2col copies, odd sizes
+    (4, 48, 33, 35, 64, 5, 5, 3, 2),      # stride 3
+    (3, 80, 30, 30, 64, 1, 1, 2, 0),      # strided 1x1 with five chunks
 ])
 def test_conv_int8_bit_exact(U, oracle, n, ci, h, w, co, kh, kw, s, p):
     rng = np.random.default_rng(hash((n, ci, h, w, co, kh, kw, s, p)) % 2 ** 32)
@@ -186,11 +196,13 @@ def test_wide_layer_bias_beyond_staged_vector(U, oracle):
         assert np.array_equal(gots.cpu().numpy(), oracle.conv2d_u8s8(x, w, bias=b))
 
 
-@pytest.mark.parametrize('hw,k,p', [(32, 7, 3), (33, 7, 3), (30, 3, 1), (30, 5, 2), (18, 7, 0), (20, 4, 1), (26, 6, 2)])
+@pytest.mark.parametrize('hw,k,p', [(64, 7, 3), (33, 7, 3), (62, 3, 1), (60, 5, 2), (18, 7, 0), (20, 4, 1), (66, 6, 2)])
 def test_stem_stride2_geometries(U, oracle, hw, k, p):
     """Stride-2 NCHW4c convolutions: even images take the folded (scratch) path, odd ones the in-place gather."""
     rng = np.random.default_rng(hw * 100 + k)
-    x = rng.integers(0, 256, (3, 1, hw, hw + 2 * (hw % 2 == 0), 4), dtype=np.uint8)
+    # nine images: the folded image (tensor-copy fed) is then 128 KB or more for the larger sizes; the
+    # smaller ones run the in-place gather, which is checked against the same oracle
+    x = rng.integers(0, 256, (9 if hw >= 26 else 3, 1, hw, hw + 2 * (hw % 2 == 0), 4), dtype=np.uint8)
     w = rng.integers(-128, 128, (2, 1, k, k, 1, 16, 4), dtype=np.int8)
     b = rng.integers(-2 ** 15, 2 ** 15, 32, dtype=np.int32)
     got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=2, padding=p)
@@ -205,7 +217,8 @@ def test_stem_wide_rows_one_copy_per_kernel_row(U, oracle, h, w, k, p):
     """Folded stride-2 convolutions whose output rows fill a 128-row sub-tile on their own: the taps
     of a kernel row are fetched with one copy and addressed as shifted windows."""
     rng = np.random.default_rng(h * 1000 + w + k)
-    x = rng.integers(0, 256, (2, 1, h, w, 4), dtype=np.uint8)
+    n = -(-131072 // (h * w * 4))   # enough images for the folded tensor to reach 128 KB (tensor-copy fed)
+    x = rng.integers(0, 256, (n, 1, h, w, 4), dtype=np.uint8)
     wt = rng.integers(-128, 128, (4, 1, k, k, 1, 16, 4), dtype=np.int8)
     b = rng.integers(-2 ** 15, 2 ** 15, 64, dtype=np.int32)
     got = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=2, padding=p)
@@ -259,9 +272,10 @@ def test_resnet50_sweep_config3(U, oracle, batch):
     """BASELINE config 3: every ResNet-50 conv shape, batch 1 and 16, fused bias + requant, bit-exact."""
     from unit_b200 import resnet50 as R
     vnni = oracle.host_has_vnni()
+    if batch > 1 and not vnni:
+        pytest.skip('the batch-16 sweep needs the AVX-512 VNNI oracle (the scalar oracle would take minutes)')
     for li, l in enumerate(R.LAYERS):
-        b_eff = batch if (vnni or batch == 1) else 2
-        x, w, b = R.make_layer_inputs(l, li, b_eff, config=3)
+        x, w, b = R.make_layer_inputs(l, li, batch, config=3)
         got = U.conv2d_NCHWc_int8(dev(x), dev(w), stride=l.stride, padding=l.pad, bias=dev(b), out_dtype='uint8')
         U.device_status()
         ref = oracle.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
@@ -315,6 +329,10 @@ def test_dense_4096_config2(U, oracle):
 @pytest.mark.parametrize('n,ci,h,w,co,k,s,p', [
     (1, 16, 6, 6, 16, 3, 1, 0), (2, 32, 10, 10, 32, 3, 1, 1), (3, 64, 14, 14, 128, 3, 2, 1), (2, 256, 14, 14, 256, 1, 1, 0),
     (1, 1024, 14, 14, 256, 1, 1, 0), (4, 256, 14, 14, 256, 3, 1, 1),
+    # strided convolutions on tensors of 128 KB and more: the im2col tensor copies
+    # (the reference's strided form: python/tensorizer/ops/gpu.py:47-53)
+    (8, 256, 28, 28, 256, 3, 2, 1), (8, 256, 28, 28, 512, 1, 2, 0), (5, 48, 31, 29, 80, 3, 2, 1), (3, 32, 33, 35, 32, 5, 3, 2),
+    (9, 32, 23, 21, 48, 3, 1, 1),     # ragged box copies
 ])
 def test_conv_fp16(U, oracle, n, ci, h, w, co, k, s, p):
     rng = np.random.default_rng(n + ci + co + k)

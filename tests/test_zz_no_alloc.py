@@ -32,7 +32,7 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
     from unit_b200 import _lib
     L = _lib.lib()
     assert L.unit_noalloc_scratch_capacity() == 8 << 20
-    n, hw = 3, 64
+    n, hw = 9, 64   # the folded image is 144 KB: large enough for the scratch path (tensor copies) to be taken
     d = _lib.ConvDesc(n, 4, hw, hw, 4, 64, 7, 7, 2, 2, 3, 3)
     need = L.unit_conv2d_workspace_bytes(ctypes.byref(d))
     assert 0 < need <= L.unit_noalloc_scratch_capacity()
@@ -49,6 +49,14 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
         assert _call_conv(L, 'noalloc', d, x, pw, bias, got) == 0
         U.device_status()
         assert torch.equal(got, want), f'call {call}: outputs differ'
+    # the property the entry point exists for: a call obtains no device memory, neither from the
+    # driver nor from torch's allocator
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    used0 = torch.cuda.memory_allocated()
+    assert _call_conv(L, 'noalloc', d, x, pw, bias, got) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == used0
     # a geometry that needs no scratch is forwarded unchanged
     d16 = _lib.ConvDesc(2, 32, 10, 10, 16, 32, 3, 3, 1, 1, 1, 1)
     x16 = torch.randint(0, 256, (2, 2, 10, 10, 16), dtype=torch.uint8, device='cuda', generator=g)
@@ -65,6 +73,10 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
 def test_noalloc_entry_point_refuses_sizes_beyond_its_scratch():
     from unit_b200 import _lib
     L = _lib.lib()
+    # the documented edge: a 224 x 224 stem fits up to batch 41 (41 * 112 * 112 * 16 B <= 8 MiB < 42 * ...)
+    cap = L.unit_noalloc_scratch_capacity()
+    edge = lambda nb: L.unit_conv2d_workspace_bytes(ctypes.byref(_lib.ConvDesc(nb, 4, 224, 224, 4, 64, 7, 7, 2, 2, 3, 3)))
+    assert edge(41) <= cap < edge(42)
     big = _lib.ConvDesc(64, 4, 224, 224, 4, 64, 7, 7, 2, 2, 3, 3)   # needs 64 * 112 * 112 * 16 B = 12.25 MiB
     assert L.unit_conv2d_workspace_bytes(ctypes.byref(big)) > L.unit_noalloc_scratch_capacity()
     buf = torch.empty(4096, dtype=torch.uint8, device='cuda')

@@ -29,13 +29,33 @@ class ConvDesc(ctypes.Structure):
                 ('n', 'c_in', 'h', 'w', 'c_block', 'c_out', 'kh', 'kw', 'stride_h', 'stride_w', 'pad_h', 'pad_w')]
 
 
+class Epilogue(ctypes.Structure):
+    """Mirror of ``unit_epilogue``."""
+    _fields_ = [('d_bias', ctypes.c_void_p), ('mul', ctypes.c_int32), ('shift', ctypes.c_int32),
+                ('out_u8', ctypes.c_int32), ('d_residual', ctypes.c_void_p), ('x_signed', ctypes.c_int32)]
+
+
+class ConvPlan(ctypes.Structure):
+    """Mirror of ``unit_conv_plan`` (opaque bytes owned by the caller)."""
+    _fields_ = [('opaque', ctypes.c_uint64 * 128)]
+
+
+DEBUG_WAIT_LIMIT_NS = 1
+DEBUG_STALL_WEIGHT_COPIES = 2
+
 _dp = ctypes.POINTER(ConvDesc)
+_ep = ctypes.POINTER(Epilogue)
+_pp = ctypes.POINTER(ConvPlan)
 SIGNATURES = {
     'unit_version': (_ci, []),
     'unit_status_string': (ctypes.c_char_p, [_ci]),
     'unit_device_status': (_ci, [_vp]),
     'unit_launch_count': (ctypes.c_uint64, []),
     'unit_trace_attach': (_ci, [_vp, _ci]),
+    'unit_variant_count': (_ci, []),
+    'unit_variant_name': (ctypes.c_char_p, [_ci]),
+    'unit_variant_launches': (ctypes.c_uint64, [_ci]),
+    'unit_debug_set': (_ci, [_ci, ctypes.c_longlong]),
     'unit_packed_weights_bytes_conv_i8': (_sz, [_dp]),
     'unit_pack_weights_conv_i8': (_ci, [_dp, _vp, _vp, _vp]),
     'unit_packed_weights_bytes_conv_f16': (_sz, [_dp]),
@@ -47,6 +67,9 @@ SIGNATURES = {
     'unit_conv2d_workspace_bytes': (_sz, [_dp]),
     'unit_conv2d_u8s8s32_nchwc': (_ci, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     'unit_conv2d_u8s8_requant_nchwc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp, _sz, _vp]),
+    'unit_conv2d_int8_nchwc': (_ci, [_dp, _vp, _vp, _ep, _vp, _vp, _sz, _vp]),
+    'unit_conv2d_plan_int8': (_ci, [_dp, _vp, _vp, _ep, _vp, _vp, _sz, _pp]),
+    'unit_conv2d_run': (_ci, [_pp, _vp]),
     'unit_noalloc_scratch_capacity': (_sz, []),
     'unit_conv2d_u8s8_requant_nchwc_noalloc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp]),
     'unit_dense_u8s8s32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),

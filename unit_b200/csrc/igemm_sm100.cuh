@@ -77,8 +77,11 @@ __host__ __device__ constexpr bool a_mode_uses_tma(int m) { return m == A_CONV_T
 enum EpiMode : int {
   EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
   EPI_REQ_NCHWC = 1,  // + bias, round-shift, clamp -> u8 [n][oc/16][oh][ow][16]
-  EPI_RAW_ROWS = 2    // 32-bit accumulator -> row-major [m][n]
+  EPI_RAW_ROWS = 2,   // 32-bit accumulator -> row-major [m][n]
+  EPI_MUL_NCHWC = 3,  // (accumulator + s32 bias) * mul, wrapping -> s32 [n][oc/16][oh][ow][16]
+  EPI_RES_NCHWC = 4   // EPI_REQ_NCHWC with a u8 residual tensor added after the shift, before the clamp
 };
+__host__ __device__ constexpr bool epi_requantises(int e) { return e == EPI_REQ_NCHWC || e == EPI_RES_NCHWC; }
 
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 12;
@@ -91,7 +94,7 @@ constexpr uint32_t kFoldBytes = 2 * kFoldBBytes + 2 * 128 * 16;  // two sets + t
 #endif
 constexpr uint32_t kWaitHintNs = UNIT_WAIT_HINT_NS;  // longest suspension of one mbarrier probe
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
-constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4;
+constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4, kErrWaitBias = 5;
 
 // n / d for 0 <= n < 2^31 with a host-computed multiplier (mul == 0: d is a power of two).
 struct FastDiv {
@@ -141,7 +144,13 @@ struct IgemmParams {
   int row_bytes;  // bytes one row copy delivers: (box_w + KW - 1) * 16
   FastDiv div_n_tiles;      // tile index -> (row block, column block)
   long long acc_bound;  // EPI_REQ_NCHWC: upper bound of |accumulator| (255 * 128 * reduction length)
-  int fold_bias;  // 0: the drain always adds the bias (comparison runs)
+  int fold_bias;  // 0: the drain always adds the bias
+  int a_signed;   // int8 kinds: 1 = the A operand is s8 (0 = u8)
+  int mul;        // EPI_MUL_NCHWC: the s32 multiplier
+  const uint8_t *residual;  // EPI_RES_NCHWC: u8 tensor in the output's layout
+  int tmem_cols;  // TMEM columns to allocate: a power of two >= 32 that holds the accumulator sets
+  unsigned long long wait_limit_ns;  // bound of every mbarrier wait
+  int inject;     // diagnostics: 1 = the B producer issues nothing (the waits then run out)
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
 };
@@ -190,45 +199,58 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after ~1 s (or when another role already aborted).  Retries back
-// off (suspended try_wait plus a short sleep) so that waiting threads leave the issue slots
-// and the shared-memory pipe to the warps that have work.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned int *err, uint32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
+// What a bounded wait needs besides the barrier: the CTA's abort flag, the global error word and
+// the time limit (1 s in production; the diagnostics hook of the C ABI can shorten it).
+struct WaitCtx {
+  volatile int *abort_flag;
+  unsigned int *err;
+  unsigned long long limit_ns;
+};
+#ifndef UNIT_SPIN_PROBES
+#define UNIT_SPIN_PROBES 8
+#endif
+// Bounded wait: gives up after the limit (or when another role already aborted).  The first few
+// probes spin, since most waits end within a few hundred cycles; later retries back off (suspended
+// try_wait plus a short sleep) so that waiting threads leave the issue slots and the shared-memory
+// pipe to the warps that have work.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx &wc, uint32_t code) {
+#pragma unroll 1
+  for (int i = 0; i < UNIT_SPIN_PROBES; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t it = 0; it < (1u << 26); ++it) {
     if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
     __nanosleep(32);
     if ((it & 15u) == 15u) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > 1000000000ull) break;
+      if (*wc.abort_flag) return false;
+      if (global_timer_ns() - t0 > wc.limit_ns) break;
     }
   }
-  *abort_flag = 1;
-  atomicCAS(err, 0u, code);
+  *wc.abort_flag = 1;
+  atomicCAS(wc.err, 0u, code);
   return false;
 }
 // Warp-collective form, called by all 32 lanes together.  Every lane probes the barrier (one
 // warp-wide instruction on one address) and the lanes agree by vote, so the warp stays converged.
 // Measured: a warp whose lane 0 polls while the other lanes are parked at a warp-level
 // synchronisation point runs that lane markedly slower (10-20 % on whole K-loop-bound layers).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                               unsigned int *err, uint32_t code) {
-  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx &wc, uint32_t code) {
+#pragma unroll 1
+  for (int i = 0; i < UNIT_SPIN_PROBES; ++i)
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
   const unsigned long long t0 = global_timer_ns();
   bool timed_out = true;
   for (uint32_t it = 0; it < (1u << 26); ++it) {
     if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, kWaitHintNs) ? 1 : 0)) return true;
     __nanosleep(32);
     if ((it & 15u) == 15u) {
-      if (__any_sync(0xffffffffu, *abort_flag)) { timed_out = false; break; }
-      if (__any_sync(0xffffffffu, global_timer_ns() - t0 > 1000000000ull ? 1 : 0)) break;
+      if (__any_sync(0xffffffffu, *wc.abort_flag)) { timed_out = false; break; }
+      if (__any_sync(0xffffffffu, global_timer_ns() - t0 > wc.limit_ns ? 1 : 0)) break;
     }
   }
   if (timed_out && (threadIdx.x & 31) == 0) {
-    *abort_flag = 1;
-    atomicCAS(err, 0u, code);
+    *wc.abort_flag = 1;
+    atomicCAS(wc.err, 0u, code);
   }
   return false;
 }
@@ -381,6 +403,15 @@ __device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, in
   if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 16u + slot] = (unsigned long long)clock64();
 }
 
+// Kernel-level marks of CTA 0 in nanoseconds of the global timer (row 0 of the trace, slots 8-11):
+// kernel entry, prologue done, predecessor's memory visible, teardown done.
+__device__ __forceinline__ void trace_mark_ns(const IgemmParams &p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && p.trace_cap > 0) {
+    p.trace[slot] = global_timer_ns();
+    p.trace[slot + 4] = (unsigned long long)clock64();  // the same moment in SM cycles (slots 12-15)
+  }
+}
+
 // Shared-memory matrix descriptor, K-major, no swizzle.
 //   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
@@ -405,8 +436,8 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t addr) {
 // B format bits 10-12 (i8 kinds: 0 = u8, 1 = s8; f16 kind: 0 = fp16), both operands
 // K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 template <bool F16>
-__device__ __forceinline__ uint32_t make_idesc(int bn) {
-  uint32_t d = F16 ? (1u << 4) : ((2u << 4) | (0u << 7) | (1u << 10));
+__device__ __forceinline__ uint32_t make_idesc(int bn, int a_signed) {
+  uint32_t d = F16 ? (1u << 4) : ((2u << 4) | ((a_signed ? 1u : 0u) << 7) | (1u << 10));
   d |= (uint32_t)(bn >> 3) << 17;
   d |= (uint32_t)(kTileM >> 4) << 24;
   return d;
@@ -419,6 +450,7 @@ struct alignas(16) PipeShared {
   unsigned long long empty[kMaxStages];
   unsigned long long tfull[2];
   unsigned long long tempty[2];
+  unsigned long long bready[2];  // per accumulator set: the bias of the set's next tile is staged
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -426,87 +458,101 @@ struct alignas(16) PipeShared {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
+// Final step of the epilogue for 16 consecutive columns of one row: t = accumulator + bias
+// (+ rounding constant), o = the row's element offset in the output (and residual) tensor.
+// The sums cannot leave the s32 range in the requantising modes (host-side bound on |acc| plus
+// the staging check); in the s32 modes they wrap like the reference's s32 arithmetic.
+template <int EPI>
+__device__ __forceinline__ void finish_group16(const IgemmParams &p, const uint32_t *t, long long o) {
+  if constexpr (!epi_requantises(EPI)) {
+    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+    if constexpr (EPI == EPI_MUL_NCHWC) {
+      const uint32_t m = (uint32_t)p.mul;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(t[4 * q] * m, t[4 * q + 1] * m, t[4 * q + 2] * m, t[4 * q + 3] * m);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(t[4 * q], t[4 * q + 1], t[4 * q + 2], t[4 * q + 3]);
+    }
+  } else {
+    uint32_t w[4];
+    if constexpr (EPI == EPI_RES_NCHWC) {
+      // the u8 residual joins after the shift; the saturating pack is the clamp (and the ReLU)
+      const uint4 r = *reinterpret_cast<const uint4 *>(p.residual + o);
+      const uint32_t res[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int32_t x0 = ((int32_t)t[4 * q] >> p.shift) + (int32_t)(res[q] & 0xffu);
+        const int32_t x1 = ((int32_t)t[4 * q + 1] >> p.shift) + (int32_t)((res[q] >> 8) & 0xffu);
+        const int32_t x2 = ((int32_t)t[4 * q + 2] >> p.shift) + (int32_t)((res[q] >> 16) & 0xffu);
+        const int32_t x3 = ((int32_t)t[4 * q + 3] >> p.shift) + (int32_t)(res[q] >> 24);
+        w[q] = pack_sat_u8(x1, x0, pack_sat_u8(x3, x2, 0u));
+      }
+    } else if (p.shift == 8) {
+      // clamp to [0, 65535] while packing pairs, then keep the high byte of each half-word:
+      // min(max(x, 0), 65535) >> 8 == min(max(x >> 8, 0), 255)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        w[q] = __byte_perm(pack_sat_u16((int32_t)t[4 * q + 1], (int32_t)t[4 * q]),
+                           pack_sat_u16((int32_t)t[4 * q + 3], (int32_t)t[4 * q + 2]), 0x7531);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        w[q] = pack_sat_u8((int32_t)t[4 * q + 1] >> p.shift, (int32_t)t[4 * q] >> p.shift,
+                           pack_sat_u8((int32_t)t[4 * q + 3] >> p.shift, (int32_t)t[4 * q + 2] >> p.shift, 0u));
+    }
+    *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // Epilogue for 16 consecutive columns of one row: v = accumulator words, bias_s = this
 // group's 16 staged bias values in shared memory (bias + rounding constant for the
-// requantising epilogue).
+// requantising epilogues).
 template <int EPI>
 __device__ __forceinline__ void store_group16(const IgemmParams &p, const int32_t *bias_s, bool folded, bool wide,
                                               const uint32_t *v, long long o) {
   if (EPI == EPI_RAW_ROWS || folded) {
     // the accumulator is final: bias and rounding constant, if any, came in through the MMA
-    if constexpr (EPI == EPI_REQ_NCHWC) {
-      uint32_t w[4];
-      if (p.shift == 8) {
-        // clamp to [0, 65535] while packing pairs, then keep the high byte of each half-word:
-        // min(max(x, 0), 65535) >> 8 == min(max(x >> 8, 0), 255)
+    finish_group16<EPI>(p, v, o);
+    return;
+  }
+  int32_t bv[16];
+  const int4 *bp = reinterpret_cast<const int4 *>(bias_s);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          w[q] = __byte_perm(pack_sat_u16((int32_t)v[4 * q + 1], (int32_t)v[4 * q]),
-                             pack_sat_u16((int32_t)v[4 * q + 3], (int32_t)v[4 * q + 2]), 0x7531);
-      } else {
+  for (int q = 0; q < 4; ++q) {
+    const int4 t = bp[q];  // same address in every lane: a broadcast read
+    bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+  }
+  if (!epi_requantises(EPI) || !wide) {
+    uint32_t t[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          w[q] = pack_sat_u8((int32_t)v[4 * q + 1] >> p.shift, (int32_t)v[4 * q] >> p.shift,
-                             pack_sat_u8((int32_t)v[4 * q + 3] >> p.shift, (int32_t)v[4 * q + 2] >> p.shift, 0u));
-      }
-      *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
-    } else {
-      uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    for (int q = 0; q < 16; ++q) t[q] = v[q] + (uint32_t)bv[q];
+    finish_group16<EPI>(p, t, o);
+    return;
+  }
+  if constexpr (epi_requantises(EPI)) {
+    // bv holds the plain bias: 64-bit sum, for shifts and magnitudes the 32-bit path cannot take
+    const long long rnd = 1ll << (p.shift - 1);
+    uint32_t res[4] = {0u, 0u, 0u, 0u};
+    if constexpr (EPI == EPI_RES_NCHWC) {
+      const uint4 r = *reinterpret_cast<const uint4 *>(p.residual + o);
+      res[0] = r.x; res[1] = r.y; res[2] = r.z; res[3] = r.w;
     }
-  } else {
-    int32_t bv[16];
-    const int4 *bp = reinterpret_cast<const int4 *>(bias_s);
+    uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int4 t = bp[q];  // same address in every lane: a broadcast read
-      bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
-    }
-    if constexpr (EPI == EPI_RAW_NCHWC) {
-      uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint32_t *>(p.out) + o);
+      uint32_t packed = 0;
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        dst[q] = make_uint4(v[4 * q] + (uint32_t)bv[4 * q], v[4 * q + 1] + (uint32_t)bv[4 * q + 1],
-                            v[4 * q + 2] + (uint32_t)bv[4 * q + 2], v[4 * q + 3] + (uint32_t)bv[4 * q + 3]);
-    } else {
-      uint32_t w[4];
-      if (!wide) {
-        // bv holds bias + 2^(shift-1); the host-side bound on |acc| and the staging check
-        // guarantee that acc + bv cannot leave the s32 range
-        int32_t t[16];
-#pragma unroll
-        for (int q = 0; q < 16; ++q) t[q] = (int32_t)v[q] + bv[q];
-        if (p.shift == 8) {
-          // clamp to [0, 65535] while packing pairs, then keep the high byte of each half-word:
-          // min(max(x, 0), 65535) >> 8 == min(max(x >> 8, 0), 255)
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            w[q] = __byte_perm(pack_sat_u16(t[4 * q + 1], t[4 * q]), pack_sat_u16(t[4 * q + 3], t[4 * q + 2]), 0x7531);
-        } else {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            w[q] = pack_sat_u8(t[4 * q + 1] >> p.shift, t[4 * q] >> p.shift,
-                               pack_sat_u8(t[4 * q + 3] >> p.shift, t[4 * q + 2] >> p.shift, 0u));
-        }
-      } else {
-        // bv holds the plain bias: 64-bit sum, for shifts and magnitudes the 32-bit path cannot take
-        const long long rnd = 1ll << (p.shift - 1);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t packed = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            long long t = (long long)(int32_t)v[4 * q + e] + (long long)bv[4 * q + e] + rnd;
-            t >>= p.shift;
-            t = t < 0 ? 0 : (t > 255 ? 255 : t);
-            packed |= (uint32_t)t << (8 * e);
-          }
-          w[q] = packed;
-        }
+      for (int e = 0; e < 4; ++e) {
+        long long t = (long long)(int32_t)v[4 * q + e] + (long long)bv[4 * q + e] + rnd;
+        t >>= p.shift;
+        if constexpr (EPI == EPI_RES_NCHWC) t += (long long)((res[q] >> (8 * e)) & 0xffu);
+        t = t < 0 ? 0 : (t > 255 ? 255 : t);
+        packed |= (uint32_t)t << (8 * e);
       }
-      *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+      w[q] = packed;
     }
+    *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -530,7 +576,7 @@ template <int EPI>
 __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps, uint8_t *fold_mem, uint32_t slot,
                                            uint32_t version, int n_tile, int wl, int gw, int lane, bool &folded,
                                            bool &wide) {
-  constexpr bool kReq = EPI == EPI_REQ_NCHWC;
+  constexpr bool kReq = epi_requantises(EPI);
   if (!kReq && p.bias == nullptr) {  // nothing to add at all: the accumulator is final without an extra step
     folded = true;
     wide = false;
@@ -585,10 +631,9 @@ template <int AMODE, int EPI, bool F16, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) uint8_t smem[];  // (1 KB: a swizzled operand atom is 8 rows x 128 bytes)
-  // let the next kernel of the stream start its own prologue as soon as SMs become free
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  trace_mark_ns(p, 8);
 
   constexpr uint32_t kSubBytes = kTileM * 16u;                       // one K column of one 128-row sub-tile
   const uint32_t a_sub_bytes = (uint32_t)p.kc * kSubBytes;           // one sub-tile of one stage
@@ -598,6 +643,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes + kFoldBytes);
   const uint32_t smem_base = smem_u32(smem);
   volatile int *abort_flag = &ps->abort_flag;
+  const WaitCtx wc{abort_flag, p.err, p.wait_limit_ns};
   // accumulator sets that fit in the 512 TMEM columns (2 = drain overlaps the next main loop)
   const uint32_t nslots = (512u / ((uint32_t)MT * (uint32_t)p.bn)) >= 2u ? 2u : 1u;
 
@@ -610,12 +656,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ps->tfull[i]), 1 + MT);        // the first issuing thread's arrival + one commit per issuer
       mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps / nslots);  // the drain warps that serve the set
+      mbar_init(smem_u32(&ps->bready[i]), kDrainWarps / nslots);
     }
     ps->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&ps->tmem_base), 512);
+    tmem_alloc(smem_u32(&ps->tmem_base), (uint32_t)p.tmem_cols);
     tmem_relinquish();
     if constexpr (!F16 && EPI != EPI_RAW_ROWS) {
       // the constant A block of the bias step: column 0 = bytes {1, 128 x 15} in every row, column 1 = zeros
@@ -629,11 +676,17 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ps->tmem_base;
+  // From here on this CTA holds its tensor memory, so a dependent kernel's CTA that becomes
+  // resident on the same SM can never be the one that keeps this CTA waiting in tcgen05.alloc:
+  // let the next kernel of the stream start its own prologue as soon as SMs become free.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  trace_mark_ns(p, 9);
   // Programmatic dependent launch: everything above touched only this CTA's shared memory and
   // TMEM, so it may run while the previous kernel in the stream is still finishing; from here
   // on global memory is read and written, which has to wait for that kernel's completion.
   // (A no-op when the kernel was launched without the attribute.)
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  trace_mark_ns(p, 10);
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
@@ -682,7 +735,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 0);
       int ci = 0, kh = 0, kw = 0;  // position of the next K column (conv modes)
       for (int ks = 0; ks < p.k_stages; ++ks) {
-        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
+        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
           break;
         }
@@ -829,7 +882,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
       const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
       for (int ks = 0; ks < p.k_stages; ++ks) {
-        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
+        if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
           break;
         }
@@ -886,7 +939,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
   } else if (warp == kBWarp) {
     // ===================== B producer =====================
-    if (lane == 0) {
+    // (p.inject: diagnostics.  The producer issues nothing, so no stage ever completes and the
+    // bounded waits of the other roles run out: the path that reports UNIT_ERR_DEVICE_WAIT.)
+    if (lane == 0 && p.inject == 0) {
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;
       bool alive = true;
@@ -894,7 +949,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const int n_tile = tile - (int)fast_div((uint32_t)tile, p.div_n_tiles) * p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, abort_flag, p.err, kErrWaitEmpty)) {
+          if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
             alive = false;
             break;
           }
@@ -919,7 +974,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const uint32_t fold_base = smem_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
     const uint32_t my_t = warp == kMmaWarp ? 0u : 1u;  // the sub-tile this thread issues for
     if (lane == 0) {
-      const uint32_t idesc = make_idesc<F16>(p.bn);
+      const uint32_t idesc = make_idesc<F16>(p.bn, p.a_signed);
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
       const uint64_t a_desc_row = make_smem_desc(0u, 16u, 128u);  // row form: K columns 16 bytes apart
       const uint64_t a_desc_sw = make_smem_desc_sw128(0u);         // dense matrices in the swizzled layout
@@ -935,8 +990,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
         const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
         const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
-        // the drain warps arrive once before the set's first use (bias prepared) and once after every drain
-        if (!mbar_wait(smem_u32(&ps->tempty[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
+        // the drain warps arrive on "empty" after every drain of the set: its first use needs no wait
+        if (use > 0u && !mbar_wait(smem_u32(&ps->tempty[slot]), (use - 1u) & 1u, wc, kErrWaitTmemEmpty)) {
           alive = false;
           break;
         }
@@ -944,16 +999,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (my_t == 0u) trace_mark(p, lt, 3);
         const uint32_t d_tmem = tmem_base + (slot * (uint32_t)MT + my_t) * (uint32_t)p.bn;  // this thread's accumulator
         uint32_t started = 0u;
-        if constexpr (kCanFold) {
-          if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0) {
-            const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
-            const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
-            tc_mma<F16>(d_tmem, adesc, bdesc, idesc, 0u);
-            started = 1u;
-          }
-        }
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, abort_flag, p.err, kErrWaitFull)) {
+          if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull)) {
             alive = false;
             break;
           }
@@ -995,6 +1042,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
         if (alive) {
+          if constexpr (kCanFold) {
+            // The bias step comes last: the drain warps stage the set's bias while the main loop
+            // runs (for a CTA's first tiles that is the whole of global-memory latency), and integer
+            // sums do not depend on the order of their terms.
+            if (!mbar_wait(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0) {
+              const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
+              const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
+              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+            }
+          }
           // "accumulators ready" completes with every issuer's commit plus one plain arrival (a
           // release that passes the drain warps' bias integers on to whichever warp reads them)
           if (my_t == 0u) mbar_arrive(smem_u32(&ps->tfull[slot]));
@@ -1042,15 +1104,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     bool folded = true, wide = false;
     uint32_t ver = 0;
     const int first_tile = blockIdx.x + (int)slot * (int)gridDim.x;
-    // before the set's first use: prepare its bias, then hand the set to the MMA warp
+    // before the set's first use: stage its bias (the MMA warp runs the main loop meanwhile)
     if constexpr (kCanFold) {
       if (first_tile < total_tiles) {
         staged_n = first_tile - (int)fast_div((uint32_t)first_tile, p.div_n_tiles) * p.n_tiles;
         stage_bias<EPI>(p, ps, fold_mem, slot, ver, staged_n, wl, gw, lane, folded, wide);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ps->bready[slot]));
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
     uint32_t use = 0;  // how many tiles this group has drained
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++use) {
       const uint32_t lt = use * nslots + slot;  // the CTA's tile counter, for the trace
@@ -1081,7 +1143,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
       }
       const int32_t *tile_bias = &ps->bias[slot][ver][0];
-      if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, abort_flag, p.err, kErrWaitTmemFull)) break;
+      if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, wc, kErrWaitTmemFull)) break;
       tc_fence_after();
       if (wl == 0 && lane == 0) trace_mark(p, lt, 6);
       const uint32_t t_row =
@@ -1102,7 +1164,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (has_b && mvalid) store_group16<EPI>(p, tile_bias + (g + 1) * 16, folded, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait();
       }
-      // prepare the set for the group's next tile, unless that tile has the same column block
+      // the accumulator set is free again: the MMA warp may start the set's next main loop
+      tc_fence_before();
+      __syncwarp();
+      if (wl == 0 && lane == 0) trace_mark(p, lt, 7);
+      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
+      // stage the bias of the group's next tile, unless that tile has the same column block
       if constexpr (kCanFold) {
         const int next = tile + tile_step;
         if (next < total_tiles) {
@@ -1113,11 +1180,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             staged_n = nt;
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ps->bready[slot]));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (wl == 0 && lane == 0) trace_mark(p, lt, 7);
-      if (lane == 0) mbar_arrive(smem_u32(&ps->tempty[slot]));
     }
   }
 
@@ -1131,8 +1196,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
+  trace_mark_ns(p, 11);
 }
 
 }  // namespace unit

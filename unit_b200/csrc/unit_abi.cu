@@ -7,7 +7,9 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "igemm_sm100.cuh"
@@ -36,6 +38,19 @@ constexpr size_t kSmemBudget = 200 * 1024;
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// Tile-shape and path overrides exist only in experiment builds (-DUNIT_B200_TUNING): the shipped
+// library reads no environment variable, so a packed weight buffer depends on nothing but the
+// arguments of its pack call.
+static int tuning_int(const char *name, int dflt) {
+#ifdef UNIT_B200_TUNING
+  const char *e = getenv(name);
+  return e ? atoi(e) : dflt;
+#else
+  (void)name;
+  return dflt;
+#endif
+}
+
 // Depends on the weight tensor only (never on the batch), so packed weights stay valid
 // for every input size.  kc is chosen so that four stages of the larger (two sub-tile)
 // CTA tile fit in shared memory.
@@ -47,10 +62,9 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
   // each tile's drain (about 2.7 k cycles) is exposed; that is paid back by the halved weight
   // traffic only when the reduction is long.  Measured at batch 256: reductions of 128..1024
   // bytes (8..64 columns) run 8-13 % faster with 128-wide blocks (two sets, drain overlapped),
-  // longer ones 15-50 % slower.  UNIT_B200_BN overrides (experiments).
+  // longer ones 15-50 % slower.
   static const int forced_bn = [] {
-    const char *e = getenv("UNIT_B200_BN");
-    const int v = e ? atoi(e) : 0;
+    const int v = tuning_int("UNIT_B200_BN", 0);
     return (v >= 16 && v <= 256 && v % 16 == 0) ? v : 0;
   }();
   // (cheap_a = false: the A operand comes through the slower im2col copies, where fetching it
@@ -61,9 +75,8 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
   const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
   static const int cand[] = {8, 6, 4, 12, 10, 14, 16};
-  static const int forced_kc = [] {  // UNIT_B200_KC: preferred stage depth in columns (experiments)
-    const char *e = getenv("UNIT_B200_KC");
-    const int v = e ? atoi(e) : 0;
+  static const int forced_kc = [] {
+    const int v = tuning_int("UNIT_B200_KC", 0);
     return (v >= 2 && v <= 16 && v % 2 == 0) ? v : 0;
   }();
   c.kc = 0;
@@ -96,10 +109,7 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
 // the A operand is the bottleneck (im2col copies: slow_a) a single sub-tile costs nothing extra,
 // so it is taken when it fills the last round of tiles markedly better.  Measured at batch 256.
 static int choose_mt(const TileCfg &c, long long m_total, int sms, bool slow_a) {
-  static const int forced = [] {
-    const char *e = getenv("UNIT_B200_MT");
-    return e ? atoi(e) : 0;
-  }();
+  static const int forced = tuning_int("UNIT_B200_MT", 0);
   if (forced == 1 || forced == 2) return forced;
   const long long tiles2 = (m_total + 2 * kTileM - 1) / (2 * kTileM) * c.n_tiles;
   const long long tiles1 = (m_total + kTileM - 1) / kTileM * c.n_tiles;
@@ -401,65 +411,99 @@ __global__ void fold2x2_kernel(const uint2 *__restrict__ src, uint4 *__restrict_
 // ---------------------------------------------------------------------------
 // launches of the contraction kernel
 // ---------------------------------------------------------------------------
-// UNIT_B200_ROW=0 keeps one copy per tap for the folded stem (for comparison runs).
+// Experiment builds: UNIT_B200_ROW=0 keeps one copy per tap for the folded stem.
 static bool use_row_form() {
-  static const int v = [] {
-    const char *e = getenv("UNIT_B200_ROW");
-    return e ? atoi(e) : 1;
-  }();
+  static const int v = tuning_int("UNIT_B200_ROW", 1);
   return v != 0;
 }
 
-// UNIT_B200_PDL=0 launches the contraction kernels fully serialised (for comparison runs).
+// Experiment builds: UNIT_B200_PDL=0 launches the contraction kernels fully serialised.
 static bool use_pdl() {
-  static const int v = [] {
-    const char *e = getenv("UNIT_B200_PDL");
-    return e ? atoi(e) : 1;
-  }();
+  static const int v = tuning_int("UNIT_B200_PDL", 1);
   return v != 0;
 }
 
-// UNIT_B200_FOLD=0 makes the drain add every bias (for comparison runs); the default lets the tensor core do it.
+// Experiment builds: UNIT_B200_FOLD=0 makes the drain add every bias; the default lets the tensor core do it.
 static bool use_fold() {
-  static const int v = [] {
-    const char *e = getenv("UNIT_B200_FOLD");
-    return e ? atoi(e) : 1;
-  }();
+  static const int v = tuning_int("UNIT_B200_FOLD", 1);
   return v != 0;
 }
+
+// ---------------------------------------------------------------------------
+// kernel variants: one slot per instantiated igemm_kernel<AMODE, EPI, F16, MT>
+// ---------------------------------------------------------------------------
+constexpr int kNumAModes = 7, kNumEpis = 5;
+constexpr int kMaxVariants = kNumAModes * kNumEpis * 2 * 2;
+struct VariantSlot {
+  char name[72];
+  bool present;
+  std::atomic<uint64_t> launches;
+  std::atomic<bool> attr_done[64];  // per device: the kernel's dynamic shared-memory limit is raised
+};
+static VariantSlot *variant_table() {
+  static VariantSlot table[kMaxVariants];  // static storage: zero-initialised
+  return table;
+}
+static bool register_variant(int index, int amode, int epi, bool f16, int mt) {
+  static const char *const amodes[kNumAModes] = {"A_CONV_I8", "A_CONV_F16", "A_STEM_I8", "A_DENSE", "A_CONV_TMA", "A_CONV_BOX", "A_DENSE_TMA"};
+  static const char *const epis[kNumEpis] = {"EPI_RAW_NCHWC", "EPI_REQ_NCHWC", "EPI_RAW_ROWS", "EPI_MUL_NCHWC", "EPI_RES_NCHWC"};
+  VariantSlot &v = variant_table()[index];
+  snprintf(v.name, sizeof(v.name), "igemm_kernel<%s, %s, %s, MT=%d>", amodes[amode], epis[epi], f16 ? "f16" : "i8", mt);
+  v.present = true;
+  return true;
+}
+template <int AMODE, int EPI, bool F16, int MT>
+struct Variant {
+  static constexpr int index = ((AMODE * kNumEpis + EPI) * 2 + (F16 ? 1 : 0)) * 2 + (MT - 1);
+  static const bool registered;  // set while the library is loaded, so that never-launched variants are listed too
+};
+template <int AMODE, int EPI, bool F16, int MT>
+const bool Variant<AMODE, EPI, F16, MT>::registered = register_variant(Variant<AMODE, EPI, F16, MT>::index, AMODE, EPI, F16, MT);
+
+// ---------------------------------------------------------------------------
+// launch plans
+// ---------------------------------------------------------------------------
+// Everything one contraction launch needs, as plain data without pointers into the library's own
+// memory except the kernel's entry and the error word: the filled kernel parameters, the tensor
+// map, the grid.  Every entry point fills one on its stack and runs it; unit_conv2d_plan_int8
+// hands one to the caller (unit_conv_plan), so that repeated calls on the same buffers skip the
+// argument checks, the tile selection and the tensor-map encoding.
+constexpr uint32_t kPlanMagic = 0x756e6974u;
+struct PlanImpl {
+  uint32_t magic;
+  int32_t variant, device;
+  uint32_t grid, smem_bytes;
+  int32_t fold_n, fold_h2, fold_w2;  // fold_n > 0: the stem's 2 x 2 fold into scratch runs first
+  const void *fold_src;
+  void *fold_dst;
+  const void *kernel;
+  IgemmParams p;
+  unsigned char map[sizeof(CUtensorMap)];
+};
+static_assert(sizeof(PlanImpl) <= sizeof(unit_conv_plan), "unit_conv_plan too small for the launch plan");
+
+static std::atomic<unsigned long long> g_wait_limit_ns{1000000000ull};
+static std::atomic<int> g_inject{0};
 
 template <int AMODE, int EPI, bool F16, int MT>
-static int launch_igemm_mt(IgemmParams &p, const TileCfg &c, cudaStream_t st, int sms, const CUtensorMap &tmap) {
-  static std::once_flag once[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  auto kern = igemm_kernel<AMODE, EPI, F16, MT>;
-  cudaError_t attr_err = cudaSuccess;
-  std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  });
-  if (attr_err != cudaSuccess) return UNIT_ERR_LAUNCH;
+static int prepare_mt(PlanImpl &pl, const TileCfg &c, int sms) {
+  if (!Variant<AMODE, EPI, F16, MT>::registered) return UNIT_ERR_LAUNCH;
+  IgemmParams &p = pl.p;
+  pl.variant = Variant<AMODE, EPI, F16, MT>::index;
+  pl.kernel = reinterpret_cast<const void *>(igemm_kernel<AMODE, EPI, F16, MT>);
   size_t smem_bytes = 0;
   p.stages = stages_for(c, MT, &smem_bytes);
+  pl.smem_bytes = (uint32_t)smem_bytes;
   p.m_tiles = (int)((p.m_total + kTileM * MT - 1) / (kTileM * MT));
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  // launched with programmatic stream serialisation: the kernel's prologue (barrier set-up,
-  // TMEM allocation) may overlap the tail of the previous kernel in the stream; the kernel waits
-  // for that kernel's completion (griddepcontrol.wait) before it touches global memory
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kNumThreads);
-  cfg.dynamicSmemBytes = smem_bytes;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = use_pdl() ? 1 : 0;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p, tmap);
-  g_launches.fetch_add(1);
-  return (le == cudaSuccess && cudaGetLastError() == cudaSuccess) ? UNIT_OK : UNIT_ERR_LAUNCH;
+  pl.grid = (unsigned)(tiles < sms ? tiles : sms);
+  // tensor memory: a power of two of columns that holds the accumulator sets (the kernel derives the
+  // same number of sets from MT and bn)
+  const int sets = (512 / (MT * c.bn)) >= 2 ? 2 : 1;
+  int cols = 32;
+  while (cols < sets * MT * c.bn) cols *= 2;
+  p.tmem_cols = cols;
+  return UNIT_OK;
 }
 
 static FastDiv make_fast_div(uint32_t d);
@@ -480,10 +524,13 @@ static unsigned int *error_word_address() {
   return cached[dev];
 }
 
+// Fills the tile fields of the plan's parameters and picks the sub-tile count.  max_mt = 1 for
+// operand paths that only small problems reach.
 template <int AMODE, int EPI, bool F16>
-static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const CUtensorMap *tmap_in = nullptr) {
-  static const CUtensorMap no_map{};
-  const CUtensorMap &tmap = tmap_in ? *tmap_in : no_map;
+static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = nullptr, int max_mt = 2) {
+  IgemmParams &p = pl.p;
+  if (tmap_in) memcpy(pl.map, tmap_in, sizeof(CUtensorMap));
+  else memset(pl.map, 0, sizeof(pl.map));
   p.bn = c.bn;
   p.kc = c.kc;
   p.cols = c.cols;
@@ -493,12 +540,71 @@ static int launch_igemm(IgemmParams &p, const TileCfg &c, cudaStream_t st, const
   p.div_n_tiles = make_fast_div((uint32_t)c.n_tiles);
   p.err = error_word_address();
   if (p.err == nullptr) return UNIT_ERR_LAUNCH;
-  p.fold_bias = use_fold() ? 1 : 0;
+  if (cudaGetDevice(&pl.device) != cudaSuccess) return UNIT_ERR_LAUNCH;
+  if (p.a_signed == 0) p.fold_bias = use_fold() ? 1 : 0;  // (the bias step's constant block is u8)
+  const int sms = sm_count();
+  pl.magic = kPlanMagic;
+  if (max_mt >= 2 && choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2>(pl, c, sms);
+  return prepare_mt<AMODE, EPI, F16, 1>(pl, c, sms);
+}
+
+// The int8 convolution's epilogue is chosen at run time: one instantiation per mode.
+template <int AMODE>
+static int prepare_conv_i8(PlanImpl &pl, const TileCfg &c, int epi, const CUtensorMap *tmap = nullptr) {
+  switch (epi) {
+    case EPI_RAW_NCHWC: return prepare<AMODE, EPI_RAW_NCHWC, false>(pl, c, tmap);
+    case EPI_REQ_NCHWC: return prepare<AMODE, EPI_REQ_NCHWC, false>(pl, c, tmap);
+    case EPI_MUL_NCHWC: return prepare<AMODE, EPI_MUL_NCHWC, false>(pl, c, tmap);
+    case EPI_RES_NCHWC: return prepare<AMODE, EPI_RES_NCHWC, false>(pl, c, tmap);
+    default: return UNIT_ERR_SHAPE;
+  }
+}
+
+static int run_plan(const PlanImpl &pl, cudaStream_t st) {
+  if (pl.magic != kPlanMagic || pl.variant < 0 || pl.variant >= kMaxVariants) return UNIT_ERR_SHAPE;
+  VariantSlot &v = variant_table()[pl.variant];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != pl.device || dev < 0) return UNIT_ERR_LAUNCH;
+  if (!v.attr_done[dev & 63].load(std::memory_order_acquire)) {
+    // not latched on failure: the next call tries again
+    if (cudaFuncSetAttribute(pl.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return UNIT_ERR_LAUNCH;
+    }
+    v.attr_done[dev & 63].store(true, std::memory_order_release);
+  }
+  if (pl.fold_n > 0) {
+    const long long total = (long long)pl.fold_n * pl.fold_h2 * pl.fold_w2;
+    fold2x2_kernel<<<grid_for(total), 256, 0, st>>>(static_cast<const uint2 *>(pl.fold_src), static_cast<uint4 *>(pl.fold_dst),
+                                                    pl.fold_n, pl.fold_h2, pl.fold_w2);
+    g_launches.fetch_add(1);
+    if (cudaGetLastError() != cudaSuccess) return UNIT_ERR_LAUNCH;
+  }
+  IgemmParams p = pl.p;
   p.trace = g_trace.load();
   p.trace_cap = g_trace_cap.load();
-  const int sms = sm_count();
-  if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return launch_igemm_mt<AMODE, EPI, F16, 2>(p, c, st, sms, tmap);
-  return launch_igemm_mt<AMODE, EPI, F16, 1>(p, c, st, sms, tmap);
+  p.wait_limit_ns = g_wait_limit_ns.load();
+  p.inject = g_inject.load();
+  alignas(64) CUtensorMap map;
+  memcpy(&map, pl.map, sizeof(map));
+  // launched with programmatic stream serialisation: the kernel's prologue (barrier set-up,
+  // TMEM allocation) may overlap the tail of the previous kernel in the stream; the kernel waits
+  // for that kernel's completion (griddepcontrol.wait) before it touches global memory
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = use_pdl() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void *args[2] = {&p, &map};
+  const cudaError_t le = cudaLaunchKernelExC(&cfg, pl.kernel, args);
+  g_launches.fetch_add(1);
+  v.launches.fetch_add(1);
+  return (le == cudaSuccess && cudaGetLastError() == cudaSuccess) ? UNIT_OK : UNIT_ERR_LAUNCH;
 }
 
 // Multiplier for n / d, valid for 0 <= n < 2^31: q = umulhi(n, mul) >> shr (mul == 0: shift only).
@@ -515,6 +621,14 @@ static FastDiv make_fast_div(uint32_t d) {
   }
   return f;
 }
+
+// Tensors smaller than 128 KB are never described by a tensor map.  For such tensors, with
+// drivers up to CUDA 13.1, CUTLASS edits the descriptor that cuTensorMapEncodeTiled /
+// cuTensorMapEncodeIm2col return (cute/atom/copy_traits_sm90_tma.hpp and
+// copy_traits_sm90_im2col.hpp clear one bit of its second word when the tensor's extent is below
+// 131072 bytes); the descriptor is opaque and this library does not edit it, so operands below that
+// size take the cp.async gather instead, which loses nothing on problems that small.
+static bool tensor_map_allowed(long long tensor_bytes) { return tensor_bytes >= 131072; }
 
 // im2col-mode tensor map over NCHW16c activations, seen as the 5-D tensor
 //   (c = 16 channels of a chunk, w, h, d = image, n = channel chunk)
@@ -534,8 +648,7 @@ static bool make_im2col_map(CUtensorMap *map, const unit_conv_desc *d, const voi
     return reinterpret_cast<EncodeFn>(fn);
   }();
   if (!encode) return false;
-  // small tensors stay on the cp.async path (the driver needs a descriptor fix-up for them)
-  if ((long long)d->n * d->c_in * d->h * d->w * (f16 ? 2 : 1) < 131072) return false;
+  if (!tensor_map_allowed((long long)d->n * d->c_in * d->h * d->w * (f16 ? 2 : 1))) return false;
   if (d->c_block != 16 || d->pad_w > 15 || d->pad_h > 15 || d->kw > 16 || d->kh > 16 || d->stride_w > 8 || d->stride_h > 8)
     return false;
   const cuuint64_t eb = f16 ? 2 : 1;
@@ -598,7 +711,7 @@ static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const 
       fn = nullptr;
     return reinterpret_cast<EncodeFn>(fn);
   }();
-  if (!encode) return false;
+  if (!encode || !tensor_map_allowed((long long)n * c_in * h * w)) return false;
   const cuuint64_t cc = (cuuint64_t)c_in / 16;
   const cuuint64_t dims[4] = {(cuuint64_t)w * 2, (cuuint64_t)h, cc, (cuuint64_t)n};
   const cuuint64_t row = (cuuint64_t)w * 16;
@@ -628,6 +741,7 @@ static bool make_dense_map(CUtensorMap *map, const void *a, long long rows, long
     return reinterpret_cast<EncodeFn>(fn);
   }();
   if (!encode || ld >= (1ll << 40) || rows > 0x7fffffffll - 512) return false;
+  if (!tensor_map_allowed((rows - 1) * ld + row_bytes)) return false;
   const cuuint64_t dims[3] = {2, (cuuint64_t)(row_bytes / 16), (cuuint64_t)rows};
   const cuuint64_t strides[2] = {16, (cuuint64_t)ld};
   const cuuint32_t box[3] = {2, 1, 128};
@@ -654,7 +768,7 @@ static bool make_box_map_f16(CUtensorMap *map, int n, int c_in, int h, int w, co
       fn = nullptr;
     return reinterpret_cast<EncodeFn>(fn);
   }();
-  if (!encode) return false;
+  if (!encode || !tensor_map_allowed(2ll * n * c_in * h * w)) return false;
   const cuuint64_t cc = (cuuint64_t)c_in / 16;
   const cuuint64_t dims[5] = {4, (cuuint64_t)w, (cuuint64_t)h, cc, (cuuint64_t)n};
   const cuuint64_t row = (cuuint64_t)w * 32;
@@ -684,6 +798,7 @@ static bool make_dense_map_sw128(CUtensorMap *map, const void *a, long long rows
     return reinterpret_cast<EncodeFn>(fn);
   }();
   if (!encode || ld >= (1ll << 40) || rows > 0x7fffffffll - 512 || row_bytes >= (1ll << 31)) return false;
+  if (!tensor_map_allowed((rows - 1) * ld + row_bytes)) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld};
   const cuuint32_t box[2] = {128, 128};
@@ -694,21 +809,15 @@ static bool make_dense_map_sw128(CUtensorMap *map, const void *a, long long rows
   return r == CUDA_SUCCESS;
 }
 
-// UNIT_B200_SW128=0 keeps the column copies for plain matrices (for comparison runs).
+// Experiment builds: UNIT_B200_SW128=0 keeps the column copies for plain matrices.
 static bool use_sw128() {
-  static const int v = [] {
-    const char *e = getenv("UNIT_B200_SW128");
-    return e ? atoi(e) : 1;
-  }();
+  static const int v = tuning_int("UNIT_B200_SW128", 1);
   return v != 0;
 }
 
-// The im2col TMA path is the default; UNIT_B200_TMA=0 selects the cp.async gather (for comparison runs).
+// Experiment builds: UNIT_B200_TMA=0 selects the cp.async gather everywhere.
 static bool use_tma() {
-  static const int v = [] {
-    const char *e = getenv("UNIT_B200_TMA");
-    return e ? atoi(e) : 1;
-  }();
+  static const int v = tuning_int("UNIT_B200_TMA", 1);
   return v != 0;
 }
 
@@ -742,19 +851,33 @@ static size_t stem_workspace_bytes(const unit_conv_desc *d) {
   return f.ok ? (size_t)d->n * f.h2 * f.w2 * 16 : 0;
 }
 
-static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias, int shift,
-                   void *out, bool requant, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+// The int8 convolution's epilogue as the entry points describe it.
+struct EpilogueArgs {
+  const int32_t *bias = nullptr;
+  int mul = 1;                      // s32 output only
+  int shift = 0;                    // u8 output only
+  bool out_u8 = false;
+  const uint8_t *residual = nullptr;  // u8 output only
+  bool x_signed = false;
+};
+
+static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, const void *pw, const EpilogueArgs &e,
+                        void *out, void *workspace, size_t workspace_bytes) {
   int rc = check_conv(d, false);
   if (rc) return rc;
   if (!x || !pw || !out) return UNIT_ERR_NULL;
-  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (bias && !aligned16(bias)) ||
-      (workspace && !aligned16(workspace)))
+  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (e.bias && !aligned16(e.bias)) ||
+      (workspace && !aligned16(workspace)) || (e.residual && !aligned16(e.residual)))
     return UNIT_ERR_ALIGN;
-  if (requant && (shift < 1 || shift > 31)) return UNIT_ERR_SHAPE;
+  if (e.out_u8 && (e.shift < 1 || e.shift > 31 || e.mul != 1)) return UNIT_ERR_SHAPE;
+  if (!e.out_u8 && (e.residual != nullptr || e.shift != 0)) return UNIT_ERR_SHAPE;
   if ((rc = check_arch())) return rc;
+  const int epi = e.out_u8 ? (e.residual ? EPI_RES_NCHWC : EPI_REQ_NCHWC) : (e.mul != 1 ? EPI_MUL_NCHWC : EPI_RAW_NCHWC);
   const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
-  IgemmParams p{};
-  p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = bias; p.shift = shift;
+  pl = PlanImpl{};
+  IgemmParams &p = pl.p;
+  p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = e.bias; p.shift = e.shift;
+  p.mul = e.mul; p.residual = e.residual; p.a_signed = e.x_signed ? 1 : 0;
   fill_conv(p, d, 1);
   p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
   CUtensorMap map;
@@ -764,49 +887,48 @@ static int conv_i8(const unit_conv_desc *d, const uint8_t *x, const void *pw, co
       const BoxGeom g = choose_box(d->n, p.OH, p.OW);
       if (make_box_map(&map, d->n, d->c_in, d->h, d->w, x, g)) {
         set_box(p, g, d->n);
-        return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(p, c, st, &map)
-                       : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(p, c, st, &map);
+        return prepare_conv_i8<A_CONV_BOX>(pl, c, epi, &map);
       }
     }
-    if (use_tma() && make_im2col_map(&map, d, x, false))
-      return requant ? launch_igemm<A_CONV_TMA, EPI_REQ_NCHWC, false>(p, c, st, &map)
-                     : launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, false>(p, c, st, &map);
-    return requant ? launch_igemm<A_CONV_I8, EPI_REQ_NCHWC, false>(p, c, st)
-                   : launch_igemm<A_CONV_I8, EPI_RAW_NCHWC, false>(p, c, st);
+    if (use_tma() && make_im2col_map(&map, d, x, false)) return prepare_conv_i8<A_CONV_TMA>(pl, c, epi, &map);
+    return prepare_conv_i8<A_CONV_I8>(pl, c, epi);
   }
   // NCHW4c.  With scratch memory a stride-2 stem runs as a stride-1 convolution on 2x2-folded
   // pixels (whole pixel rows per copy); otherwise the 4-byte gather does it in place.
   const StemFold f = stem_fold(d, true);
   const size_t need = stem_workspace_bytes(d);
   if (use_tma() && f.ok && workspace != nullptr && workspace_bytes >= need) {
-    const long long total = (long long)d->n * f.h2 * f.w2;
-    fold2x2_kernel<<<grid_for(total), 256, 0, st>>>(reinterpret_cast<const uint2 *>(x),
-                                                    static_cast<uint4 *>(workspace), d->n, f.h2, f.w2);
-    g_launches.fetch_add(1);
-    if (cudaGetLastError() != cudaSuccess) return UNIT_ERR_LAUNCH;
     const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
     const size_t generic_bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
-    IgemmParams q = p;  // OH, OW, output geometry and epilogue stay; the input side changes
-    q.a = static_cast<const uint8_t *>(workspace);
-    q.b = static_cast<const uint8_t *>(pw) + generic_bytes;
-    q.H = f.h2; q.W = f.w2; q.Cc = 1; q.KH = f.th; q.KW = f.tw; q.sh = q.sw = 1; q.ph = f.pad_h; q.pw = f.pad_w;
-    q.img_bytes = (long long)f.h2 * f.w2 * 16;
-    const BoxGeom g = choose_box(d->n, q.OH, q.OW);
+    PlanImpl q = pl;  // OH, OW, output geometry and epilogue stay; the input side changes
+    q.p.a = static_cast<const uint8_t *>(workspace);
+    q.p.b = static_cast<const uint8_t *>(pw) + generic_bytes;
+    q.p.H = f.h2; q.p.W = f.w2; q.p.Cc = 1; q.p.KH = f.th; q.p.KW = f.tw; q.p.sh = q.p.sw = 1; q.p.ph = f.pad_h; q.p.pw = f.pad_w;
+    q.p.img_bytes = (long long)f.h2 * f.w2 * 16;
+    const BoxGeom g = choose_box(d->n, q.p.OH, q.p.OW);
     // row form (one copy per kernel row instead of one per tap) when a sub-tile is a single row
     // segment, the kernel width is even (column pairs stay inside a kernel row) and the stages
     // hold whole kernel rows
     const bool row_form = use_row_form() && g.bn == 1 && g.bh == 1 && f.tw % 2 == 0 && cf.kc % f.tw == 0 &&
                           cf.cols % cf.kc == 0 && (g.bw + f.tw - 1) * 2 <= 256;
     if (make_box_map(&map, d->n, 16, f.h2, f.w2, workspace, g, row_form ? f.tw - 1 : 0)) {
-      set_box(q, g, d->n);
-      q.row_kw = row_form ? f.tw : 0;
-      q.row_bytes = (g.bw + f.tw - 1) * 16;
-      return requant ? launch_igemm<A_CONV_BOX, EPI_REQ_NCHWC, false>(q, cf, st, &map)
-                     : launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, false>(q, cf, st, &map);
+      set_box(q.p, g, d->n);
+      q.p.row_kw = row_form ? f.tw : 0;
+      q.p.row_bytes = (g.bw + f.tw - 1) * 16;
+      q.fold_n = d->n; q.fold_h2 = f.h2; q.fold_w2 = f.w2;
+      q.fold_src = x; q.fold_dst = workspace;
+      pl = q;
+      return prepare_conv_i8<A_CONV_BOX>(pl, cf, epi, &map);
     }
   }
-  return requant ? launch_igemm<A_STEM_I8, EPI_REQ_NCHWC, false>(p, c, st)
-                 : launch_igemm<A_STEM_I8, EPI_RAW_NCHWC, false>(p, c, st);
+  return prepare_conv_i8<A_STEM_I8>(pl, c, epi);
+}
+
+static int conv_i8(const unit_conv_desc *d, const void *x, const void *pw, const EpilogueArgs &e, void *out,
+                   void *workspace, size_t workspace_bytes, cudaStream_t st) {
+  PlanImpl pl;
+  const int rc = plan_conv_i8(pl, d, x, pw, e, out, workspace, workspace_bytes);
+  return rc ? rc : run_plan(pl, st);
 }
 
 // Device address of g_static_scratch on the current device.  In host code the array's name is
@@ -870,6 +992,32 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles) {
   g_trace_cap.store(d_buf ? capacity_tiles : 0);
   g_trace.store(static_cast<unsigned long long *>(d_buf));
   return UNIT_OK;
+}
+
+int unit_variant_count(void) { return kMaxVariants; }
+
+const char *unit_variant_name(int index) {
+  if (index < 0 || index >= kMaxVariants || !variant_table()[index].present) return nullptr;
+  return variant_table()[index].name;
+}
+
+uint64_t unit_variant_launches(int index) {
+  if (index < 0 || index >= kMaxVariants) return 0;
+  return variant_table()[index].launches.load();
+}
+
+int unit_debug_set(int key, long long value) {
+  switch (key) {
+    case UNIT_DEBUG_WAIT_LIMIT_NS:
+      if (value < 1000 || value > 60000000000ll) return UNIT_ERR_SHAPE;
+      g_wait_limit_ns.store((unsigned long long)value);
+      return UNIT_OK;
+    case UNIT_DEBUG_STALL_WEIGHT_COPIES:
+      g_inject.store(value != 0 ? 1 : 0);
+      return UNIT_OK;
+    default:
+      return UNIT_ERR_SHAPE;
+  }
 }
 
 // ---- packed weights --------------------------------------------------------
@@ -982,13 +1130,57 @@ int unit_pack_weights_gemm_f16(int32_t n, int32_t k, const void *b, void *packed
 // ---- contractions ------------------------------------------------------------
 int unit_conv2d_u8s8s32_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
                               int32_t *out, void *workspace, size_t workspace_bytes, void *stream) {
-  return conv_i8(d, x, pw, bias, 0, out, false, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  EpilogueArgs e;
+  e.bias = bias;
+  return conv_i8(d, x, pw, e, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int unit_conv2d_u8s8_requant_nchwc(const unit_conv_desc *d, const uint8_t *x, const void *pw, const int32_t *bias,
                                    int32_t shift, uint8_t *out, void *workspace, size_t workspace_bytes,
                                    void *stream) {
-  return conv_i8(d, x, pw, bias, shift, out, true, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  EpilogueArgs e;
+  e.bias = bias; e.shift = shift; e.out_u8 = true;
+  return conv_i8(d, x, pw, e, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+static int epilogue_from(const unit_epilogue *epi, EpilogueArgs *e) {
+  if (!epi) return UNIT_ERR_NULL;
+  e->bias = epi->d_bias;
+  e->mul = epi->mul;
+  e->shift = epi->shift;
+  e->out_u8 = epi->out_u8 != 0;
+  e->residual = epi->d_residual;
+  e->x_signed = epi->x_signed != 0;
+  return UNIT_OK;
+}
+
+int unit_conv2d_int8_nchwc(const unit_conv_desc *d, const void *x, const void *pw, const unit_epilogue *epi, void *out,
+                           void *workspace, size_t workspace_bytes, void *stream) {
+  EpilogueArgs e;
+  const int rc = epilogue_from(epi, &e);
+  if (rc) return rc;
+  return conv_i8(d, x, pw, e, out, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int unit_conv2d_plan_int8(const unit_conv_desc *d, const void *x, const void *pw, const unit_epilogue *epi, void *out,
+                          void *workspace, size_t workspace_bytes, unit_conv_plan *plan) {
+  if (!plan) return UNIT_ERR_NULL;
+  EpilogueArgs e;
+  int rc = epilogue_from(epi, &e);
+  if (rc) return rc;
+  PlanImpl pl;
+  rc = plan_conv_i8(pl, d, x, pw, e, out, workspace, workspace_bytes);
+  if (rc) return rc;
+  memset(plan, 0, sizeof(*plan));
+  memcpy(plan, &pl, sizeof(pl));
+  return UNIT_OK;
+}
+
+int unit_conv2d_run(const unit_conv_plan *plan, void *stream) {
+  if (!plan) return UNIT_ERR_NULL;
+  PlanImpl pl;
+  memcpy(&pl, plan, sizeof(pl));
+  return run_plan(pl, static_cast<cudaStream_t>(stream));
 }
 
 size_t unit_noalloc_scratch_capacity(void) { return kStaticScratchBytes; }
@@ -997,6 +1189,8 @@ int unit_conv2d_u8s8_requant_nchwc_noalloc(const unit_conv_desc *d, const uint8_
                                            const int32_t *bias, int32_t shift, uint8_t *out, void *stream) {
   const int rc = check_conv(d, false);
   if (rc) return rc;
+  if (!x || !pw || !out) return UNIT_ERR_NULL;
+  if (shift < 1 || shift > 31) return UNIT_ERR_SHAPE;
   const size_t need = stem_workspace_bytes(d);
   if (need > kStaticScratchBytes) return UNIT_ERR_TOO_LARGE;  // beyond the built-in scratch: use the workspace form
   void *scratch = nullptr;
@@ -1004,31 +1198,43 @@ int unit_conv2d_u8s8_requant_nchwc_noalloc(const unit_conv_desc *d, const uint8_
     const int rs = static_scratch_address(&scratch);
     if (rs) return rs;
   }
-  return conv_i8(d, x, pw, bias, shift, out, true, scratch, need ? kStaticScratchBytes : 0,
-                 static_cast<cudaStream_t>(stream));
+  EpilogueArgs e;
+  e.bias = bias; e.shift = shift; e.out_u8 = true;
+  return conv_i8(d, x, pw, e, out, scratch, need ? kStaticScratchBytes : 0, static_cast<cudaStream_t>(stream));
+}
+
+static int run_dense(bool f16, int32_t m, int32_t n, int32_t k, const void *a, int64_t lda, const void *pw, void *cmat,
+                     int64_t ldc, cudaStream_t st) {
+  const int eb = f16 ? 2 : 1;
+  const int kq = 16 / eb;  // elements per 16-byte K column
+  if (m < 1 || n < 16 || n % 16 || k < kq || k % kq) return UNIT_ERR_SHAPE;
+  if (!a || !pw || !cmat) return UNIT_ERR_NULL;
+  if (!aligned16(a) || !aligned16(pw) || !aligned16(cmat) || lda % 16 || lda < (int64_t)eb * k || ldc % 4 || ldc < n)
+    return UNIT_ERR_ALIGN;
+  int rc = check_arch();
+  if (rc) return rc;
+  const TileCfg c = make_cfg(n, k / kq, false, true);
+  PlanImpl pl{};
+  IgemmParams &p = pl.p;
+  p.a = static_cast<const uint8_t *>(a); p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
+  p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
+  p.OH = p.OW = 1;
+  CUtensorMap map;
+  if (use_tma() && use_sw128() && c.kc % 8 == 0 && make_dense_map_sw128(&map, a, m, (long long)eb * k, lda)) {
+    p.a_sw128 = 1;
+    rc = f16 ? prepare<A_DENSE_TMA, EPI_RAW_ROWS, true>(pl, c, &map) : prepare<A_DENSE_TMA, EPI_RAW_ROWS, false>(pl, c, &map);
+  } else if (use_tma() && make_dense_map(&map, a, m, (long long)eb * k, lda)) {
+    rc = f16 ? prepare<A_DENSE_TMA, EPI_RAW_ROWS, true>(pl, c, &map) : prepare<A_DENSE_TMA, EPI_RAW_ROWS, false>(pl, c, &map);
+  } else {
+    // matrices below the tensor-map size limit: the cp.async gather, single sub-tiles
+    rc = f16 ? prepare<A_DENSE, EPI_RAW_ROWS, true>(pl, c, nullptr, 1) : prepare<A_DENSE, EPI_RAW_ROWS, false>(pl, c, nullptr, 1);
+  }
+  return rc ? rc : run_plan(pl, st);
 }
 
 int unit_dense_u8s8s32(int32_t m, int32_t n, int32_t k, const uint8_t *a, int64_t lda, const void *pw, int32_t *cmat,
                        int64_t ldc, void *stream) {
-  if (m < 1 || n < 16 || n % 16 || k < 16 || k % 16) return UNIT_ERR_SHAPE;
-  if (!a || !pw || !cmat) return UNIT_ERR_NULL;
-  if (!aligned16(a) || !aligned16(pw) || !aligned16(cmat) || lda % 16 || lda < k || ldc % 4 || ldc < n)
-    return UNIT_ERR_ALIGN;
-  int rc = check_arch();
-  if (rc) return rc;
-  const TileCfg c = make_cfg(n, k / 16, false, true);
-  IgemmParams p{};
-  p.a = a; p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
-  p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
-  p.OH = p.OW = 1;
-  CUtensorMap map;
-  if (use_tma() && use_sw128() && c.kc % 8 == 0 && make_dense_map_sw128(&map, a, m, k, lda)) {
-    p.a_sw128 = 1;
-    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream), &map);
-  }
-  if (use_tma() && make_dense_map(&map, a, m, k, lda))
-    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream), &map);
-  return launch_igemm<A_DENSE, EPI_RAW_ROWS, false>(p, c, static_cast<cudaStream_t>(stream));
+  return run_dense(false, m, n, k, a, lda, pw, cmat, ldc, static_cast<cudaStream_t>(stream));
 }
 
 int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const void *pw, float *out, void *stream) {
@@ -1038,45 +1244,31 @@ int unit_conv2d_f16f32_nchw16c(const unit_conv_desc *d, const void *x, const voi
   if (!aligned16(x) || !aligned16(pw) || !aligned16(out)) return UNIT_ERR_ALIGN;
   if ((rc = check_arch())) return rc;
   const TileCfg c = make_cfg(d->c_out, conv_cols_f16(d), false);
-  IgemmParams p{};
+  PlanImpl pl{};
+  IgemmParams &p = pl.p;
   p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out;
   fill_conv(p, d, 2);
   CUtensorMap map;
+  rc = -1;
   if (use_tma() && use_sw128() && d->stride_h == 1 && d->stride_w == 1 && c.kc % 2 == 0) {
     // stride 1: whole pixel rows per copy, one copy per K step
     const BoxGeom g = choose_box(d->n, p.OH, p.OW);
     if (make_box_map_f16(&map, d->n, d->c_in, d->h, d->w, x, g)) {
       set_box(p, g, d->n);
       p.a_sw32 = 1;
-      return launch_igemm<A_CONV_BOX, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream), &map);
+      rc = prepare<A_CONV_BOX, EPI_RAW_NCHWC, true>(pl, c, &map);
     }
   }
-  if (use_tma() && make_im2col_map(&map, d, x, true))
-    return launch_igemm<A_CONV_TMA, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream), &map);
-  return launch_igemm<A_CONV_F16, EPI_RAW_NCHWC, true>(p, c, static_cast<cudaStream_t>(stream));
+  if (rc == -1) {
+    if (use_tma() && make_im2col_map(&map, d, x, true)) rc = prepare<A_CONV_TMA, EPI_RAW_NCHWC, true>(pl, c, &map);
+    else rc = prepare<A_CONV_F16, EPI_RAW_NCHWC, true>(pl, c);
+  }
+  return rc ? rc : run_plan(pl, static_cast<cudaStream_t>(stream));
 }
 
 int unit_gemm_f16f32(int32_t m, int32_t n, int32_t k, const void *a, int64_t lda, const void *pw, float *cmat,
                      int64_t ldc, void *stream) {
-  if (m < 1 || n < 16 || n % 16 || k < 8 || k % 8) return UNIT_ERR_SHAPE;
-  if (!a || !pw || !cmat) return UNIT_ERR_NULL;
-  if (!aligned16(a) || !aligned16(pw) || !aligned16(cmat) || lda % 16 || lda < 2ll * k || ldc % 4 || ldc < n)
-    return UNIT_ERR_ALIGN;
-  int rc = check_arch();
-  if (rc) return rc;
-  const TileCfg c = make_cfg(n, k / 8, false, true);
-  IgemmParams p{};
-  p.a = static_cast<const uint8_t *>(a); p.b = static_cast<const uint8_t *>(pw); p.out = cmat;
-  p.m_total = m; p.n_total = n; p.lda = lda; p.ldc = ldc;
-  p.OH = p.OW = 1;
-  CUtensorMap map;
-  if (use_tma() && use_sw128() && c.kc % 8 == 0 && make_dense_map_sw128(&map, a, m, 2ll * k, lda)) {
-    p.a_sw128 = 1;
-    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream), &map);
-  }
-  if (use_tma() && make_dense_map(&map, a, m, 2ll * k, lda))
-    return launch_igemm<A_DENSE_TMA, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream), &map);
-  return launch_igemm<A_DENSE, EPI_RAW_ROWS, true>(p, c, static_cast<cudaStream_t>(stream));
+  return run_dense(true, m, n, k, a, lda, pw, cmat, ldc, static_cast<cudaStream_t>(stream));
 }
 
 // ---- layout transforms ---------------------------------------------------------

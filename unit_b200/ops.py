@@ -26,7 +26,7 @@ from typing import Optional, Sequence, Tuple, Union
 import torch
 
 from . import _lib
-from ._lib import ConvDesc, check
+from ._lib import ConvDesc, ConvPlan as _CPlan, Epilogue, check
 
 IntPair = Union[int, Sequence[int]]
 
@@ -87,6 +87,15 @@ class PackedWeights:
         self.kind = kind
         self.buf = buf
         self.key = key
+        # the pack kernel was queued on the stream current at pack time: other streams wait for it
+        self._stream = _stream()
+        self._ready = torch.cuda.Event()
+        self._ready.record()
+
+    def sync_to_current_stream(self) -> None:
+        """Make the current stream wait for the pack kernel if it is not the stream that packed."""
+        if self._ready is not None and _stream() != self._stream:
+            torch.cuda.current_stream().wait_event(self._ready)
 
     @property
     def nbytes(self) -> int:
@@ -212,32 +221,52 @@ def pack_gemm_weights_f16(b: torch.Tensor) -> PackedWeights:
 _WORKSPACES: dict = {}
 
 
+_RETIRED_WORKSPACES: list = []
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Scratch buffer per (device, stream), grown on demand; calls on one stream run in order,
-    so they can share it."""
+    so they can share it.  A buffer that has been handed out is never freed (a captured CUDA
+    graph or a plan may still name it): when a larger one is needed the old one is retired,
+    not dropped."""
     key = (device.index, _stream())
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _RETIRED_WORKSPACES.append(buf)
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = buf
     return buf
 
 
 
-def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: IntPair = 0, dilation: IntPair = 1,
-                      layout: str = 'NCHW4c', out_layout: str = 'NCHW16c', out_dtype: str = 'int32', *,
-                      bias: Optional[torch.Tensor] = None, requant_shift: Optional[int] = None,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """u8 x s8 -> s32 convolution on blocked layouts.
+class ConvPlan:
+    """A prepared int8 convolution bound to its buffers: ``run()`` is one call into the library
+    with no argument checks, tile selection or tensor-map encoding (``unit_conv2d_plan_int8`` /
+    ``unit_conv2d_run``).  The counterpart of calling a built TVM module repeatedly
+    (poc/vnni/vnni_dense.py:40-66).  Keeps its tensors alive."""
 
-    data   u8  ``[N][C/cb][H][W][cb]``, cb = 16 (or 4 for a 3/4-channel stem)
-    kernel s8  ``[O/16][C/cb][KH][KW][cb/4][16][4]`` or a ``PackedWeights``
-    result s32 ``[N][O/16][OH][OW][16]``; with ``out_dtype='uint8'`` (or
-    ``requant_shift``) the fused epilogue
-    ``clamp((acc + bias + 2^(shift-1)) >> shift, 0, 255)`` gives u8 instead.
-    ``layout`` is accepted for signature compatibility; the channel block is
-    read from ``data``'s last dimension as the reference's compute does.
-    """
+    def __init__(self, plan: _CPlan, out: torch.Tensor, keep: tuple):
+        self._plan = plan
+        self._ref = ctypes.byref(plan)
+        self.out = out
+        self._keep = keep
+        self._run = _lib.lib().unit_conv2d_run
+
+    def run(self) -> torch.Tensor:
+        rc = self._run(self._ref, torch.cuda.current_stream().cuda_stream)
+        if rc:
+            check(rc, 'unit_conv2d_run')
+        return self.out
+
+
+_PLAN_CACHE: dict = {}
+
+
+def _conv_int8_prepare(data, kernel, stride, padding, dilation, out_layout, out_dtype, bias, requant_shift, mul,
+                       residual, out):
+    """Shared front end of ``conv2d_NCHWc_int8`` and ``conv2d_NCHWc_int8_plan``: checks the layout
+    contract and returns (library, descriptor, tensors, epilogue, out, workspace, host flag)."""
     L = _require_cuda_lib()
     if _pair(dilation) != (1, 1):
         raise ValueError('dilation other than 1 is not supported (the reference only uses 1)')
@@ -247,7 +276,10 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
         raise ValueError("out_dtype must be 'int32' or 'uint8'")
     stride, padding = _pair(stride), _pair(padding)
     host = not data.is_cuda
-    data = _to_device(data, torch.uint8, 'data')
+    if data.dtype not in (torch.uint8, torch.int8):
+        raise TypeError(f'data: expected torch.uint8 (or torch.int8 for signed activations), got {data.dtype}')
+    signed = data.dtype == torch.int8
+    data = _to_device(data, data.dtype, 'data')
     if data.dim() != 5 or data.shape[4] not in (4, 16):
         raise ValueError(f'data must be [N][C/cb][H][W][cb] with cb in (4, 16), got {tuple(data.shape)}')
     n, cc, h, w, cb = (int(s) for s in data.shape)
@@ -255,13 +287,16 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
         pw = kernel if isinstance(kernel, PackedWeights) else pack_conv_weights_int8(kernel, stride, padding)
         if pw.kind != 'conv_i8':
             raise ValueError('kernel was packed for a different operator')
+        pw.sync_to_current_stream()
         _, c_out, c_in, pcb, kh, kw, pstride, ppad = pw.key
         if c_in != cc * cb or pcb != cb:
             raise ValueError(f'channel mismatch: data has {cc}x{cb}, kernel expects {c_in} in blocks of {pcb}')
         if pstride != stride or (cb == 4 and ppad != padding):
             raise ValueError('weights were packed for a different stride (or, NCHW4c, padding)')
-        requant = out_dtype == 'uint8' or requant_shift is not None
-        shift = 8 if requant_shift is None else int(requant_shift)
+        requant = out_dtype == 'uint8' or requant_shift is not None or residual is not None
+        shift = (8 if requant_shift is None else int(requant_shift)) if requant else 0
+        if requant and int(mul) != 1:
+            raise ValueError('mul applies to the int32 output only')
         d = _conv_desc(n, c_in, h, w, cb, c_out, kh, kw, stride, padding)
         if h + 2 * padding[0] < kh or w + 2 * padding[1] < kw:
             raise ValueError('kernel larger than padded input')
@@ -272,6 +307,10 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
             if bias.numel() != c_out:
                 raise ValueError(f'bias must have {c_out} elements')
         oshape = (n, c_out // 16, oh, ow, 16)
+        if residual is not None:
+            residual = _to_device(residual, torch.uint8, 'residual')
+            if tuple(residual.shape) != oshape:
+                raise ValueError(f'residual must have the output shape {oshape}')
         odt = torch.uint8 if requant else torch.int32
         if out is None:
             out_t = torch.empty(oshape, dtype=odt, device=data.device)
@@ -279,18 +318,60 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
             out_t = out
             if tuple(out_t.shape) != oshape or out_t.dtype != odt or not out_t.is_cuda or not out_t.is_contiguous():
                 raise ValueError(f'out must be a contiguous CUDA {odt} tensor of shape {oshape}')
-        if n == 0:
-            return out_t.cpu() if (host and out is None) else out_t
-        ws_bytes = int(L.unit_conv2d_workspace_bytes(ctypes.byref(d)))
+        ws_bytes = int(L.unit_conv2d_workspace_bytes(ctypes.byref(d))) if n > 0 else 0
         ws = _workspace(data.device, ws_bytes) if ws_bytes else None
-        if requant:
-            check(L.unit_conv2d_u8s8_requant_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), shift,
-                                                   _ptr(out_t), _ptr(ws), ws_bytes, _stream()),
-                  'unit_conv2d_u8s8_requant_nchwc')
-        else:
-            check(L.unit_conv2d_u8s8s32_nchwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), _ptr(bias), _ptr(out_t),
-                                              _ptr(ws), ws_bytes, _stream()), 'unit_conv2d_u8s8s32_nchwc')
+        epi = Epilogue(None if bias is None else bias.data_ptr(), int(mul), shift, 1 if requant else 0,
+                       None if residual is None else residual.data_ptr(), 1 if signed else 0)
+    return L, d, (data, pw, bias, residual), epi, out_t, ws, ws_bytes, host, n
+
+
+def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: IntPair = 0, dilation: IntPair = 1,
+                      layout: str = 'NCHW4c', out_layout: str = 'NCHW16c', out_dtype: str = 'int32', *,
+                      bias: Optional[torch.Tensor] = None, requant_shift: Optional[int] = None, mul: int = 1,
+                      residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """u8 x s8 -> s32 convolution on blocked layouts.
+
+    data   u8  ``[N][C/cb][H][W][cb]``, cb = 16 (or 4 for a 3/4-channel stem); an s8 tensor
+           selects signed activations (the reference shifts them to u8 and compensates,
+           apps/cpu/relay/result.log:4-6,15-21; the tensor core takes s8 x s8 as it is)
+    kernel s8  ``[O/16][C/cb][KH][KW][cb/4][16][4]`` or a ``PackedWeights``
+    result s32 ``[N][O/16][OH][OW][16]`` = ``(acc + bias) * mul`` (``mul = 11`` is the reference's
+    fused graph operator, apps/cpu/relay/conv2d.py:21-23); with ``out_dtype='uint8'`` (or
+    ``requant_shift`` / ``residual``) the fused epilogue
+    ``clamp(((acc + bias + 2^(shift-1)) >> shift) + residual, 0, 255)`` gives u8 instead.
+    ``layout`` is accepted for signature compatibility; the channel block is
+    read from ``data``'s last dimension as the reference's compute does.
+    """
+    L, d, tensors, epi, out_t, ws, ws_bytes, host, n = _conv_int8_prepare(
+        data, kernel, stride, padding, dilation, out_layout, out_dtype, bias, requant_shift, mul, residual, out)
+    if n == 0:
+        return out_t.cpu() if (host and out is None) else out_t
+    x, pw = tensors[0], tensors[1]
+    with torch.cuda.device(x.device):
+        check(L.unit_conv2d_int8_nchwc(ctypes.byref(d), _ptr(x), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _ptr(ws),
+                                       ws_bytes, _stream()), 'unit_conv2d_int8_nchwc')
     return out_t.cpu() if (host and out is None) else out_t
+
+
+def conv2d_NCHWc_int8_plan(data: torch.Tensor, kernel, stride: IntPair = 1, padding: IntPair = 0,
+                           dilation: IntPair = 1, layout: str = 'NCHW4c', out_layout: str = 'NCHW16c',
+                           out_dtype: str = 'int32', *, bias: Optional[torch.Tensor] = None,
+                           requant_shift: Optional[int] = None, mul: int = 1,
+                           residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> ConvPlan:
+    """Same arguments as ``conv2d_NCHWc_int8`` (CUDA tensors only); returns a ``ConvPlan`` whose
+    ``run()`` repeats the convolution on these buffers."""
+    if not data.is_cuda:
+        raise ValueError('a plan is bound to device buffers: pass CUDA tensors')
+    L, d, tensors, epi, out_t, ws, ws_bytes, _host, n = _conv_int8_prepare(
+        data, kernel, stride, padding, dilation, out_layout, out_dtype, bias, requant_shift, mul, residual, out)
+    if n == 0:
+        raise ValueError('empty batch')
+    x, pw = tensors[0], tensors[1]
+    plan = _CPlan()
+    with torch.cuda.device(x.device):
+        check(L.unit_conv2d_plan_int8(ctypes.byref(d), _ptr(x), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _ptr(ws),
+                                      ws_bytes, ctypes.byref(plan)), 'unit_conv2d_plan_int8')
+    return ConvPlan(plan, out_t, tensors + (ws,))
 
 
 def dense_dotprod(data: torch.Tensor, weight, bias: Optional[torch.Tensor] = None, out_dtype: str = 'int32', *,
