@@ -13,12 +13,16 @@ layer finds its data in L2 from an earlier launch.
 Prints one JSON line (rank 0).  ``value`` is whole-job TOPS with inputs
 resident in HBM; ``e2e`` is the same sweep through the Python operator with
 pinned host buffers copied in and results copied out inside the timed region.
+On one GPU the line also carries ``configs``: the other configurations of the
+baseline (single 3x3 convolution, int8 GEMM 4096^3, the batch-1 and batch-16
+sweeps, the fp16 convolution) and the tensor-core peak probe.
 ``--impl reference`` times the AVX-512 VNNI + OpenMP restatement of the
-reference's CPU loop nest on the host cores over a bounded sample.
+reference's CPU loop nest on the host cores, on the same batch-256 sweep.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -32,6 +36,10 @@ sys.path.insert(0, ROOT)
 
 TOTAL_BATCH = 256
 METRIC = 'int8 conv2d TOPS (ResNet-50 conv-layer sweep, batch 256)'
+# The reference's own logged time for the config-1 shape (3x3 64->64 @56^2, batch 1) on its CPU
+# (cpu-tune.log:160 of were/UNIT: 24.27 us = 9.5 TOPS; hardware inferred as Cascade Lake).
+REFERENCE_LOG = {'shape': 'int8 3x3 64->64 @56^2, batch 1', 'us': 24.27, 'tops': 9.53,
+                 'source': 'cpu-tune.log:160 (reference log, different hardware)'}
 
 
 def _peaks():
@@ -99,70 +107,71 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU legs (the oracle is the thing timed here, never the thing shipped)
 # ---------------------------------------------------------------------------
-def cpu_sweep(sample_batch: int, min_seconds: float, max_passes: int = 50):
-    """Times the VNNI/OpenMP restatement over the 53 convolutions at a small batch."""
-    import numpy as np
-    from oracle import c_oracle as co
-    from unit_b200 import resnet50 as R
-    vnni = co.host_has_vnni()
-    co.use_all_cores()
-    data = []
-    for i, l in enumerate(R.LAYERS):
-        x, w, b = R.make_layer_inputs(l, i, sample_batch, config=5)
-        data.append((l, x, w, b))
+def _host_batch(want: int) -> int:
+    """The batch the CPU sweep can hold in host memory (about 16 MB per image for inputs and outputs)."""
+    try:
+        with open('/proc/meminfo') as f:
+            avail_kb = next(int(line.split()[1]) for line in f if line.startswith('MemAvailable'))
+    except Exception:
+        return want
+    b = want
+    while b > 8 and b * 16e6 * 1.5 > avail_kb * 1024:
+        b //= 2
+    return b
 
-    def one_pass():
+
+class CpuSweep:
+    """The VNNI/OpenMP restatement over the 53 convolutions, outputs preallocated (a fresh output
+    array per call would be timed as page faults)."""
+
+    def __init__(self, batch: int):
+        import numpy as np
+        from oracle import c_oracle as co
+        from unit_b200 import resnet50 as R
+        self.co, self.R, self.batch = co, R, batch
+        self.vnni = co.host_has_vnni()
+        co.use_all_cores()
+        self.cores = int(co.lib().oracle_max_threads())
+        self.data = []
+        for i, l in enumerate(R.LAYERS):
+            x, w, b = R.make_layer_inputs(l, i, batch, config=5)
+            out = np.zeros((batch, l.c_out // 16, l.out_hw, l.out_hw, 16), np.uint8)
+            self.data.append((l, x, w, b, out))
+        self.ops = R.sweep_ops(batch)
+
+    def one_pass(self) -> float:
         t0 = time.perf_counter()
-        for l, x, w, b in data:
+        for l, x, w, b, out in self.data:
             for _ in range(l.count):
-                co.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
+                self.co.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=self.vnni,
+                                    out=out)
         return time.perf_counter() - t0
 
-    one_pass()  # warm-up
-    times = []
-    t_start = time.perf_counter()
-    while len(times) < max_passes and (not times or time.perf_counter() - t_start < min_seconds):
-        times.append(one_pass())
-    ops = R.sweep_ops(sample_batch)
-    return {'times': times, 'ops': ops, 'cores': int(co.lib().oracle_max_threads()), 'vnni': vnni,
-            'tops': ops / statistics.median(times) / 1e12}
+    def describe(self) -> str:
+        how = 'AVX-512 VNNI + OpenMP' if self.vnni else 'scalar + OpenMP'
+        whole = 'the whole batch' if self.batch == TOTAL_BATCH else f'batch {self.batch} of {TOTAL_BATCH} (host memory)'
+        return f'all 53 convolutions, {whole}, {how} restatement of the reference loop nest on pre-padded inputs'
 
 
 def run_reference(args):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return 0
-    sample = 8
-    import numpy as np  # noqa: F401
-    from oracle import c_oracle as co
-    from unit_b200 import resnet50 as R
-    vnni = co.host_has_vnni()
-    co.use_all_cores()
-    data = [(l,) + R.make_layer_inputs(l, i, sample, config=5) for i, l in enumerate(R.LAYERS)]
-
-    def step():
-        for l, x, w, b in data:
-            for _ in range(l.count):
-                co.conv2d_u8s8(x, w, (l.stride, l.stride), (l.pad, l.pad), bias=b, requant_shift=8, vnni=vnni)
-
+    sweep = CpuSweep(_host_batch(TOTAL_BATCH))
     for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
-    tops = R.sweep_ops(sample) / dt / 1e12
-    cores = int(co.lib().oracle_max_threads())
-    kind = 'port'
-    sample_txt = (f'all 53 convolutions at batch {sample} of {TOTAL_BATCH} per step, '
-                  f'{"AVX-512 VNNI + OpenMP" if vnni else "scalar + OpenMP"} restatement of the reference loop nest')
+        sweep.one_pass()
+    times = [sweep.one_pass() for _ in range(args.steps)]
+    dt = sum(times) / len(times)
+    tops = sweep.ops / dt / 1e12
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': tops, 'unit': 'TOPS', 'n_gpus': args.gpus,
-        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3 * TOTAL_BATCH / sweep.batch,
+        'higher_is_better': True,
         'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
-        'config': {'workload': 'resnet50-int8-conv-sweep', 'global_batch': TOTAL_BATCH, 'sample_batch': sample,
+        'config': {'workload': 'resnet50-int8-conv-sweep', 'global_batch': TOTAL_BATCH, 'sample_batch': sweep.batch,
                    'convolutions': 53, 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c'},
-        'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': cores, 'kind': kind, 'sample': sample_txt},
+        'cpu_baseline': {'value': tops, 'unit': 'TOPS', 'cores': sweep.cores, 'kind': 'port', 'sample': sweep.describe()},
+        'reference_log': REFERENCE_LOG,
         'e2e': {'value': tops, 'unit': 'TOPS', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
     }
     print(json.dumps(line), flush=True)
@@ -200,7 +209,6 @@ NCU_DRAM_B256 = {
     's4_1x1_512_2048': (7.54e6, 0.0),
     's4_proj_s2_1024_2048': (38.86e6, 0.50e6),
 }
-ROOFLINE_SAMPLE_LAYERS = ('s1_1x1_64_256', 's3_3x3_256_256')  # the two layers with full ncu captures
 
 
 def ncu_traffic(name, batch):
@@ -209,25 +217,6 @@ def ncu_traffic(name, batch):
         return None
     r, w = NCU_DRAM_B256[name]
     return r + w
-
-
-def roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak):
-    """Roofline objects of the fully captured layers: achieved from this run's per-layer timing."""
-    out = []
-    by_name = {r['layer']: r for r in layer_rows}
-    for l in layer_set:
-        if l.name not in ROOFLINE_SAMPLE_LAYERS or l.name not in by_name:
-            continue
-        r = by_name[l.name]
-        us = r['us']
-        if r['bound'] == 'hbm':
-            achieved, peak, unit = l.bytes(batch) / us / 1e3, peaks['hbm_gbs'], 'GB/s'
-        else:
-            achieved, peak, unit = l.ops(batch) / us / 1e6, int8_peak, 'TOPS'
-        out.append({'layer': l.name, 'bound': r['bound'], 'achieved': achieved, 'peak': peak, 'unit': unit,
-                    'frac': achieved / peak, 'traffic': ncu_traffic(l.name, batch),
-                    'algorithmic_bytes': l.bytes(batch)})
-    return out
 
 
 def write_only_bandwidth(torch, dev):
@@ -248,9 +237,201 @@ def write_only_bandwidth(torch, dev):
     return gbs
 
 
+def tensor_peak(torch, gpu_index, f16: bool, seconds: float = 0.6):
+    """The tensor-core issue-rate probe (unit_tensor_peak), run back to back for `seconds` so that the
+    figure is the sustained one under the power cap; clocks sampled beside it."""
+    from unit_b200 import _lib
+    L = _lib.lib()
+    best = None
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    out = ctypes.c_double(0.0)
+    for n, issuers in ((256, 1), (256, 2), (128, 4)):
+        rc = L.unit_tensor_peak(1 if f16 else 0, n, issuers, 2000, ctypes.byref(out), stream)   # warm-up
+        if rc != 0:
+            return {'error': f'unit_tensor_peak status {rc}'}
+        vals = []
+        with ClockSampler(gpu_index) as cs:
+            t_end = time.time() + seconds
+            while time.time() < t_end:
+                rc = L.unit_tensor_peak(1 if f16 else 0, n, issuers, 40000, ctypes.byref(out), stream)
+                if rc != 0:
+                    return {'error': f'unit_tensor_peak status {rc}'}
+                vals.append(out.value / 1e12)
+        tail = vals[len(vals) // 2:] or vals
+        rec = {'n': n, 'issuers': issuers, 'burst': max(vals), 'sustained': statistics.median(tail),
+               'sm_mhz': cs.summary()['sm_mhz'], 'launches': len(vals)}
+        if best is None or rec['sustained'] > best['sustained']:
+            best = rec
+    return best
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+def build_instances(torch, U, R, dev, layer_set, batch, rank, config=5):
+    """Packed weights shared per shape; own activations / outputs / plan per convolution instance."""
+    gen = torch.Generator(device=dev)
+    instances, per_layer = [], []
+    for l in layer_set:
+        li = R.LAYERS.index(l)
+        cb, cs = l.c_block, l.c_in_stored
+        gen.manual_seed(R.layer_seed(config, li, 1) + 7919 * rank)
+        w = torch.randn((l.c_out // 16, cs // cb, l.k, l.k, cb // 4, 16, 4), device=dev, generator=gen)
+        w = (w * 32.0).round_().clamp_(-128, 127).to(torch.int8)
+        bias = torch.randint(-2 ** 15, 2 ** 15, (l.c_out,), dtype=torch.int32, device=dev, generator=gen)
+        packed = U.pack_conv_weights_int8(w, l.stride, l.pad)
+        idxs = []
+        for c in range(l.count):
+            gen.manual_seed(R.layer_seed(config, li, 0) + 101 * c + 7919 * rank)
+            shape = (batch, cs // cb, l.hw, l.hw, cb)
+            x = torch.randint(1, 256, shape, dtype=torch.uint8, device=dev, generator=gen)
+            x *= torch.randint(0, 2, shape, dtype=torch.uint8, device=dev, generator=gen)
+            if cs != l.c_in:
+                x[..., l.c_in:] = 0
+            out = torch.empty((batch, l.c_out // 16, l.out_hw, l.out_hw, 16), dtype=torch.uint8, device=dev)
+            plan = U.conv2d_NCHWc_int8_plan(x, packed, stride=l.stride, padding=l.pad, bias=bias, out_dtype='uint8', out=out)
+            idxs.append(len(instances))
+            instances.append((l, x, packed, bias, out, plan))
+        per_layer.append((l, idxs))
+        del w
+    return instances, per_layer
+
+
+def capture_graph(torch, U, fn, warm: int = 1):
+    """Captures fn() (library launches on the current stream) into a CUDA graph; returns
+    (graph, launches per replay).  fn runs once on the capture stream first (one-off set-up of the
+    library and of the operators' per-stream scratch must not fall inside a capture)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    c0 = U.launch_count()
+    with torch.cuda.graph(graph, stream=side):
+        fn()
+    n = U.launch_count() - c0
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    return graph, n
+
+
+def time_ms(torch, fn, reps: int) -> float:
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def side_configs(torch, U, R, dev, peaks, local_rank):
+    """The other configurations of the baseline, each a small record {value, unit, ms, frac, peak}
+    (one GPU).  Kernels timed alone are set against the burst figures."""
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+    i8_burst, f16_burst = 2.0 * peaks['bf16_burst'], peaks['bf16_burst']
+
+    def flushed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps
+
+    # config 1: one int8 3x3 64->64 convolution at 56^2, batch 1, s32 out
+    torch.manual_seed(1)
+    sets = []
+    w = torch.randint(-128, 128, (4, 4, 3, 3, 4, 16, 4), dtype=torch.int8, device=dev)
+    pw = U.pack_conv_weights_int8(w, 1, 1)
+    for _ in range(8):
+        x = torch.randint(0, 256, (1, 4, 56, 56, 16), dtype=torch.uint8, device=dev)
+        o = torch.empty((1, 4, 56, 56, 16), dtype=torch.int32, device=dev)
+        sets.append((x, o, U.conv2d_NCHWc_int8_plan(x, pw, stride=1, padding=1, out=o)))
+    for s_ in sets:
+        s_[2].run()
+    torch.cuda.synchronize()
+    eager_us = time_ms(torch, lambda: [s_[2].run() for s_ in sets], 50) * 1e3 / len(sets)
+    op_us = time_ms(torch, lambda: [U.conv2d_NCHWc_int8(s_[0], pw, stride=1, padding=1, out=s_[1]) for s_ in sets], 25) * 1e3 / len(sets)
+    g, nl = capture_graph(torch, U, lambda: [s_[2].run() for s_ in sets for _ in range(16)])
+    graph_us = time_ms(torch, g.replay, 20) * 1e3 / nl
+    ops1 = 2.0 * 56 * 56 * 64 * 64 * 9
+    out['config1_conv3x3_64_b1'] = {
+        'value': eager_us, 'unit': 'us per call (prepared plan, eager launches, 8 buffer sets in turn)',
+        'us_python_operator': op_us, 'us_in_cuda_graph': graph_us, 'tops_in_cuda_graph': ops1 / graph_us / 1e6,
+        'reference_log_us': REFERENCE_LOG['us'], 'bound': 'launch latency (roofline time 0.13 us)'}
+    del sets, g
+
+    # config 2: int8 GEMM 4096^3
+    a = torch.randint(0, 256, (4096, 4096), dtype=torch.uint8, device=dev)
+    wq = torch.randint(-128, 128, (32, 1024, 128, 4), dtype=torch.int8, device=dev)
+    pwd = U.pack_dense_weights_int8(wq)
+    c = torch.empty((4096, 4096), dtype=torch.int32, device=dev)
+    ms = flushed(lambda: U.dense_dotprod(a, pwd, out=c))
+    v = 2.0 * 4096 ** 3 / ms / 1e9
+    out['config2_int8_gemm_4096'] = {'value': v, 'unit': 'TOPS', 'ms': ms, 'frac': v / i8_burst, 'peak': i8_burst,
+                                     'l2': 'flushed before every call'}
+    del a, wq, pwd, c
+
+    # config 4 and the fp16 GEMM
+    x = torch.randn((256, 16, 14, 14, 16), dtype=torch.float16, device=dev)
+    wf = torch.randn((16, 16, 3, 3, 16, 16), dtype=torch.float16, device=dev) * 0.05
+    pwf = U.pack_conv_weights_f16(wf)
+    of = U.conv2d_NCHW16c_OHWI16o(x, pwf, 1, 1, padding=1)
+    ms = flushed(lambda: U.conv2d_NCHW16c_OHWI16o(x, pwf, 1, 1, padding=1, out=of))
+    v = 2.0 * 256 * 14 * 14 * 256 * 256 * 9 / ms / 1e9
+    out['config4_fp16_conv_b256'] = {'value': v, 'unit': 'TFLOP/s', 'ms': ms, 'frac': v / f16_burst, 'peak': f16_burst,
+                                     'l2': 'flushed before every call'}
+    del x, wf, pwf, of
+    a = torch.randn((4096, 4096), dtype=torch.float16, device=dev)
+    b = torch.randn((4096, 4096), dtype=torch.float16, device=dev) * 0.05
+    pwg = U.pack_gemm_weights_f16(b)
+    c = torch.empty((4096, 4096), dtype=torch.float32, device=dev)
+    ms = flushed(lambda: U.gemm_f16f32(a, pwg, out=c))
+    v = 2.0 * 4096 ** 3 / ms / 1e9
+    out['fp16_gemm_4096'] = {'value': v, 'unit': 'TFLOP/s', 'ms': ms, 'frac': v / f16_burst, 'peak': f16_burst,
+                             'l2': 'flushed before every call'}
+    del a, b, pwg, c
+
+    # config 3: the sweep at batch 1 and 16, as a replayed CUDA graph of the 54 launches
+    for bsz in (1, 16):
+        inst, _ = build_instances(torch, U, R, dev, R.LAYERS, bsz, 0, config=3)
+        g, nl = capture_graph(torch, U, lambda: [i[5].run() for i in inst], warm=3)
+        ms = time_ms(torch, g.replay, 20)
+        eager_ms = time_ms(torch, lambda: [i[5].run() for i in inst], 5)
+        ops = R.sweep_ops(bsz)
+        out[f'config3_sweep_b{bsz}'] = {'value': ops / ms / 1e9, 'unit': 'TOPS', 'ms': ms, 'launches': nl,
+                                        'us_per_launch': ms * 1e3 / nl, 'ms_eager_plans': eager_ms,
+                                        'launch_mode': 'cuda graph replay'}
+        del inst, g
+
+    # layout kernels (NCHW <-> NCHW16c): GB/s of bytes read + written
+    xl = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device=dev)
+    yl = U.pack_data_nchwc(xl)
+    ms_p = time_ms(torch, lambda: U.pack_data_nchwc(xl), 10)
+    ms_u = time_ms(torch, lambda: U.unpack_data_nchwc(yl), 10)
+    out['layout_kernels'] = {'nchw_to_nchw16c_gbs': 2 * xl.numel() / ms_p / 1e6, 'nchw16c_to_nchw_gbs': 2 * xl.numel() / ms_u / 1e6,
+                             'tensor': 'u8 (64, 256, 56, 56), 51 MB each way', 'hbm_peak_gbs': peaks['hbm_gbs']}
+    del xl, yl, flush
+
+    # tensor-core peak, measured
+    out['tensor_peak'] = {'i8_tops': tensor_peak(torch, local_rank, False), 'f16_tflops': tensor_peak(torch, local_rank, True),
+                          'how': 'unit_tensor_peak: back-to-back tcgen05.mma 128 x n x 32 B from `issuers` threads per SM, '
+                                 'operands resident in shared memory; sustained = median of the second half of 0.6 s'}
+    return out
+
+
 def run_unit(args):
     import torch
     import torch.distributed as dist
@@ -286,72 +467,31 @@ def run_unit(args):
     if args.total_batch % world:
         raise SystemExit('--gpus must divide the batch')
     batch = args.total_batch // world
-    gen = torch.Generator(device=dev)
 
-    # ---- build the 53 instances: packed weights shared per shape, own activations/outputs per instance
-    instances = []   # (layer, x, packed, bias, out)
-    per_layer = []   # (layer, [instance indices])
     layer_set = [l for l in R.LAYERS if not args.layer or l.name in args.layer]
     if not layer_set:
         raise SystemExit('no such layer; names: ' + ', '.join(l.name for l in R.LAYERS))
-    for l in layer_set:
-        li = R.LAYERS.index(l)
-        cb, cs = l.c_block, l.c_in_stored
-        gen.manual_seed(R.layer_seed(5, li, 1) + 7919 * rank)
-        w = torch.randn((l.c_out // 16, cs // cb, l.k, l.k, cb // 4, 16, 4), device=dev, generator=gen)
-        w = (w * 32.0).round_().clamp_(-128, 127).to(torch.int8)
-        bias = torch.randint(-2 ** 15, 2 ** 15, (l.c_out,), dtype=torch.int32, device=dev, generator=gen)
-        packed = U.pack_conv_weights_int8(w, l.stride, l.pad)
-        idxs = []
-        for c in range(l.count):
-            gen.manual_seed(R.layer_seed(5, li, 0) + 101 * c + 7919 * rank)
-            shape = (batch, cs // cb, l.hw, l.hw, cb)
-            x = torch.randint(1, 256, shape, dtype=torch.uint8, device=dev, generator=gen)
-            x *= torch.randint(0, 2, shape, dtype=torch.uint8, device=dev, generator=gen)
-            if cs != l.c_in:
-                x[..., l.c_in:] = 0
-            out = torch.empty((batch, l.c_out // 16, l.out_hw, l.out_hw, 16), dtype=torch.uint8, device=dev)
-            idxs.append(len(instances))
-            instances.append((l, x, packed, bias, out))
-        per_layer.append((l, idxs))
-        del w
+    instances, per_layer = build_instances(torch, U, R, dev, layer_set, batch, rank)
     U.device_status()
-
-    def run_instance(inst):
-        l, x, packed, bias, out = inst
-        U.conv2d_NCHWc_int8(x, packed, stride=l.stride, padding=l.pad, bias=bias, out_dtype='uint8', out=out)
 
     def step():
         for inst in instances:
-            run_instance(inst)
+            inst[5].run()
 
     # ---- device-resident timing
     for _ in range(args.warmup):
         step()
     barrier()
-    # One step = 53 launches of a few tens of microseconds: replay them as a CUDA graph so that
-    # the host's per-call work (Python, ctypes, tensor-map encoding) is not what is measured.
+    # One step = 54 launches of a few tens of microseconds: replay them as a CUDA graph so that
+    # the host's per-call work is not what is measured.
     graph = None
     launches_per_step = None
     if not args.no_graph and not args.kernels_only:
         try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step()  # the operators keep their scratch per stream: create it before the capture
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            c0 = U.launch_count()
-            with torch.cuda.graph(graph, stream=side):
-                step()
-            launches_per_step = U.launch_count() - c0
-            for _ in range(args.warmup):
-                graph.replay()
-            torch.cuda.synchronize()
+            graph, launches_per_step = capture_graph(torch, U, step, warm=args.warmup)
         except Exception as exc:  # keep measuring, say how
             print(f'[bench] CUDA graph capture failed ({exc!r}); timing eager launches', file=sys.stderr)
-            graph = None
+            graph, launches_per_step = None, None
 
     def timed_step():
         if graph is not None:
@@ -385,40 +525,44 @@ def run_unit(args):
     clocks['sampled'] = 'timed region plus the same load continued untimed' if extended else 'timed region'
     gpu_launches = int(launches)
 
-    # ---- per-layer timing (explains the number; not part of `value`)
+    # ---- per-layer timing (explains the number; not part of `value`): the step's launches in
+    # their order, eager through the prepared plans, an event after each layer's instances, so
+    # that every launch meets the cold L2 it meets in the timed step
     peaks = _peaks()
     int8_peak = 2.0 * peaks['bf16_sustained']
     write_gbs = write_only_bandwidth(torch, dev) if not args.kernels_only else float(peaks['hbm_gbs'])
     layer_rows = []
     sum_kernel_ms = 0.0
     sum_roof_ms = 0.0
-    reps = 5
-    for l, idxs in ([] if args.kernels_only else per_layer):
-        for i in idxs:
-            run_instance(instances[i])
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+    if not args.kernels_only:
+        reps = max(3, min(args.steps, 10))
+        acc = [0.0] * len(per_layer)
         for _ in range(reps):
-            for i in idxs:
-                run_instance(instances[i])
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / (reps * len(idxs))
-        ops, byts = l.ops(batch), l.bytes(batch)
-        t_tensor = ops / (int8_peak * 1e12) * 1e3
-        t_hbm = byts / (peaks['hbm_gbs'] * 1e9) * 1e3
-        bound = 'tensor' if t_tensor >= t_hbm else 'hbm'
-        roof = max(t_tensor, t_hbm)
-        sum_kernel_ms += ms * len(idxs)
-        sum_roof_ms += roof * len(idxs)
-        out_bytes = float(batch) * l.c_out * l.out_hw * l.out_hw
-        t_write = out_bytes / (write_gbs * 1e9) * 1e3  # the output alone, at the measured write-only rate
-        layer_rows.append({'layer': l.name, 'count': l.count, 'us': round(ms * 1e3, 2),
-                           'tops': round(ops / ms / 1e9, 1), 'gbs': round(byts / ms / 1e6, 1), 'bound': bound,
-                           'frac': round(roof / ms, 3), 'frac_with_write_floor': round(max(roof, t_write) / ms, 3),
-                           'traffic': ncu_traffic(l.name, batch), 'algorithmic_bytes': byts})
-    if args.kernels_only:
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(per_layer) + 1)]
+            evs[0].record()
+            for k, (l, idxs) in enumerate(per_layer):
+                for i in idxs:
+                    instances[i][5].run()
+                evs[k + 1].record()
+            torch.cuda.synchronize()
+            for k in range(len(per_layer)):
+                acc[k] += evs[k].elapsed_time(evs[k + 1])
+        for k, (l, idxs) in enumerate(per_layer):
+            ms = acc[k] / reps / len(idxs)
+            ops, byts = l.ops(batch), l.bytes(batch)
+            t_tensor = ops / (int8_peak * 1e12) * 1e3
+            t_hbm = byts / (peaks['hbm_gbs'] * 1e9) * 1e3
+            bound = 'tensor' if t_tensor >= t_hbm else 'hbm'
+            roof = max(t_tensor, t_hbm)
+            sum_kernel_ms += ms * len(idxs)
+            sum_roof_ms += roof * len(idxs)
+            out_bytes = float(batch) * l.c_out * l.out_hw * l.out_hw
+            t_write = out_bytes / (write_gbs * 1e9) * 1e3  # the output alone, at the measured write-only rate
+            layer_rows.append({'layer': l.name, 'count': l.count, 'us': round(ms * 1e3, 2),
+                               'tops': round(ops / ms / 1e9, 1), 'gbs': round(byts / ms / 1e6, 1), 'bound': bound,
+                               'frac': round(roof / ms, 3), 'frac_with_write_floor': round(max(roof, t_write) / ms, 3),
+                               'traffic': ncu_traffic(l.name, batch), 'algorithmic_bytes': byts})
+    else:
         sum_kernel_ms, sum_roof_ms = ms_step, None
     kernel_tops = total_ops / world / (sum_kernel_ms * 1e-3) / 1e12
 
@@ -429,9 +573,8 @@ def run_unit(args):
     if not args.kernels_only:
         e2e_steps = max(1, min(args.steps, args.e2e_steps))
         host_in, host_out = {}, {}
-        h2d = d2h = 0
         for li, (l, idxs) in enumerate(per_layer):
-            _, x, _, _, out = instances[idxs[0]]
+            x, out = instances[idxs[0]][1], instances[idxs[0]][4]
             host_in[li] = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
             host_in[li].copy_(x)
             host_out[li] = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
@@ -450,7 +593,7 @@ def run_unit(args):
                 s_.wait_stream(main)
             for li, (l, idxs) in enumerate(per_layer):
                 for i in idxs:
-                    _, x, packed, bias, out = instances[i]
+                    _, x, packed, bias, out, _plan = instances[i]
                     with torch.cuda.stream(s_in):
                         x.copy_(host_in[li], non_blocking=True)
                         up = torch.cuda.Event()
@@ -477,25 +620,45 @@ def run_unit(args):
         e2e_ms = max_over_ranks(a.elapsed_time(b) / e2e_steps)
         e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
         U.device_status()
+        del host_in, host_out
+
+    # ---- the other configurations and the measured tensor peak (one GPU only)
+    configs = None
+    single = rank == 0 and world == 1 and not args.kernels_only and not args.layer and args.total_batch == TOTAL_BATCH
+    if single and not args.no_side_configs:
+        del instances, graph
+        instances, graph = [], None
+        torch.cuda.empty_cache()
+        try:
+            configs = side_configs(torch, U, R, dev, peaks, local_rank)
+        except Exception as exc:
+            configs = {'error': repr(exc)}
+        U.device_status()
 
     # ---- host-CPU baseline beside it (rank 0, single-GPU runs only)
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.kernels_only:
-        sample = 8
-        r = cpu_sweep(sample, min_seconds=10.0)
-        cpu = {'value': r['tops'], 'unit': 'TOPS', 'cores': r['cores'], 'kind': 'port',
-               'sample': (f'all 53 convolutions at batch {sample} of {TOTAL_BATCH}, {len(r["times"])} passes, median; '
-                          f'{"AVX-512 VNNI + OpenMP" if r["vnni"] else "scalar + OpenMP"} restatement of the '
-                          'reference loop nest')}
+    if single and not args.no_cpu_baseline:
+        sweep = CpuSweep(_host_batch(TOTAL_BATCH))
+        sweep.one_pass()  # warm-up
+        times = []
+        t_start = time.perf_counter()
+        while len(times) < 30 and (len(times) < 3 or time.perf_counter() - t_start < 12.0):
+            times.append(sweep.one_pass())
+        cpu = {'value': sweep.ops / statistics.median(times) / 1e12, 'unit': 'TOPS', 'cores': sweep.cores, 'kind': 'port',
+               'sample': f'{sweep.describe()}; {len(times)} passes, median', 'reference_log': REFERENCE_LOG}
 
     if rank == 0:
+        n_launch = sum(l.count for l in layer_set)
+        peak_measured = None
+        if configs and isinstance(configs.get('tensor_peak', {}).get('i8_tops'), dict) and 'sustained' in configs['tensor_peak']['i8_tops']:
+            peak_measured = configs['tensor_peak']['i8_tops']['sustained']
         line = {
             'metric': METRIC, 'value': value, 'unit': 'TOPS', 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'u8*s8->s32', 'data': 'synthetic',
             'config': {'workload': 'resnet50-int8-conv-sweep' + ('' if not args.layer else ':' + '+'.join(args.layer)),
                        'global_batch': args.total_batch, 'per_gpu_batch': batch,
-                       'convolutions': sum(l.count for l in layer_set), 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
+                       'convolutions': n_launch, 'epilogue': 'bias+requant(shift 8)->u8', 'layout': 'NCHW16c',
                        'parallelism': f'batch-split x{world}, weights replicated, no collective',
                        'l2': 'every convolution instance has its own buffers; %.2f GB touched per step per GPU, '
                              'larger than L2' % (sum(l.bytes(batch) * l.count for l in layer_set) / 1e9)},
@@ -504,23 +667,26 @@ def run_unit(args):
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': gpu_launches,
             'launch_mode': ('cuda graph: one captured step (%d kernel launches) replayed per timed step' % launches_per_step)
-            if graph is not None else 'eager launches through the Python operator',
+            if launches_per_step is not None else 'eager launches of prepared plans',
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
                          'frac': kernel_tops / int8_peak,
-                         'traffic': (sum(ncu_traffic(l.name, batch) * l.count for l in layer_set) / sum(l.count for l in layer_set))
+                         'traffic': (sum(ncu_traffic(l.name, batch) * l.count for l in layer_set) / n_launch)
                          if batch == TOTAL_BATCH else None,
                          'peak_source': f'2 x bf16_tflops_sustained of {peaks["source"]} peaks '
                                         '(dense int8 issues at twice the bf16 rate)',
+                         'peak_measured': peak_measured,
+                         'frac_of_peak_measured': (kernel_tops / peak_measured) if peak_measured else None,
                          'kernel': 'igemm_kernel<A_CONV_BOX|A_CONV_TMA, EPI_REQ_NCHWC, i8> over the contraction launches '
                                    'of one step (2 x ops / summed per-layer launch time, CUDA events)',
                          'traffic_note': 'mean DRAM bytes per launch over the 53 launches of a step (ncu, one capture per '
-                                         'layer shape at batch 256; per layer in `layers`); algorithmic mean %.1f MB'
-                                         % (sum(l.bytes(batch) * l.count for l in layer_set) / sum(l.count for l in layer_set) / 1e6),
+                                         'layer shape at batch 256); algorithmic mean %.1f MB'
+                                         % (sum(l.bytes(batch) * l.count for l in layer_set) / n_launch / 1e6),
                          'hbm_write_only_gbs': write_gbs,
                          'mixed_bound_frac': (sum_roof_ms / sum_kernel_ms) if sum_roof_ms else None,
-                         'hbm_peak_gbs': peaks['hbm_gbs']},
-            'roofline_samples': roofline_samples(layer_rows, layer_set, batch, peaks, int8_peak),
-            'layers': layer_rows,
+                         'hbm_peak_gbs': peaks['hbm_gbs'],
+                         # per layer: [name, count, us per launch, bound, fraction of that bound's roofline]
+                         'layers': [[r['layer'], r['count'], r['us'], r['bound'], r['frac']] for r in layer_rows]},
+            'configs': configs,
             'cpu_baseline': cpu,
         }
         print(json.dumps(line), flush=True)
@@ -530,9 +696,9 @@ def run_unit(args):
 
 
 def run_side_config(args):
-    """Other BASELINE configurations, one JSON line each (diagnostic; not the headline metric):
+    """One of the other configurations alone (for profiler runs), one JSON line:
     `gemm` = int8 GEMM 4096^3 (config 2), `fp16conv` = fp16 3x3 256->256 @14^2, N = 256 (config 4),
-    `fp16gemm` = fp16 GEMM 4096^3."""
+    `fp16gemm` = fp16 GEMM 4096^3, `peak` = the tensor-core peak probe, `layout` = the layout kernels."""
     import torch
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: the unit_b200 operators have no CPU fallback')
@@ -540,27 +706,39 @@ def run_side_config(args):
     dev = torch.device('cuda', 0)
     torch.manual_seed(0)
     peaks = _peaks()
+    if args.config == 'peak':
+        print(json.dumps({'metric': 'tensor-core peak probe', 'i8_tops': tensor_peak(torch, 0, False),
+                          'f16_tflops': tensor_peak(torch, 0, True)}), flush=True)
+        return 0
+    if args.config == 'layout':
+        x = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device=dev)
+        y = U.pack_data_nchwc(x)
+        ms_p = time_ms(torch, lambda: U.pack_data_nchwc(x), args.steps)
+        ms_u = time_ms(torch, lambda: U.unpack_data_nchwc(y), args.steps)
+        print(json.dumps({'metric': 'layout kernels, u8 (64, 256, 56, 56)', 'nchw_to_nchw16c_gbs': 2 * x.numel() / ms_p / 1e6,
+                          'nchw16c_to_nchw_gbs': 2 * x.numel() / ms_u / 1e6}), flush=True)
+        return 0
     if args.config == 'gemm':
         a = torch.randint(0, 256, (4096, 4096), dtype=torch.uint8, device=dev)
         w = torch.randint(-128, 128, (32, 1024, 128, 4), dtype=torch.int8, device=dev)
         pw = U.pack_dense_weights_int8(w)
         out = torch.empty((4096, 4096), dtype=torch.int32, device=dev)
         fn = lambda: U.dense_dotprod(a, pw, out=out)
-        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TOPS', 2.0 * peaks['bf16_sustained'], 'int8 GEMM 4096^3 (u8 x s8 -> s32)'
+        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TOPS', 2.0 * peaks['bf16_burst'], 'int8 GEMM 4096^3 (u8 x s8 -> s32)'
     elif args.config == 'fp16gemm':
         a = torch.randn((4096, 4096), dtype=torch.float16, device=dev)
         b = torch.randn((4096, 4096), dtype=torch.float16, device=dev) * 0.05
         pw = U.pack_gemm_weights_f16(b)
         out = torch.empty((4096, 4096), dtype=torch.float32, device=dev)
         fn = lambda: U.gemm_f16f32(a, pw, out=out)
-        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TFLOP/s', peaks['bf16_sustained'], 'fp16 GEMM 4096^3 (fp32 accumulate)'
+        ops, unit, peak, what = 2.0 * 4096 ** 3, 'TFLOP/s', peaks['bf16_burst'], 'fp16 GEMM 4096^3 (fp32 accumulate)'
     else:
         x = torch.randn((256, 16, 14, 14, 16), dtype=torch.float16, device=dev)
         w = torch.randn((16, 16, 3, 3, 16, 16), dtype=torch.float16, device=dev) * 0.05
         pw = U.pack_conv_weights_f16(w)
         out = U.conv2d_NCHW16c_OHWI16o(x, pw, 1, 1, padding=1)
         fn = lambda: U.conv2d_NCHW16c_OHWI16o(x, pw, 1, 1, padding=1, out=out)
-        ops, unit, peak, what = 2.0 * 256 * 14 * 14 * 256 * 256 * 9, 'TFLOP/s', peaks['bf16_sustained'], \
+        ops, unit, peak, what = 2.0 * 256 * 14 * 14 * 256 * 256 * 9, 'TFLOP/s', peaks['bf16_burst'], \
             'fp16 conv2d 3x3 256->256 @14^2, N = 256 (fp32 accumulate)'
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
     for _ in range(max(3, args.warmup)):
@@ -583,14 +761,14 @@ def run_side_config(args):
                       'ms_per_step': ms, 'higher_is_better': True, 'data': 'synthetic',
                       'config': {'workload': args.config, 'l2': 'a 256 MiB buffer is rewritten before every timed call'},
                       'roofline': {'bound': 'tensor', 'achieved': value, 'peak': peak, 'unit': unit, 'frac': value / peak,
-                                   'peak_source': f'{peaks["source"]} sustained bf16 figure (doubled for int8)'}}), flush=True)
+                                   'peak_source': f'{peaks["source"]} burst bf16 figure (doubled for int8)'}}), flush=True)
     return 0
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--config', default=None, choices=['gemm', 'fp16gemm', 'fp16conv'],
-                    help='time one of the other BASELINE configurations instead of the conv sweep (single GPU)')
+    ap.add_argument('--config', default=None, choices=['gemm', 'fp16gemm', 'fp16conv', 'peak', 'layout'],
+                    help='time one of the other configurations alone instead of the conv sweep (single GPU)')
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
@@ -599,13 +777,14 @@ def main():
     ap.add_argument('--total-batch', type=int, default=TOTAL_BATCH,
                     help='global batch (diagnostic runs; the metric is quoted on 256)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-side-configs', action='store_true', help='skip the `configs` records (single-GPU runs)')
     ap.add_argument('--no-graph', action='store_true', help='time eager launches instead of replaying a captured step')
     ap.add_argument('--layer', action='append', default=None,
                     help='restrict the sweep to the named layer(s) of unit_b200.resnet50.LAYERS (diagnostic runs; '
                          'the JSON line then describes that subset)')
     ap.add_argument('--kernels-only', action='store_true',
-                    help='timed region only: skip the per-layer pass, the end-to-end leg and the CPU baseline '
-                         '(for profiler runs)')
+                    help='timed region only: skip the per-layer pass, the end-to-end leg, the other configurations and '
+                         'the CPU baseline (for profiler runs)')
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == 'unit':
         args.warmup = 3

@@ -124,6 +124,14 @@ uint64_t unit_launch_count(void);
  * memory owned by the caller; NULL detaches.  Not for use while kernels are running. */
 int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 
+/* Tensor-core peak probe, the counterpart of the reference's instruction-rate microbenchmark
+ * (poc/vnni/micro.cc:16-51).  Every SM runs `issuers` (1-4) threads that each issue `iters`
+ * back-to-back tcgen05.mma of 128 x n x 32 bytes on operands resident in shared memory
+ * (f16 == 0: u8 x s8 -> s32; otherwise fp16 -> fp32); issuers * n <= 512.  Synchronous; writes
+ * operations per second (2 per multiply-accumulate) of the whole device to *ops_per_second. */
+int unit_tensor_peak(int32_t f16, int32_t n, int32_t issuers, int32_t iters, double *ops_per_second,
+                     void *stream);
+
 /* Which kernel variant ran: the contraction kernel exists in one compiled variant per (operand
  * path, epilogue, data type, sub-tiles per tile).  unit_variant_count() is the size of the index
  * space; unit_variant_name(i) is NULL for indices without a compiled variant, otherwise a static

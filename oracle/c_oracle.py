@@ -96,12 +96,13 @@ def out_hw(h, w, kh, kw, stride, pad):
     return ((h + 2 * pad[0] - kh) // stride[0] + 1, (w + 2 * pad[1] - kw) // stride[1] + 1)
 
 
-def conv2d_u8s8(x, w, stride=(1, 1), pad=(0, 0), bias=None, requant_shift=None, vnni=False):
+def conv2d_u8s8(x, w, stride=(1, 1), pad=(0, 0), bias=None, requant_shift=None, vnni=False, out=None):
     """x [N][Cc][H][W][cb] u8, w [Oc][Cc][KH][KW][cb/4][16][4] s8.
 
     Returns s32 [N][Oc][OH][OW][16] (bias added if given), or the requantised
     u8 tensor when ``requant_shift`` is set.  ``vnni=True`` runs the AVX-512
-    restatement (the timed baseline) instead of the scalar definition.
+    restatement (the timed baseline) instead of the scalar definition.  ``out``: a preallocated
+    result array (the timed baseline reuses one, so that page faults are not timed).
     """
     x = _c(x, np.uint8)
     w = _c(w, np.int8)
@@ -112,11 +113,13 @@ def conv2d_u8s8(x, w, stride=(1, 1), pad=(0, 0), bias=None, requant_shift=None, 
     if bias is not None:
         bias = _c(bias, np.int32)
         assert bias.size == oc * 16
+    odt = np.int32 if requant_shift is None else np.uint8
+    if out is None:
+        out = np.empty((n, oc, oh, ow, 16), odt)
+    assert out.shape == (n, oc, oh, ow, 16) and out.dtype == odt and out.flags['C_CONTIGUOUS']
     if requant_shift is None:
-        out = np.empty((n, oc, oh, ow, 16), np.int32)
         o32, o8, sh = out, None, 0
     else:
-        out = np.empty((n, oc, oh, ow, 16), np.uint8)
         o32, o8, sh = None, out, int(requant_shift)
     fn = lib().vnni_conv2d_u8s8 if vnni else lib().oracle_conv2d_u8s8
     rc = fn(_p(x), _p(w), _p(bias), _p(o32), _p(o8), sh, n, cc, h, wd, cb, oc, kh, kw,

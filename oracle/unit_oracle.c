@@ -37,6 +37,7 @@
  */
 #include <stdint.h>
 #include <stddef.h>
+#include <stdlib.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -292,6 +293,48 @@ void oracle_gemm_f16f32(const f16 *A, const f16 *B, float *C, int M, int N, int 
  * ---------------------------------------------------------------------- */
 #define OWB 14 /* output positions kept in registers per inner block */
 
+#if UNIT_HAVE_VNNI
+/* One block of BR output rows x BC output columns (BR * BC = 14 accumulators) of one output-channel
+ * block, on an input that needs no bounds checks (pre-padded, as the reference feeds its kernels:
+ * apps/cpu/kernel/conv2d.py:50 convolves with padding 0 and cpu-shapes.log lists padded sizes).
+ * Fully unrolled over the block so that every accumulator stays in a register and the 4-byte
+ * activation group is a broadcast memory operand of vpdpbusd. */
+#define VNNI_BLOCK_FN(NAME, BR, BC)                                                                          \
+  static inline void NAME(const uint8_t *x, const int8_t *w, size_t x_row, size_t x_chunk, int cb, int Cc,    \
+                          int KH, int KW, int sh, int sw, __m512i *acc) {                                     \
+    const int c4 = cb / 4;                                                                                    \
+    for (int j = 0; j < BR * BC; ++j) acc[j] = _mm512_setzero_si512();                                       \
+    for (int ic = 0; ic < Cc; ++ic)                                                                           \
+      for (int kh = 0; kh < KH; ++kh)                                                                         \
+        for (int kw = 0; kw < KW; ++kw) {                                                                     \
+          const int8_t *wp = w + (((size_t)ic * KH + kh) * KW + kw) * (size_t)(c4 * 64);                      \
+          const uint8_t *xp = x + (size_t)ic * x_chunk + (size_t)kh * x_row + (size_t)kw * cb;                \
+          for (int m = 0; m < c4; ++m) {                                                                      \
+            const __m512i wv = _mm512_loadu_si512((const void *)(wp + m * 64));                               \
+            _Pragma("GCC unroll 14") for (int j = 0; j < BR * BC; ++j) {                                      \
+              int32_t d;                                                                                      \
+              memcpy(&d, xp + (size_t)(j / BC) * sh * x_row + (size_t)(j % BC) * sw * cb + m * 4, 4);         \
+              acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);                                 \
+            }                                                                                                 \
+          }                                                                                                   \
+        }                                                                                                     \
+  }
+VNNI_BLOCK_FN(vnni_block_1x14, 1, 14)
+VNNI_BLOCK_FN(vnni_block_2x7, 2, 7)
+
+static inline void vnni_store(const __m512i acc, const __m512i vb, int32_t *o32, uint8_t *o8, int shift) {
+  if (o8) {
+    __m512i v = _mm512_add_epi32(_mm512_add_epi32(acc, vb), _mm512_set1_epi32(1 << (shift - 1)));
+    v = _mm512_srai_epi32(v, (unsigned)shift);
+    v = _mm512_max_epi32(v, _mm512_setzero_si512());
+    v = _mm512_min_epi32(v, _mm512_set1_epi32(255));
+    _mm_storeu_si128((__m128i *)o8, _mm512_cvtepi32_epi8(v));
+  } else {
+    _mm512_storeu_si512((void *)o32, _mm512_add_epi32(acc, vb));
+  }
+}
+#endif
+
 int vnni_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
                      int32_t *out_s32, uint8_t *out_u8, int shift,
                      int N, int Cc, int H, int W, int cb, int Oc,
@@ -300,6 +343,58 @@ int vnni_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
   const int OH = (H + 2 * ph - KH) / sh + 1;
   const int OW = (W + 2 * pw - KW) / sw + 1;
   const int c4 = cb / 4;
+  /* Fast form: the reference's kernels run on a pre-padded input; pad once here, then every block
+   * is interior.  Blocks of 1 x 14 output positions, or 2 x 7 for 7-wide maps; a ragged last block
+   * is moved back to overlap its neighbour (the same values are written twice). */
+  const int wide = OW >= 14, two_rows = !wide && OW == 7 && OH >= 2;
+  if (wide || two_rows) {
+    const int HP = H + 2 * ph, WP = W + 2 * pw;
+    const uint8_t *xin = x;
+    uint8_t *padded = NULL;
+    if (ph || pw) {
+      padded = (uint8_t *)malloc((size_t)N * Cc * HP * WP * cb);
+      if (!padded) return -3;
+#pragma omp parallel for collapse(2) schedule(static)
+      for (int nc = 0; nc < N * Cc; ++nc)
+        for (int h = 0; h < HP; ++h) {
+          uint8_t *dst = padded + ((size_t)nc * HP + h) * (size_t)WP * cb;
+          if (h < ph || h >= ph + H) {
+            memset(dst, 0, (size_t)WP * cb);
+          } else {
+            memset(dst, 0, (size_t)pw * cb);
+            memcpy(dst + (size_t)pw * cb, x + ((size_t)nc * H + (h - ph)) * (size_t)W * cb, (size_t)W * cb);
+            memset(dst + (size_t)(pw + W) * cb, 0, (size_t)pw * cb);
+          }
+        }
+      xin = padded;
+    }
+    const size_t x_row = (size_t)WP * cb, x_chunk = (size_t)HP * x_row;
+    const int br = wide ? 1 : 2, bc = wide ? 14 : 7;
+    const int nrb = (OH + br - 1) / br, ncb = (OW + bc - 1) / bc;
+#pragma omp parallel for collapse(3) schedule(static)
+    for (int n = 0; n < N; ++n)
+      for (int oc = 0; oc < Oc; ++oc)
+        for (int rb = 0; rb < nrb; ++rb)
+          for (int cbk = 0; cbk < ncb; ++cbk) {
+            int oh0 = rb * br, ow0 = cbk * bc;
+            if (oh0 + br > OH) oh0 = OH - br;
+            if (ow0 + bc > OW) ow0 = OW - bc;
+            const uint8_t *xb = xin + (size_t)n * Cc * x_chunk + (size_t)oh0 * sh * x_row + (size_t)ow0 * sw * cb;
+            const int8_t *wb = w + (size_t)oc * Cc * KH * KW * (size_t)(c4 * 64);
+            __m512i acc[OWB];
+            if (wide) vnni_block_1x14(xb, wb, x_row, x_chunk, cb, Cc, KH, KW, sh, sw, acc);
+            else vnni_block_2x7(xb, wb, x_row, x_chunk, cb, Cc, KH, KW, sh, sw, acc);
+            const __m512i vb = bias ? _mm512_loadu_si512((const void *)(bias + oc * 16)) : _mm512_setzero_si512();
+            for (int j = 0; j < br * bc; ++j) {
+              if (oh0 + j / bc < rb * br || ow0 + j % bc < cbk * bc) continue;  /* the neighbour block's */
+              const size_t o = ((((size_t)n * Oc + oc) * OH + (oh0 + j / bc)) * OW + (ow0 + j % bc)) * 16;
+              vnni_store(acc[j], vb, out_s32 ? out_s32 + o : NULL, out_u8 ? out_u8 + o : NULL, shift);
+            }
+          }
+    free(padded);
+    return 0;
+  }
+  /* General form (narrow or odd-sized maps): bounds-checked taps. */
   const int nblk = (OW + OWB - 1) / OWB;
 #pragma omp parallel for collapse(3) schedule(static)
   for (int n = 0; n < N; ++n)
@@ -320,42 +415,21 @@ int vnni_conv2d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias,
               for (int kw = 0; kw < KW; ++kw) {
                 const int8_t *wp = w + ((((size_t)oc * Cc + ic) * KH + kh) * KW + kw) * (size_t)(c4 * 64);
                 const int iwb = ow0 * sw + kw - pw;
-                const int interior = (iwb >= 0) && (iwb + (nw - 1) * sw < W);
                 for (int m = 0; m < c4; ++m) {
                   const __m512i wv = _mm512_loadu_si512((const void *)(wp + m * 64));
-                  if (interior && nw == OWB) {
-#pragma GCC unroll 14
-                    for (int j = 0; j < OWB; ++j) {
-                      int32_t d;
-                      memcpy(&d, xrow + (size_t)(iwb + j * sw) * cb + m * 4, 4);
-                      acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);
-                    }
-                  } else {
-                    for (int j = 0; j < nw; ++j) {
-                      const int iw = iwb + j * sw;
-                      if (iw < 0 || iw >= W) continue;
-                      int32_t d;
-                      memcpy(&d, xrow + (size_t)iw * cb + m * 4, 4);
-                      acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);
-                    }
+                  for (int j = 0; j < nw; ++j) {
+                    const int iw = iwb + j * sw;
+                    if (iw < 0 || iw >= W) continue;
+                    int32_t d;
+                    memcpy(&d, xrow + (size_t)iw * cb + m * 4, 4);
+                    acc[j] = _mm512_dpbusd_epi32(acc[j], _mm512_set1_epi32(d), wv);
                   }
                 }
               }
             }
           const size_t o = ((((size_t)n * Oc + oc) * OH + oh) * OW + ow0) * 16;
-          if (out_u8) {
-            const __m512i rnd = _mm512_set1_epi32(1 << (shift - 1));
-            for (int j = 0; j < nw; ++j) {
-              __m512i v = _mm512_add_epi32(_mm512_add_epi32(acc[j], vb), rnd);
-              v = _mm512_srai_epi32(v, (unsigned)shift);
-              v = _mm512_max_epi32(v, _mm512_setzero_si512());
-              v = _mm512_min_epi32(v, _mm512_set1_epi32(255));
-              _mm_storeu_si128((__m128i *)(out_u8 + o + (size_t)j * 16), _mm512_cvtepi32_epi8(v));
-            }
-          } else {
-            for (int j = 0; j < nw; ++j)
-              _mm512_storeu_si512((void *)(out_s32 + o + (size_t)j * 16), _mm512_add_epi32(acc[j], vb));
-          }
+          for (int j = 0; j < nw; ++j)
+            vnni_store(acc[j], vb, out_s32 ? out_s32 + o + (size_t)j * 16 : NULL, out_u8 ? out_u8 + o + (size_t)j * 16 : NULL, shift);
         }
   return 0;
 #else

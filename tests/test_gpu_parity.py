@@ -477,7 +477,7 @@ def test_error_behaviour(U):
     x = torch.zeros((1, 4, 8, 8, 16), dtype=torch.uint8, device='cuda')
     w = torch.zeros((4, 4, 3, 3, 4, 16, 4), dtype=torch.int8, device='cuda')
     with pytest.raises(TypeError):
-        U.conv2d_NCHWc_int8(x.to(torch.int8), w)
+        U.conv2d_NCHWc_int8(x.to(torch.int32), w)                # (s8 data is accepted: signed activations)
     with pytest.raises(ValueError):
         U.conv2d_NCHWc_int8(x[:, :2], w)                       # channel mismatch
     with pytest.raises(ValueError):

@@ -75,6 +75,15 @@ def test_golden_dense_and_fp16(oracle, golden):
     (1, 16, 12, 9, 16, 1, 7, 1, 0),
     (1, 16, 12, 9, 16, 7, 1, 1, 3),
     (3, 48, 8, 8, 64, 1, 1, 2, 0),
+    # the blocked forms of the AVX-512 restatement: rows of 14 and more outputs (1 x 14 blocks, the
+    # last one moved back when ragged), 7-wide maps (2 x 7 blocks, odd row count), with and without padding
+    (2, 32, 14, 14, 32, 3, 3, 1, 1),
+    (1, 16, 19, 17, 16, 3, 3, 1, 1),
+    (1, 16, 33, 31, 32, 3, 3, 2, 1),
+    (2, 32, 7, 7, 32, 3, 3, 1, 1),
+    (1, 48, 14, 14, 16, 3, 3, 2, 1),
+    (1, 16, 9, 9, 16, 3, 3, 1, 0),
+    (2, 16, 30, 30, 16, 1, 1, 1, 0),
 ])
 def test_c_oracle_equals_numpy_definition(oracle, n, ci, h, w, co, kh, kw, s, p):
     rng = np.random.default_rng(n * 1000 + ci + kh)

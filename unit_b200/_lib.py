@@ -52,6 +52,7 @@ SIGNATURES = {
     'unit_device_status': (_ci, [_vp]),
     'unit_launch_count': (ctypes.c_uint64, []),
     'unit_trace_attach': (_ci, [_vp, _ci]),
+    'unit_tensor_peak': (_ci, [_ci, _ci, _ci, _ci, ctypes.POINTER(ctypes.c_double), _vp]),
     'unit_variant_count': (_ci, []),
     'unit_variant_name': (ctypes.c_char_p, [_ci]),
     'unit_variant_launches': (ctypes.c_uint64, [_ci]),

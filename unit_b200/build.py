@@ -8,7 +8,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, 'libunit_b200.so')
 _SOURCES = [os.path.join(_HERE, 'csrc', 'unit_abi.cu')]
-_DEPS = _SOURCES + [os.path.join(_HERE, 'csrc', 'igemm_sm100.cuh'),
+_DEPS = _SOURCES + [os.path.join(_HERE, 'csrc', 'igemm_sm100.cuh'), os.path.join(_HERE, 'csrc', 'tensor_peak.cuh'),
                     os.path.join(os.path.dirname(_HERE), 'include', 'unit_b200.h')]
 
 

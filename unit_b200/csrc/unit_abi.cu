@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "igemm_sm100.cuh"
+#include "tensor_peak.cuh"
 
 namespace unit {
 
@@ -992,6 +993,14 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles) {
   g_trace_cap.store(d_buf ? capacity_tiles : 0);
   g_trace.store(static_cast<unsigned long long *>(d_buf));
   return UNIT_OK;
+}
+
+int unit_tensor_peak(int32_t f16, int32_t n, int32_t issuers, int32_t iters, double *ops_per_second, void *stream) {
+  int rc = check_arch();
+  if (rc) return rc;
+  unsigned int *err = error_word_address();
+  if (err == nullptr) return UNIT_ERR_LAUNCH;
+  return run_tensor_peak(f16 != 0, n, issuers, iters, err, ops_per_second, static_cast<cudaStream_t>(stream));
 }
 
 int unit_variant_count(void) { return kMaxVariants; }

@@ -87,15 +87,20 @@ class PackedWeights:
         self.kind = kind
         self.buf = buf
         self.key = key
-        # the pack kernel was queued on the stream current at pack time: other streams wait for it
-        self._stream = _stream()
+        # the pack kernel was queued on the stream current at pack time: other streams wait for it once
         self._ready = torch.cuda.Event()
         self._ready.record()
+        self._synced = {_stream()}
 
     def sync_to_current_stream(self) -> None:
-        """Make the current stream wait for the pack kernel if it is not the stream that packed."""
-        if self._ready is not None and _stream() != self._stream:
-            torch.cuda.current_stream().wait_event(self._ready)
+        """Make the current stream wait for the pack kernel, once per stream.  (Not while the stream
+        is being captured into a CUDA graph: a captured stream cannot wait for work outside the
+        capture, and a capture is preceded by a warm-up call on that stream anyway.)"""
+        st = _stream()
+        if st in self._synced or torch.cuda.is_current_stream_capturing():
+            return
+        torch.cuda.current_stream().wait_event(self._ready)
+        self._synced.add(st)
 
     @property
     def nbytes(self) -> int:
@@ -389,6 +394,7 @@ def dense_dotprod(data: torch.Tensor, weight, bias: Optional[torch.Tensor] = Non
     m, k = int(data.shape[0]), int(data.shape[1])
     with torch.cuda.device(data.device):
         pw = weight if isinstance(weight, PackedWeights) else pack_dense_weights_int8(weight)
+        pw.sync_to_current_stream()
         if pw.kind != 'dense_i8':
             raise ValueError('weight was packed for a different operator')
         _, n, pk, _t = pw.key
@@ -496,6 +502,7 @@ def conv2d_NCHW16c_OHWI16o(a: torch.Tensor, b, stride_h: int = 1, stride_w: int 
     n, cc, h, w, _ = (int(s) for s in a.shape)
     with torch.cuda.device(a.device):
         pw = b if isinstance(b, PackedWeights) else pack_conv_weights_f16(b)
+        pw.sync_to_current_stream()
         if pw.kind != 'conv_f16':
             raise ValueError('b was packed for a different operator')
         _, c_out, c_in, kh, kw = pw.key
@@ -547,6 +554,7 @@ def gemm_f16f32(a: torch.Tensor, b, *, out: Optional[torch.Tensor] = None) -> to
     m, k = int(a.shape[0]), int(a.shape[1])
     with torch.cuda.device(a.device):
         pw = b if isinstance(b, PackedWeights) else pack_gemm_weights_f16(b)
+        pw.sync_to_current_stream()
         if pw.kind != 'gemm_f16':
             raise ValueError('b was packed for a different operator')
         _, n, pk = pw.key
