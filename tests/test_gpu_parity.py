@@ -394,6 +394,17 @@ def test_layout_kernels_match_numpy(U):
         y = U.pack_data_nchwc(dev(x), cb)
         assert np.array_equal(y.cpu().numpy(), no.pack_nchw_to_nchwc(x, cb))
         assert np.array_equal(U.unpack_data_nchwc(y, 19).cpu().numpy(), x)
+    # shapes whose rows are whole 4-byte words take the vectorised kernels (register transpose,
+    # 16-byte stores); channel counts that do not fill the last block, every element size
+    for shape, dt in (((3, 19, 6, 8), np.uint8), ((2, 37, 12, 12), np.uint8), ((2, 35, 5, 6), np.float16),
+                      ((2, 21, 3, 5), np.int32), ((4, 3, 16, 16), np.uint8)):
+        xv = rng.integers(0, 200, shape).astype(dt)
+        for cb in (4, 16):
+            yv = U.pack_data_nchwc(dev(xv), cb)
+            assert np.array_equal(yv.cpu().numpy(), no.pack_nchw_to_nchwc(xv, cb)), (shape, dt, cb)
+            assert np.array_equal(U.unpack_data_nchwc(yv, shape[1]).cpu().numpy(), xv), (shape, dt, cb)
+    with pytest.raises(ValueError):      # fewer channels than the stored blocks could hold one block less of
+        U.unpack_data_nchwc(U.pack_data_nchwc(dev(x), 4), 3)
     xf = rng.standard_normal((2, 32, 4, 4)).astype(np.float16)
     assert np.array_equal(U.pack_data_nchwc(dev(xf)).cpu().numpy(), no.pack_nchw_to_nchwc(xf))
     xi = rng.integers(-2 ** 31, 2 ** 31 - 1, (2, 16, 3, 3), dtype=np.int32)

@@ -84,7 +84,8 @@ SIGNATURES = {
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """The in-tree library; UNIT_B200_LIB names another build of it (comparison runs of two builds)."""
+    return os.environ.get('UNIT_B200_LIB') or _build.LIB_PATH
 
 
 def lib() -> ctypes.CDLL:

@@ -280,8 +280,120 @@ static int launch_pack(const PackParams &pp, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
-// layout kernels (bandwidth work: one 16-byte store per thread)
+// layout kernels (bandwidth work)
 // ---------------------------------------------------------------------------
+// NCHW <-> [n][c/CB][hw][CB] as a register transpose of 4-byte words.  A thread owns one channel
+// block and the P = 4 / EB pixels of one 4-byte word: on the NCHW side it touches one word per
+// channel, and consecutive threads touch consecutive words of the same channel row (a warp reads
+// or writes 128 contiguous bytes per instruction); on the blocked side its P pixels x CB channels
+// are P * CB * EB contiguous bytes, moved as 16-byte vectors.  Needs h * w to be a multiple of P and
+// 16-byte aligned tensors; other shapes take the element loops below.
+template <int EB, int CB>
+__device__ __forceinline__ void transpose_words(const uint32_t (&in)[CB], uint32_t (&out)[CB]) {
+  // in[c] = P pixels of channel c;  out = pixel-major: P pixels x CB channels, EB bytes each
+  if constexpr (EB == 4) {
+#pragma unroll
+    for (int c = 0; c < CB; ++c) out[c] = in[c];
+  } else if constexpr (EB == 2) {
+#pragma unroll
+    for (int q = 0; q < CB / 2; ++q) {
+      out[q] = __byte_perm(in[2 * q], in[2 * q + 1], 0x5410);           // pixel 0: low halves
+      out[CB / 2 + q] = __byte_perm(in[2 * q], in[2 * q + 1], 0x7632);  // pixel 1: high halves
+    }
+  } else {
+#pragma unroll
+    for (int px = 0; px < 4; ++px)
+#pragma unroll
+      for (int q = 0; q < CB / 4; ++q) {
+        const uint32_t sel = (uint32_t)((4 + px) << 4 | px);
+        const uint32_t lo = __byte_perm(in[4 * q], in[4 * q + 1], sel);
+        const uint32_t hi = __byte_perm(in[4 * q + 2], in[4 * q + 3], sel);
+        out[px * (CB / 4) + q] = __byte_perm(lo, hi, 0x5410);
+      }
+  }
+}
+// the inverse: in = pixel-major words, out[c] = P pixels of channel c
+template <int EB, int CB>
+__device__ __forceinline__ void untranspose_words(const uint32_t (&in)[CB], uint32_t (&out)[CB]) {
+  if constexpr (EB == 4) {
+#pragma unroll
+    for (int c = 0; c < CB; ++c) out[c] = in[c];
+  } else if constexpr (EB == 2) {
+#pragma unroll
+    for (int q = 0; q < CB / 2; ++q) {
+      out[2 * q] = __byte_perm(in[q], in[CB / 2 + q], 0x5410);
+      out[2 * q + 1] = __byte_perm(in[q], in[CB / 2 + q], 0x7632);
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < CB / 4; ++q) {
+      // words of pixels 0..3 holding channels 4q .. 4q+3
+      const uint32_t p0 = in[q], p1 = in[CB / 4 + q], p2 = in[2 * (CB / 4) + q], p3 = in[3 * (CB / 4) + q];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t sel = (uint32_t)((4 + k) << 4 | k);
+        out[4 * q + k] = __byte_perm(__byte_perm(p0, p1, sel), __byte_perm(p2, p3, sel), 0x5410);
+      }
+    }
+  }
+}
+
+template <int EB, int CB>
+__global__ void nchw_to_nchwc_vec_kernel(const uint32_t *__restrict__ src, uint32_t *__restrict__ dst, int n, int c,
+                                         long long hw_words) {
+  const int cc = (c + CB - 1) / CB;
+  const long long total = (long long)n * cc * hw_words;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long wpos = idx % hw_words;
+    const long long t = idx / hw_words;
+    const int chunk = (int)(t % cc);
+    const long long img = t / cc;
+    uint32_t in[CB], out[CB];
+#pragma unroll
+    for (int k = 0; k < CB; ++k) {
+      const int ch = chunk * CB + k;
+      in[k] = ch < c ? __ldg(src + (img * c + ch) * hw_words + wpos) : 0u;
+    }
+    transpose_words<EB, CB>(in, out);
+    uint32_t *d = dst + idx * CB;
+    if constexpr (CB >= 4) {
+#pragma unroll
+      for (int q = 0; q < CB / 4; ++q)
+        reinterpret_cast<uint4 *>(d)[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+    }
+  }
+}
+
+template <int EB, int CB>
+__global__ void nchwc_to_nchw_vec_kernel(const uint32_t *__restrict__ src, uint32_t *__restrict__ dst, int n, int c,
+                                         int cb_total, long long hw_words) {
+  // cb_total = stored channel blocks of the source; only the first c channels are written
+  const long long total = (long long)n * cb_total * hw_words;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long wpos = idx % hw_words;
+    const long long t = idx / hw_words;
+    const int chunk = (int)(t % cb_total);
+    const long long img = t / cb_total;
+    if (chunk * CB >= c) continue;
+    uint32_t in[CB], out[CB];
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src + idx * CB);
+#pragma unroll
+    for (int q = 0; q < CB / 4; ++q) {
+      const uint4 v = __ldg(s4 + q);
+      in[4 * q] = v.x; in[4 * q + 1] = v.y; in[4 * q + 2] = v.z; in[4 * q + 3] = v.w;
+    }
+    untranspose_words<EB, CB>(in, out);
+#pragma unroll
+    for (int k = 0; k < CB; ++k) {
+      const int ch = chunk * CB + k;
+      if (ch < c) dst[(img * c + ch) * hw_words + wpos] = out[k];
+    }
+  }
+}
+
+// element loops: any shape
 template <typename T>
 __global__ void nchw_to_nchwc_kernel(const T *__restrict__ src, T *__restrict__ dst, int n, int c, int h, int w,
                                      int cb) {
@@ -525,10 +637,10 @@ static unsigned int *error_word_address() {
   return cached[dev];
 }
 
-// Fills the tile fields of the plan's parameters and picks the sub-tile count.  max_mt = 1 for
-// operand paths that only small problems reach.
-template <int AMODE, int EPI, bool F16>
-static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = nullptr, int max_mt = 2) {
+// Fills the tile fields of the plan's parameters and picks the sub-tile count.  MAX_MT = 1 for
+// operand paths that only small problems reach (no two-sub-tile variant is compiled for them).
+template <int AMODE, int EPI, bool F16, int MAX_MT = 2>
+static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = nullptr) {
   IgemmParams &p = pl.p;
   if (tmap_in) memcpy(pl.map, tmap_in, sizeof(CUtensorMap));
   else memset(pl.map, 0, sizeof(pl.map));
@@ -545,7 +657,9 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
   if (p.a_signed == 0) p.fold_bias = use_fold() ? 1 : 0;  // (the bias step's constant block is u8)
   const int sms = sm_count();
   pl.magic = kPlanMagic;
-  if (max_mt >= 2 && choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2>(pl, c, sms);
+  if constexpr (MAX_MT >= 2) {
+    if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2>(pl, c, sms);
+  }
   return prepare_mt<AMODE, EPI, F16, 1>(pl, c, sms);
 }
 
@@ -950,6 +1064,18 @@ static int static_scratch_address(void **out) {
   return UNIT_OK;
 }
 
+template <int EB, int CB>
+static void launch_pack_vec(const void *src, void *dst, int n, int c, long long hw_words, cudaStream_t st) {
+  const long long total = (long long)n * ((c + CB - 1) / CB) * hw_words;
+  nchw_to_nchwc_vec_kernel<EB, CB><<<grid_for(total), 256, 0, st>>>(static_cast<const uint32_t *>(src), static_cast<uint32_t *>(dst), n, c, hw_words);
+}
+template <int EB, int CB>
+static void launch_unpack_vec(const void *src, void *dst, int n, int c, long long hw_words, cudaStream_t st) {
+  const int cb_total = (c + CB - 1) / CB;
+  const long long total = (long long)n * cb_total * hw_words;
+  nchwc_to_nchw_vec_kernel<EB, CB><<<grid_for(total), 256, 0, st>>>(static_cast<const uint32_t *>(src), static_cast<uint32_t *>(dst), n, c, cb_total, hw_words);
+}
+
 }  // namespace unit
 
 using namespace unit;
@@ -1236,7 +1362,7 @@ static int run_dense(bool f16, int32_t m, int32_t n, int32_t k, const void *a, i
     rc = f16 ? prepare<A_DENSE_TMA, EPI_RAW_ROWS, true>(pl, c, &map) : prepare<A_DENSE_TMA, EPI_RAW_ROWS, false>(pl, c, &map);
   } else {
     // matrices below the tensor-map size limit: the cp.async gather, single sub-tiles
-    rc = f16 ? prepare<A_DENSE, EPI_RAW_ROWS, true>(pl, c, nullptr, 1) : prepare<A_DENSE, EPI_RAW_ROWS, false>(pl, c, nullptr, 1);
+    rc = f16 ? prepare<A_DENSE, EPI_RAW_ROWS, true, 1>(pl, c) : prepare<A_DENSE, EPI_RAW_ROWS, false, 1>(pl, c);
   }
   return rc ? rc : run_plan(pl, st);
 }
@@ -1286,13 +1412,28 @@ int unit_pack_data_nchw_to_nchwc(const void *src, void *dst, int32_t n, int32_t 
   if (!src || !dst) return UNIT_ERR_NULL;
   if (n < 1 || c < 1 || h < 1 || w < 1) return UNIT_ERR_SHAPE;
   if (cb != 4 && cb != 16) return UNIT_ERR_LAYOUT;
+  if (eb != 1 && eb != 2 && eb != 4) return UNIT_ERR_LAYOUT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long total = (long long)n * ((c + cb - 1) / cb) * h * w;
-  const unsigned g = grid_for(total);
-  if (eb == 1) nchw_to_nchwc_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
-  else if (eb == 2) nchw_to_nchwc_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
-  else if (eb == 4) nchw_to_nchwc_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
-  else return UNIT_ERR_LAYOUT;
+  const long long hw = (long long)h * w;
+  if (hw * eb % 4 == 0 && aligned16(src) && aligned16(dst)) {
+    // register transpose of 4-byte words, 16-byte stores
+    const long long hww = hw * eb / 4;
+    if (cb == 16) {
+      if (eb == 1) launch_pack_vec<1, 16>(src, dst, n, c, hww, st);
+      else if (eb == 2) launch_pack_vec<2, 16>(src, dst, n, c, hww, st);
+      else launch_pack_vec<4, 16>(src, dst, n, c, hww, st);
+    } else {
+      if (eb == 1) launch_pack_vec<1, 4>(src, dst, n, c, hww, st);
+      else if (eb == 2) launch_pack_vec<2, 4>(src, dst, n, c, hww, st);
+      else launch_pack_vec<4, 4>(src, dst, n, c, hww, st);
+    }
+  } else {
+    const long long total = (long long)n * ((c + cb - 1) / cb) * hw;
+    const unsigned g = grid_for(total);
+    if (eb == 1) nchw_to_nchwc_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
+    else if (eb == 2) nchw_to_nchwc_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
+    else nchw_to_nchwc_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
+  }
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
 }
@@ -1302,12 +1443,26 @@ int unit_unpack_data_nchwc_to_nchw(const void *src, void *dst, int32_t n, int32_
   if (!src || !dst) return UNIT_ERR_NULL;
   if (n < 1 || c < 1 || h < 1 || w < 1) return UNIT_ERR_SHAPE;
   if (cb != 4 && cb != 16) return UNIT_ERR_LAYOUT;
+  if (eb != 1 && eb != 2 && eb != 4) return UNIT_ERR_LAYOUT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned g = grid_for((long long)n * c * h * w);
-  if (eb == 1) nchwc_to_nchw_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
-  else if (eb == 2) nchwc_to_nchw_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
-  else if (eb == 4) nchwc_to_nchw_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
-  else return UNIT_ERR_LAYOUT;
+  const long long hw = (long long)h * w;
+  if (hw * eb % 4 == 0 && aligned16(src) && aligned16(dst)) {
+    const long long hww = hw * eb / 4;
+    if (cb == 16) {
+      if (eb == 1) launch_unpack_vec<1, 16>(src, dst, n, c, hww, st);
+      else if (eb == 2) launch_unpack_vec<2, 16>(src, dst, n, c, hww, st);
+      else launch_unpack_vec<4, 16>(src, dst, n, c, hww, st);
+    } else {
+      if (eb == 1) launch_unpack_vec<1, 4>(src, dst, n, c, hww, st);
+      else if (eb == 2) launch_unpack_vec<2, 4>(src, dst, n, c, hww, st);
+      else launch_unpack_vec<4, 4>(src, dst, n, c, hww, st);
+    }
+  } else {
+    const unsigned g = grid_for((long long)n * c * hw);
+    if (eb == 1) nchwc_to_nchw_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t *)src, (uint8_t *)dst, n, c, h, w, cb);
+    else if (eb == 2) nchwc_to_nchw_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *)src, (uint16_t *)dst, n, c, h, w, cb);
+    else nchwc_to_nchw_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *)src, (uint32_t *)dst, n, c, h, w, cb);
+  }
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? UNIT_OK : UNIT_ERR_LAUNCH;
 }

@@ -442,8 +442,8 @@ def unpack_data_nchwc(x: torch.Tensor, channels: Optional[int] = None) -> torch.
     x = x.contiguous()
     n, cc, h, w, cb = (int(s) for s in x.shape)
     c = cc * cb if channels is None else int(channels)
-    if c < 1 or c > cc * cb:
-        raise ValueError('channels out of range')
+    if c < 1 or c > cc * cb or (c + cb - 1) // cb != cc:
+        raise ValueError(f'channels must fill {cc} blocks of {cb} (last block partly): got {c}')
     y = torch.empty((n, c, h, w), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         check(L.unit_unpack_data_nchwc_to_nchw(_ptr(x), _ptr(y), n, c, h, w, cb, x.element_size(), _stream()),
