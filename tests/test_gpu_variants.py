@@ -59,12 +59,16 @@ INT8_CASES = {
     'gather_mt2': (32, 16, 225, 225, 16, 1, 9, 0, 16),
     'stem_gather_mt1': (2, 4, 33, 35, 32, 7, 2, 3, 4),
     'stem_gather_mt2': (8, 4, 227, 227, 16, 3, 2, 1, 4),
+    # few tiles and a long reduction: split-K over a thread-block cluster (6 CTAs per tile here)
+    'box_splitk': (1, 256, 24, 24, 64, 3, 1, 1, 16),
+    'im2col_splitk': (1, 256, 24, 24, 64, 3, 2, 1, 16),
 }
 INT8_VARIANTS = {
     'box_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'box_mt2': 'A_CONV_BOX, {}, i8, MT=2',
     'im2col_mt1': 'A_CONV_TMA, {}, i8, MT=1', 'im2col_mt2': 'A_CONV_TMA, {}, i8, MT=2',
     'gather_mt1': 'A_CONV_I8, {}, i8, MT=1', 'gather_mt2': 'A_CONV_I8, {}, i8, MT=2',
     'stem_gather_mt1': 'A_STEM_I8, {}, i8, MT=1', 'stem_gather_mt2': 'A_STEM_I8, {}, i8, MT=2',
+    'box_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K', 'im2col_splitk': 'A_CONV_TMA, {}, i8, MT=1, split-K',
 }
 
 
@@ -104,6 +108,8 @@ FP16_CASES = {
     'im2col_mt2': ((8, 16, 112, 112, 16, 3, 2, 1), 'A_CONV_TMA, EPI_RAW_NCHWC, f16, MT=2'),
     'gather_mt1': ((2, 32, 13, 11, 32, 3, 2, 1), 'A_CONV_F16, EPI_RAW_NCHWC, f16, MT=1'),
     'gather_mt2': ((32, 16, 225, 225, 16, 1, 9, 0), 'A_CONV_F16, EPI_RAW_NCHWC, f16, MT=2'),
+    'box_splitk': ((1, 256, 24, 24, 64, 3, 1, 1), 'A_CONV_BOX, EPI_RAW_NCHWC, f16, MT=1, split-K'),
+    'im2col_splitk': ((1, 256, 24, 24, 64, 3, 2, 1), 'A_CONV_TMA, EPI_RAW_NCHWC, f16, MT=1, split-K'),
 }
 
 
@@ -124,7 +130,9 @@ def test_fp16_conv_variants(U, oracle, case):
 DENSE_CASES = {
     # (m, n, k): matrices of at least 128 KB arrive by tensor copies (128-byte-swizzled rows when K is a
     # multiple of 128 bytes, 16-byte columns otherwise); smaller ones by the cp.async gather
-    'tma_sw128_mt1': ((300, 512, 1024), 'A_DENSE_TMA, EPI_RAW_ROWS, {}, MT=1'),
+    'tma_sw128_mt1': ((10000, 64, 384), 'A_DENSE_TMA, EPI_RAW_ROWS, {}, MT=1'),
+    # the reference's split-K GEMM shape (poc/tensorcore/gemm-prefetch.cu: 128 x 768 x 3072): three tiles, eight CTAs each
+    'tma_splitk': ((128, 768, 3072), 'A_DENSE_TMA, EPI_RAW_ROWS, {}, MT=1, split-K'),
     'tma_cols_mt1': ((2000, 64, 144), 'A_DENSE_TMA, EPI_RAW_ROWS, {}, MT=1'),
     'tma_mt2': ((20000, 16, 128), 'A_DENSE_TMA, EPI_RAW_ROWS, {}, MT=2'),
     'gather_mt1': ((129, 48, 80), 'A_DENSE, EPI_RAW_ROWS, {}, MT=1'),
@@ -166,6 +174,33 @@ def test_tensor_map_size_boundary(U, oracle):
             assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (s, s), (1, 1)))
             name = f'igemm_kernel<{path}, EPI_RAW_NCHWC, i8, MT=1>'
             assert variant_counts()[name] > before[name], (h, w, s, name)
+
+
+@pytest.mark.parametrize('n,ci,hw,co,k,s', [
+    (12, 256, 14, 256, 3, 1),     # 19 tiles -> clusters of 7
+    (32, 256, 14, 256, 3, 1),     # 49 tiles -> clusters of 3 (the ResNet-50 stage-3 3x3 at batch 32)
+    (44, 64, 14, 320, 1, 1),      # 68 tiles x 2 column blocks: just under the limit of half the SMs -> no split
+    (32, 1024, 14, 256, 1, 1),    # clusters of 3, short slices (8 stages)
+    (32, 512, 7, 512, 3, 1),      # 26 tiles -> clusters of 5, two column blocks
+    (1, 512, 28, 128, 1, 1),      # 7 tiles -> clusters of 8
+    (20, 512, 14, 512, 3, 2),     # im2col copies, 8 x 2 tiles
+    (33, 2048, 7, 208, 1, 1),     # column block of 208: 13 groups dealt to the cluster's CTAs unevenly
+])
+def test_split_k_cluster_sizes_bit_exact(U, oracle, n, ci, hw, co, k, s):
+    """Split-K with every cluster size: partial sums exchanged through distributed shared memory, bias
+    added once, requantised by the owners of the columns; integer sums, so still bit-exact."""
+    rng = np.random.default_rng(n * 131 + ci + co)
+    x = rng.integers(0, 256, (n, ci // 16, hw, hw, 16), dtype=np.uint8)
+    wt = rng.integers(-128, 128, (co // 16, ci // 16, k, k, 4, 16, 4), dtype=np.int8)
+    p = k // 2
+    for hi in (2 ** 15, 2 ** 28):     # biases that enter through the tensor core, and ones the drain adds
+        b = rng.integers(-hi, hi, co, dtype=np.int64).astype(np.int32)
+        got = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=s, padding=p, bias=dev(b), out_dtype='uint8')
+        gots = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=s, padding=p, bias=dev(b))
+        U.device_status()
+        vn = oracle.host_has_vnni()
+        assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (s, s), (p, p), bias=b, requant_shift=8, vnni=vn))
+        assert np.array_equal(gots.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (s, s), (p, p), bias=b, vnni=vn))
 
 
 def test_plan_then_run_equals_the_direct_call(U, oracle):

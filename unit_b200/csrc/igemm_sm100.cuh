@@ -94,7 +94,7 @@ constexpr uint32_t kFoldBytes = 2 * kFoldBBytes + 2 * 128 * 16;  // two sets + t
 #endif
 constexpr uint32_t kWaitHintNs = UNIT_WAIT_HINT_NS;  // longest suspension of one mbarrier probe
 constexpr int kBiasSmem = 256;  // bias values of the current N tile, staged in shared memory per accumulator set
-constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4, kErrWaitBias = 5;
+constexpr uint32_t kErrWaitFull = 1, kErrWaitEmpty = 2, kErrWaitTmemFull = 3, kErrWaitTmemEmpty = 4, kErrWaitBias = 5, kErrWaitPeer = 6;
 
 // n / d for 0 <= n < 2^31 with a host-computed multiplier (mul == 0: d is a power of two).
 struct FastDiv {
@@ -151,6 +151,10 @@ struct IgemmParams {
   int tmem_cols;  // TMEM columns to allocate: a power of two >= 32 that holds the accumulator sets
   unsigned long long wait_limit_ns;  // bound of every mbarrier wait
   int inject;     // diagnostics: 1 = the B producer issues nothing (the waits then run out)
+  // Split-K (kernel template parameter SPLITK): the CTAs of one thread-block cluster of ksplit CTAs
+  // share one tile; CTA `rank` accumulates pipeline stages [rank * ks_per, (rank + 1) * ks_per) and the
+  // partial accumulators are exchanged through distributed shared memory (see the kernel)
+  int ksplit, ks_per;
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
 };
@@ -187,6 +191,18 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Same test with acquire semantics at cluster scope (the barrier is arrived on by other CTAs).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Same test, but the thread may stay suspended for up to `hint_ns` before it reports "not yet".
 __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
@@ -207,12 +223,12 @@ struct WaitCtx {
   unsigned long long limit_ns;
 };
 #ifndef UNIT_SPIN_PROBES
-#define UNIT_SPIN_PROBES 8
+#define UNIT_SPIN_PROBES 1
 #endif
-// Bounded wait: gives up after the limit (or when another role already aborted).  The first few
-// probes spin, since most waits end within a few hundred cycles; later retries back off (suspended
-// try_wait plus a short sleep) so that waiting threads leave the issue slots and the shared-memory
-// pipe to the warps that have work.
+// Bounded wait: gives up after the limit (or when another role already aborted).  After the first
+// probe, retries back off (suspended try_wait plus a short sleep) so that waiting threads leave the
+// issue slots and the shared-memory pipe to the warps that have work.  (Measured: eight or
+// thirty-two spinning probes before the back-off cost 1.8 % on the batch-256 and batch-32 sweeps.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx &wc, uint32_t code) {
 #pragma unroll 1
   for (int i = 0; i < UNIT_SPIN_PROBES; ++i)
@@ -234,14 +250,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 // warp-wide instruction on one address) and the lanes agree by vote, so the warp stays converged.
 // Measured: a warp whose lane 0 polls while the other lanes are parked at a warp-level
 // synchronisation point runs that lane markedly slower (10-20 % on whole K-loop-bound layers).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx &wc, uint32_t code) {
+// (cluster_scope: the barrier is arrived on by other CTAs of the cluster, whose writes to this CTA's
+// shared memory the wait has to acquire.)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx &wc, uint32_t code,
+                                               bool cluster_scope = false) {
 #pragma unroll 1
   for (int i = 0; i < UNIT_SPIN_PROBES; ++i)
-    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
+    if (__all_sync(0xffffffffu, (cluster_scope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) ? 1 : 0)) return true;
   const unsigned long long t0 = global_timer_ns();
   bool timed_out = true;
   for (uint32_t it = 0; it < (1u << 26); ++it) {
-    if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, kWaitHintNs) ? 1 : 0)) return true;
+    if (__all_sync(0xffffffffu, (cluster_scope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait_hint(bar, parity, kWaitHintNs)) ? 1 : 0))
+      return true;
     __nanosleep(32);
     if ((it & 15u) == 15u) {
       if (__any_sync(0xffffffffu, *wc.abort_flag)) { timed_out = false; break; }
@@ -398,6 +418,32 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- thread-block cluster / distributed shared memory (split-K) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// one arrival on an mbarrier of another CTA of the cluster; releases this thread's earlier writes at cluster scope
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+// every thread of every CTA of the cluster: nobody leaves while a peer may still touch its shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Tile trace: CTA 0 records when each role passes a point of tile `lt` (slot 0-7).
 __device__ __forceinline__ void trace_mark(const IgemmParams &p, uint32_t lt, int slot) {
   if (p.trace != nullptr && blockIdx.x == 0 && lt < (uint32_t)p.trace_cap) p.trace[lt * 16u + slot] = (unsigned long long)clock64();
@@ -451,6 +497,8 @@ struct alignas(16) PipeShared {
   unsigned long long tfull[2];
   unsigned long long tempty[2];
   unsigned long long bready[2];  // per accumulator set: the bias of the set's next tile is staged
+  unsigned long long xfree[8];   // split-K: peer CTA r's operand ring may be overwritten with partial sums
+  unsigned long long xfull;      // split-K: every peer's partial sums for this CTA's columns have arrived
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -627,9 +675,10 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
   wide = need_wide;
 }
 
-template <int AMODE, int EPI, bool F16, int MT>
+template <int AMODE, int EPI, bool F16, int MT, bool SPLITK = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
+  static_assert(!SPLITK || (MT == 1 && a_mode_uses_tma(AMODE)), "split-K: single sub-tiles, tensor-copy-fed A operand");
   extern __shared__ __align__(1024) uint8_t smem[];  // (1 KB: a swizzled operand atom is 8 rows x 128 bytes)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -645,7 +694,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   volatile int *abort_flag = &ps->abort_flag;
   const WaitCtx wc{abort_flag, p.err, p.wait_limit_ns};
   // accumulator sets that fit in the 512 TMEM columns (2 = drain overlaps the next main loop)
-  const uint32_t nslots = (512u / ((uint32_t)MT * (uint32_t)p.bn)) >= 2u ? 2u : 1u;
+  // (split-K: a CTA has one tile only, so one set and all sixteen warps drain it)
+  const uint32_t nslots = (!SPLITK && (512u / ((uint32_t)MT * (uint32_t)p.bn)) >= 2u) ? 2u : 1u;
+  // Split-K: the cluster's CTAs share tile (cluster index); this CTA's stages are [ks_begin, ks_end).
+  // Otherwise tiles are dealt round-robin over the grid.
+  const uint32_t crank = SPLITK ? cluster_ctarank() : 0u;
+  const int tile0 = SPLITK ? (int)(blockIdx.x / (uint32_t)p.ksplit) : (int)blockIdx.x;
+  const int ks_begin = SPLITK ? (int)crank * p.ks_per : 0;
+  const int ks_end = SPLITK ? min(ks_begin + p.ks_per, p.k_stages) : p.k_stages;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -657,6 +713,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       mbar_init(smem_u32(&ps->tfull[i]), 1 + MT);        // the first issuing thread's arrival + one commit per issuer
       mbar_init(smem_u32(&ps->tempty[i]), kDrainWarps / nslots);  // the drain warps that serve the set
       mbar_init(smem_u32(&ps->bready[i]), kDrainWarps / nslots);
+    }
+    if constexpr (SPLITK) {
+      for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&ps->xfree[i]), 1);
+      mbar_init(smem_u32(&ps->xfull), (uint32_t)(p.ksplit - 1) * kDrainWarps);
     }
     ps->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -676,6 +736,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ps->tmem_base;
+  if constexpr (SPLITK) cluster_sync_all();  // every peer's barriers exist before anybody arrives on them
   // From here on this CTA holds its tensor memory, so a dependent kernel's CTA that becomes
   // resident on the same SM can never be the one that keeps this CTA waiting in tcgen05.alloc:
   // let the next kernel of the stream start its own prologue as soon as SMs become free.
@@ -689,6 +750,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   trace_mark_ns(p, 10);
 
   const int total_tiles = p.m_tiles * p.n_tiles;
+  const int tstep = SPLITK ? total_tiles : (int)gridDim.x;  // split-K: exactly one tile per CTA
 
   if (!a_mode_uses_tma(AMODE) && warp >= kFirstProducerWarp && warp < kFirstProducerWarp + 4) {
     // ===================== A producers =====================
@@ -696,7 +758,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t s = 0, ring_phase = 0;  // ring position and the number of wraps (mod 2)
     uint32_t lt = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+    for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
       const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       const long long m0 = (long long)m_tile * (kTileM * MT);
 
@@ -829,7 +891,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t s = 0, ring_phase = 0;
     uint32_t lt = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+    for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
       const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       // origin of this lane's sub-tile
       int c0 = 0, c1 = 0, c2 = 0;  // BOX: x (8-byte units), y, first image; TMA: w, h, image
@@ -870,18 +932,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // (box mode: jj counts chunks, which for fp16 are whole K steps of two columns)
       const int cpc = (AMODE == A_CONV_BOX) ? 1 : p.cols_per_chunk;
       const int half = jj % cpc;
-      int q0 = jj / cpc;  // chunk index along K
+      const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
+      int q0 = jj / cpc + ks_begin * chunk_step;  // chunk index along K of this lane's first column
       int kh = 0, kw = 0, ci = 0;
       if constexpr (AMODE != A_DENSE_TMA) {
         kh = q0 / (p.Cc * p.KW);
         kw = (q0 / p.Cc) % p.KW;
         ci = q0 % p.Cc;
       }
-      const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
       // row form: jj counts kernel rows of the stage, each copied once into the slot of its first column
       const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
       const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
-      for (int ks = 0; ks < p.k_stages; ++ks) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
           break;
@@ -945,10 +1007,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+      for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
         const int n_tile = tile - (int)fast_div((uint32_t)tile, p.div_n_tiles) * p.n_tiles;
         const uint8_t *src = p.b + (size_t)n_tile * p.k_stages * b_stage_bytes;
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
           if (!mbar_wait(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
             alive = false;
             break;
@@ -987,7 +1049,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;  // tiles done by this CTA
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++lt) {
+      for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
         const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
         const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
         // the drain warps arrive on "empty" after every drain of the set: its first use needs no wait
@@ -999,7 +1061,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (my_t == 0u) trace_mark(p, lt, 3);
         const uint32_t d_tmem = tmem_base + (slot * (uint32_t)MT + my_t) * (uint32_t)p.bn;  // this thread's accumulator
         uint32_t started = 0u;
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
           if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull)) {
             alive = false;
             break;
@@ -1051,7 +1113,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               break;
             }
             tc_fence_after();
-            if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0) {
+            // (split-K: the bias enters the first CTA's partial sum only)
+            if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0 && (!SPLITK || crank == 0u)) {
               const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
               const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
               tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
@@ -1096,14 +1159,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       dw = rr - dh * (uint32_t)p.box_w;
     }
     const long long gstride = (EPI == EPI_RAW_ROWS) ? 16 : (long long)ohw * 16;  // between 16-column groups
-    const int tile_step = (int)nslots * (int)gridDim.x;  // from one tile of this group to its next
+    const int tile_step = (int)nslots * tstep;  // from one tile of this group to its next
     // The set's bias: the column block it is prepared for, the verdict, and which of the two
     // integer buffers holds the values (it flips at every preparation, so that a warp preparing
     // the next tile never overwrites what a slower warp still reads for this one).
     int staged_n = -1;
     bool folded = true, wide = false;
     uint32_t ver = 0;
-    const int first_tile = blockIdx.x + (int)slot * (int)gridDim.x;
+    const int first_tile = tile0 + (int)slot * tstep;
     // before the set's first use: stage its bias (the MMA warp runs the main loop meanwhile)
     if constexpr (kCanFold) {
       if (first_tile < total_tiles) {
@@ -1149,6 +1212,67 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const uint32_t t_row =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
       const int g_stop = min(g_end, (p.n_total - n_tile * p.bn + 15) >> 4);  // groups that hold real columns
+      if constexpr (SPLITK) {
+        // ---- split-K: reduce-scatter of the cluster's partial accumulators through distributed
+        // shared memory.  Column group g (16 columns) belongs to CTA g % S: every CTA sends the
+        // groups it does not own to their owners (into the owner's operand ring, which is idle once
+        // the owner's MMAs have completed), then adds what it received to its own partial sums,
+        // which never leave tensor memory, and runs the epilogue on the groups it owns.
+        const uint32_t S = (uint32_t)p.ksplit;
+        const uint32_t n_own = ((uint32_t)groups + S - 1u) / S;     // groups a CTA owns at most
+        // this CTA's MMAs are complete: its ring may be overwritten
+        if (warp == 0 && (uint32_t)lane < S && (uint32_t)lane != crank)
+          mbar_arrive_remote(map_to_cta(smem_u32(&ps->xfree[crank]), (uint32_t)lane));
+        uint32_t peer_ready = 0u;  // bit r: CTA r's ring is known to be free
+        bool xok = true;
+        for (int g = g_begin; g < g_stop && xok; ++g) {
+          const uint32_t owner = (uint32_t)g % S;
+          if (owner == crank) continue;
+          uint32_t v[16];
+          tmem_ld16(t_row + (uint32_t)g * 16u, v);
+          tmem_ld_wait();
+          if (!(peer_ready >> owner & 1u)) {
+            xok = mbar_wait_warp(smem_u32(&ps->xfree[owner]), 0u, wc, kErrWaitPeer, true);
+            peer_ready |= 1u << owner;
+            if (!xok) break;
+          }
+          // slot of this CTA among the owner's S - 1 senders; 64 bytes per (group, row)
+          const uint32_t sender = crank - (crank > owner ? 1u : 0u);
+          const uint32_t local = smem_base + ((sender * n_own + (uint32_t)g / S) * (uint32_t)kTileM + r) * 64u;
+          const uint32_t remote = map_to_cta(local, owner);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) st_cluster_v4(remote + 16u * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+        // every warp tells every peer that its share has been written (also when it had nothing for it)
+        fence_cluster();
+        __syncwarp();
+        if ((uint32_t)lane < S && (uint32_t)lane != crank) mbar_arrive_remote(map_to_cta(smem_u32(&ps->xfull), (uint32_t)lane));
+        if (xok) xok = mbar_wait_warp(smem_u32(&ps->xfull), 0u, wc, kErrWaitPeer, true);
+        if (xok) {
+          for (int g = g_begin; g < g_stop; ++g) {
+            if ((uint32_t)g % S != crank) continue;
+            uint32_t v[16];
+            tmem_ld16(t_row + (uint32_t)g * 16u, v);
+            tmem_ld_wait();
+            for (uint32_t sdr = 0; sdr + 1u < S; ++sdr) {
+              const uint4 *src = reinterpret_cast<const uint4 *>(smem + ((size_t)(sdr * n_own + (uint32_t)g / S) * kTileM + r) * 64u);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 t = src[q];
+                if constexpr (F16) {
+                  v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + __uint_as_float(t.x));
+                  v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + __uint_as_float(t.y));
+                  v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + __uint_as_float(t.z));
+                  v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + __uint_as_float(t.w));
+                } else {
+                  v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+                }
+              }
+            }
+            if (mvalid) store_group16<EPI>(p, tile_bias + g * 16, folded, wide, v, obase + g * gstride);
+          }
+        }
+      } else {
       // software pipeline: the read of group g + 1 is in flight while group g is processed
       uint32_t va[16], vb[16];
       if (g_begin < g_stop) {
@@ -1163,6 +1287,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (g + 2 < g_stop) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
         if (has_b && mvalid) store_group16<EPI>(p, tile_bias + (g + 1) * 16, folded, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait();
+      }
       }
       // the accumulator set is free again: the MMA warp may start the set's next main loop
       tc_fence_before();
@@ -1198,6 +1323,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tc_fence_after();
     tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
+  // split-K: no CTA leaves while a peer may still write into its shared memory or arrive on its barriers
+  if constexpr (SPLITK) cluster_sync_all();
   trace_mark_ns(p, 11);
 }
 

@@ -338,29 +338,54 @@ __device__ __forceinline__ void untranspose_words(const uint32_t (&in)[CB], uint
   }
 }
 
+// With 16-channel blocks a thread's result is 64 bytes (four 16-byte pieces).  Written straight
+// from the thread, every store instruction of a warp would touch 32 separate half sectors; the
+// pieces go through shared memory instead, so that consecutive lanes store consecutive 16 bytes
+// (512 contiguous bytes per warp instruction).  kPackPad staggers the four piece planes by 32 bytes,
+// which makes both the writes and the reads of the staging buffer conflict-free.
+constexpr int kPackThreads = 256, kPackPad = 2;
 template <int EB, int CB>
-__global__ void nchw_to_nchwc_vec_kernel(const uint32_t *__restrict__ src, uint32_t *__restrict__ dst, int n, int c,
-                                         long long hw_words) {
+__global__ void __launch_bounds__(kPackThreads)
+    nchw_to_nchwc_vec_kernel(const uint32_t *__restrict__ src, uint32_t *__restrict__ dst, int n, int c, long long hw_words) {
+  constexpr int NP = CB / 4;  // 16-byte pieces per thread
+  __shared__ uint4 stage[NP > 1 ? NP * (kPackThreads + kPackPad) : 1];
   const int cc = (c + CB - 1) / CB;
   const long long total = (long long)n * cc * hw_words;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const long long wpos = idx % hw_words;
-    const long long t = idx / hw_words;
-    const int chunk = (int)(t % cc);
-    const long long img = t / cc;
-    uint32_t in[CB], out[CB];
+  const long long span = (long long)gridDim.x * blockDim.x;
+  for (long long base = blockIdx.x * (long long)blockDim.x; base < total; base += span) {
+    const long long idx = base + threadIdx.x;
+    uint32_t out[CB];
+    if (idx < total) {
+      const long long wpos = idx % hw_words;
+      const long long t = idx / hw_words;
+      const int chunk = (int)(t % cc);
+      const long long img = t / cc;
+      uint32_t in[CB];
 #pragma unroll
-    for (int k = 0; k < CB; ++k) {
-      const int ch = chunk * CB + k;
-      in[k] = ch < c ? __ldg(src + (img * c + ch) * hw_words + wpos) : 0u;
+      for (int k = 0; k < CB; ++k) {
+        const int ch = chunk * CB + k;
+        in[k] = ch < c ? __ldg(src + (img * c + ch) * hw_words + wpos) : 0u;
+      }
+      transpose_words<EB, CB>(in, out);
     }
-    transpose_words<EB, CB>(in, out);
-    uint32_t *d = dst + idx * CB;
-    if constexpr (CB >= 4) {
+    if constexpr (NP == 1) {
+      if (idx < total) reinterpret_cast<uint4 *>(dst)[idx] = make_uint4(out[0], out[1], out[2], out[3]);
+    } else {
+      if (idx < total) {
 #pragma unroll
-      for (int q = 0; q < CB / 4; ++q)
-        reinterpret_cast<uint4 *>(d)[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+        for (int q = 0; q < NP; ++q)
+          stage[q * (kPackThreads + kPackPad) + threadIdx.x] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+      }
+      __syncthreads();
+      // piece k of the block's output (k = thread * NP + piece) is stored by thread k % 256 in round k / 256
+      uint4 *d4 = reinterpret_cast<uint4 *>(dst) + base * NP;
+      const long long pieces = (total - base < blockDim.x ? total - base : blockDim.x) * NP;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int k = i * kPackThreads + threadIdx.x;
+        if (k < pieces) d4[k] = stage[(k % NP) * (kPackThreads + kPackPad) + k / NP];
+      }
+      __syncthreads();
     }
   }
 }
@@ -546,7 +571,7 @@ static bool use_fold() {
 // kernel variants: one slot per instantiated igemm_kernel<AMODE, EPI, F16, MT>
 // ---------------------------------------------------------------------------
 constexpr int kNumAModes = 7, kNumEpis = 5;
-constexpr int kMaxVariants = kNumAModes * kNumEpis * 2 * 2;
+constexpr int kMaxVariants = kNumAModes * kNumEpis * 2 * 2 * 2;
 struct VariantSlot {
   char name[72];
   bool present;
@@ -557,21 +582,23 @@ static VariantSlot *variant_table() {
   static VariantSlot table[kMaxVariants];  // static storage: zero-initialised
   return table;
 }
-static bool register_variant(int index, int amode, int epi, bool f16, int mt) {
+static bool register_variant(int index, int amode, int epi, bool f16, int mt, bool splitk) {
   static const char *const amodes[kNumAModes] = {"A_CONV_I8", "A_CONV_F16", "A_STEM_I8", "A_DENSE", "A_CONV_TMA", "A_CONV_BOX", "A_DENSE_TMA"};
   static const char *const epis[kNumEpis] = {"EPI_RAW_NCHWC", "EPI_REQ_NCHWC", "EPI_RAW_ROWS", "EPI_MUL_NCHWC", "EPI_RES_NCHWC"};
   VariantSlot &v = variant_table()[index];
-  snprintf(v.name, sizeof(v.name), "igemm_kernel<%s, %s, %s, MT=%d>", amodes[amode], epis[epi], f16 ? "f16" : "i8", mt);
+  snprintf(v.name, sizeof(v.name), "igemm_kernel<%s, %s, %s, MT=%d%s>", amodes[amode], epis[epi], f16 ? "f16" : "i8", mt,
+           splitk ? ", split-K" : "");
   v.present = true;
   return true;
 }
-template <int AMODE, int EPI, bool F16, int MT>
+template <int AMODE, int EPI, bool F16, int MT, bool SPLITK>
 struct Variant {
-  static constexpr int index = ((AMODE * kNumEpis + EPI) * 2 + (F16 ? 1 : 0)) * 2 + (MT - 1);
+  static constexpr int index = (((AMODE * kNumEpis + EPI) * 2 + (F16 ? 1 : 0)) * 2 + (MT - 1)) * 2 + (SPLITK ? 1 : 0);
   static const bool registered;  // set while the library is loaded, so that never-launched variants are listed too
 };
-template <int AMODE, int EPI, bool F16, int MT>
-const bool Variant<AMODE, EPI, F16, MT>::registered = register_variant(Variant<AMODE, EPI, F16, MT>::index, AMODE, EPI, F16, MT);
+template <int AMODE, int EPI, bool F16, int MT, bool SPLITK>
+const bool Variant<AMODE, EPI, F16, MT, SPLITK>::registered =
+    register_variant(Variant<AMODE, EPI, F16, MT, SPLITK>::index, AMODE, EPI, F16, MT, SPLITK);
 
 // ---------------------------------------------------------------------------
 // launch plans
@@ -586,6 +613,7 @@ struct PlanImpl {
   uint32_t magic;
   int32_t variant, device;
   uint32_t grid, smem_bytes;
+  uint32_t cluster;                  // > 1: thread-block cluster size (split-K)
   int32_t fold_n, fold_h2, fold_w2;  // fold_n > 0: the stem's 2 x 2 fold into scratch runs first
   const void *fold_src;
   void *fold_dst;
@@ -598,25 +626,61 @@ static_assert(sizeof(PlanImpl) <= sizeof(unit_conv_plan), "unit_conv_plan too sm
 static std::atomic<unsigned long long> g_wait_limit_ns{1000000000ull};
 static std::atomic<int> g_inject{0};
 
-template <int AMODE, int EPI, bool F16, int MT>
-static int prepare_mt(PlanImpl &pl, const TileCfg &c, int sms) {
-  if (!Variant<AMODE, EPI, F16, MT>::registered) return UNIT_ERR_LAUNCH;
+template <int AMODE, int EPI, bool F16, int MT, bool SPLITK>
+static int prepare_mt(PlanImpl &pl, const TileCfg &c, int sms, int ksplit) {
+  if (!Variant<AMODE, EPI, F16, MT, SPLITK>::registered) return UNIT_ERR_LAUNCH;
   IgemmParams &p = pl.p;
-  pl.variant = Variant<AMODE, EPI, F16, MT>::index;
-  pl.kernel = reinterpret_cast<const void *>(igemm_kernel<AMODE, EPI, F16, MT>);
+  pl.variant = Variant<AMODE, EPI, F16, MT, SPLITK>::index;
+  pl.kernel = reinterpret_cast<const void *>(igemm_kernel<AMODE, EPI, F16, MT, SPLITK>);
   size_t smem_bytes = 0;
   p.stages = stages_for(c, MT, &smem_bytes);
   pl.smem_bytes = (uint32_t)smem_bytes;
   p.m_tiles = (int)((p.m_total + kTileM * MT - 1) / (kTileM * MT));
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
-  pl.grid = (unsigned)(tiles < sms ? tiles : sms);
+  if (SPLITK) {
+    p.ksplit = ksplit;
+    p.ks_per = (c.k_stages + ksplit - 1) / ksplit;
+    pl.grid = (unsigned)(tiles * ksplit);
+    pl.cluster = (uint32_t)ksplit;
+  } else {
+    p.ksplit = 1;
+    p.ks_per = c.k_stages;
+    pl.grid = (unsigned)(tiles < sms ? tiles : sms);
+    pl.cluster = 1;
+  }
   // tensor memory: a power of two of columns that holds the accumulator sets (the kernel derives the
-  // same number of sets from MT and bn)
-  const int sets = (512 / (MT * c.bn)) >= 2 ? 2 : 1;
+  // same number of sets from MT and bn; split-K tiles use one set)
+  const int sets = (!SPLITK && (512 / (MT * c.bn)) >= 2) ? 2 : 1;
   int cols = 32;
   while (cols < sets * MT * c.bn) cols *= 2;
   p.tmem_cols = cols;
   return UNIT_OK;
+}
+
+// Split-K factor for grids that would leave most SMs idle: S CTAs (one thread-block cluster)
+// share a tile, each accumulating a slice of the reduction, and exchange partial sums through
+// distributed shared memory (integer sums do not depend on the order, so the int8 results stay
+// bit-exact; the reference splits its reductions too: python/tensorizer/ops/gpu.py:83-87,134,
+// poc/tensorcore/gemm-prefetch.cu:29-64).  Returns 1 when the problem should not be split.
+static int choose_ksplit(const TileCfg &c, long long m_total, int sms) {
+  static const int forced = tuning_int("UNIT_B200_KSPLIT", -1);
+  if (forced == 0 || forced == 1) return 1;
+  const long long tiles = (m_total + kTileM - 1) / kTileM * c.n_tiles;
+  if (tiles * 2 > sms || c.k_stages < 4) return 1;
+  int s = (int)(sms / tiles);
+  if (s > 8) s = 8;                          // the portable cluster size
+  if (s > c.k_stages / 2) s = c.k_stages / 2;  // at least two pipeline stages per CTA
+  if (forced >= 2 && forced < s) s = forced;
+  if (s < 2) return 1;
+  const int per = (c.k_stages + s - 1) / s;
+  s = (c.k_stages + per - 1) / per;          // no CTA without stages
+  if (s < 2) return 1;
+  // the partial sums a CTA receives replace its operand ring: (S - 1) senders x owned groups x 128 rows x 64 bytes
+  size_t smem_bytes = 0;
+  const int stages = stages_for(c, 1, &smem_bytes);
+  const size_t ring = (size_t)stages * c.kc * 16 * (kTileM + c.bn);
+  const size_t recv = (size_t)(s - 1) * (((c.bn >> 4) + s - 1) / s) * kTileM * 64;
+  return recv <= ring ? s : 1;
 }
 
 static FastDiv make_fast_div(uint32_t d);
@@ -658,9 +722,13 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
   const int sms = sm_count();
   pl.magic = kPlanMagic;
   if constexpr (MAX_MT >= 2) {
-    if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2>(pl, c, sms);
+    if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
-  return prepare_mt<AMODE, EPI, F16, 1>(pl, c, sms);
+  if constexpr (a_mode_uses_tma(AMODE)) {
+    const int ks = choose_ksplit(c, p.m_total, sms);
+    if (ks > 1) return prepare_mt<AMODE, EPI, F16, 1, true>(pl, c, sms, ks);
+  }
+  return prepare_mt<AMODE, EPI, F16, 1, false>(pl, c, sms, 1);
 }
 
 // The int8 convolution's epilogue is chosen at run time: one instantiation per mode.
@@ -710,11 +778,18 @@ static int run_plan(const PlanImpl &pl, cudaStream_t st) {
   cfg.blockDim = dim3(kNumThreads);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = use_pdl() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (pl.cluster > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = pl.cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   void *args[2] = {&p, &map};
   const cudaError_t le = cudaLaunchKernelExC(&cfg, pl.kernel, args);
   g_launches.fetch_add(1);
@@ -1067,7 +1142,7 @@ static int static_scratch_address(void **out) {
 template <int EB, int CB>
 static void launch_pack_vec(const void *src, void *dst, int n, int c, long long hw_words, cudaStream_t st) {
   const long long total = (long long)n * ((c + CB - 1) / CB) * hw_words;
-  nchw_to_nchwc_vec_kernel<EB, CB><<<grid_for(total), 256, 0, st>>>(static_cast<const uint32_t *>(src), static_cast<uint32_t *>(dst), n, c, hw_words);
+  nchw_to_nchwc_vec_kernel<EB, CB><<<grid_for(total), kPackThreads, 0, st>>>(static_cast<const uint32_t *>(src), static_cast<uint32_t *>(dst), n, c, hw_words);
 }
 template <int EB, int CB>
 static void launch_unpack_vec(const void *src, void *dst, int n, int c, long long hw_words, cudaStream_t st) {
