@@ -59,9 +59,9 @@ INT8_CASES = {
     'gather_mt2': (32, 16, 225, 225, 16, 1, 9, 0, 16),
     'stem_gather_mt1': (2, 4, 33, 35, 32, 7, 2, 3, 4),
     'stem_gather_mt2': (8, 4, 227, 227, 16, 3, 2, 1, 4),
-    # few tiles and a long reduction: split-K over a thread-block cluster (6 CTAs per tile here)
-    'box_splitk': (1, 256, 24, 24, 64, 3, 1, 1, 16),
-    'im2col_splitk': (1, 256, 24, 24, 64, 3, 2, 1, 16),
+    # few tiles and a long reduction: split-K over a thread-block cluster
+    'box_splitk': (1, 256, 24, 24, 256, 3, 1, 1, 16),
+    'im2col_splitk': (1, 256, 24, 24, 256, 3, 2, 1, 16),
 }
 INT8_VARIANTS = {
     'box_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'box_mt2': 'A_CONV_BOX, {}, i8, MT=2',
@@ -102,7 +102,7 @@ def test_int8_conv_variants_all_epilogues(U, oracle, case):
 
 
 FP16_CASES = {
-    'box_mt1': ((9, 32, 23, 21, 48, 3, 1, 1), 'A_CONV_BOX, EPI_RAW_NCHWC, f16, MT=1'),
+    'box_mt1': ((9, 16, 33, 29, 48, 3, 1, 1), 'A_CONV_BOX, EPI_RAW_NCHWC, f16, MT=1'),
     'box_mt2': ((8, 16, 56, 56, 16, 3, 1, 1), 'A_CONV_BOX, EPI_RAW_NCHWC, f16, MT=2'),
     'im2col_mt1': ((4, 32, 40, 40, 32, 3, 2, 1), 'A_CONV_TMA, EPI_RAW_NCHWC, f16, MT=1'),
     'im2col_mt2': ((8, 16, 112, 112, 16, 3, 2, 1), 'A_CONV_TMA, EPI_RAW_NCHWC, f16, MT=2'),
@@ -180,9 +180,9 @@ def test_tensor_map_size_boundary(U, oracle):
     (12, 256, 14, 256, 3, 1),     # 19 tiles -> clusters of 7
     (32, 256, 14, 256, 3, 1),     # 49 tiles -> clusters of 3 (the ResNet-50 stage-3 3x3 at batch 32)
     (44, 64, 14, 320, 1, 1),      # 68 tiles x 2 column blocks: just under the limit of half the SMs -> no split
-    (32, 1024, 14, 256, 1, 1),    # clusters of 3, short slices (8 stages)
+    (32, 2048, 14, 256, 1, 1),    # clusters of 3, 1x1
     (32, 512, 7, 512, 3, 1),      # 26 tiles -> clusters of 5, two column blocks
-    (1, 512, 28, 128, 1, 1),      # 7 tiles -> clusters of 8
+    (1, 4096, 28, 128, 1, 1),     # 7 tiles -> clusters of 8
     (20, 512, 14, 512, 3, 2),     # im2col copies, 8 x 2 tiles
     (33, 2048, 7, 208, 1, 1),     # column block of 208: 13 groups dealt to the cluster's CTAs unevenly
 ])

@@ -433,6 +433,14 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// 16 bytes into another CTA's shared memory; the copy's completion is counted (as 16 transaction
+// bytes) on an mbarrier of that same CTA, so neither a fence nor a separate signal is needed
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                            uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
+               "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_mbar)
+               : "memory");
+}
 // one arrival on an mbarrier of another CTA of the cluster; releases this thread's earlier writes at cluster scope
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -716,7 +724,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
     if constexpr (SPLITK) {
       for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&ps->xfree[i]), 1);
-      mbar_init(smem_u32(&ps->xfull), (uint32_t)(p.ksplit - 1) * kDrainWarps);
+      mbar_init(smem_u32(&ps->xfull), 1);  // this CTA's own arrival, which also announces the bytes to come
     }
     ps->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1033,7 +1041,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     // (Measured: keeping them parked at a warp-level synchronisation point instead slows the
     // issuing lane's polling and costs 10-20 % on K-loop-bound layers.)
     constexpr bool kCanFold = !F16 && EPI != EPI_RAW_ROWS;
-    const uint32_t fold_base = smem_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
+    // Operand descriptors carry the shared-memory address as a 14-bit field (bits 4-17 of the offset in
+    // this CTA's window).  In a thread-block cluster the 32-bit shared address of a CTA other than the
+    // first has higher bits set (the CTA's place in the cluster's window), which must not leak into
+    // the neighbouring descriptor fields: descriptor arithmetic uses the offset alone.
+    const uint32_t desc_base = smem_base & 0x3FFFFu;
+    const uint32_t fold_base = desc_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
     const uint32_t my_t = warp == kMmaWarp ? 0u : 1u;  // the sub-tile this thread issues for
     if (lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn, p.a_signed);
@@ -1069,7 +1082,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           tc_fence_after();
           if (ks == 0 && my_t == 0u) trace_mark(p, lt, 4);
           // descriptors differ only in the start-address field (address >> 4, 14 bits)
-          const uint32_t stage_enc = (smem_base + s * stage_bytes) >> 4;
+          const uint32_t stage_enc = (desc_base + s * stage_bytes) >> 4;
           const uint32_t a_enc = stage_enc + my_t * a_sub_enc;  // this thread's sub-tile of the stage
           const uint32_t b_enc = stage_enc + (a_stage_bytes >> 4);
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
@@ -1220,9 +1233,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         // which never leave tensor memory, and runs the epilogue on the groups it owns.
         const uint32_t S = (uint32_t)p.ksplit;
         const uint32_t n_own = ((uint32_t)groups + S - 1u) / S;     // groups a CTA owns at most
-        // this CTA's MMAs are complete: its ring may be overwritten
+        // this CTA's MMAs are complete: its ring may be overwritten.  It announces how many bytes it
+        // is going to receive: 8 KB from each peer for each group it owns.
         if (warp == 0 && (uint32_t)lane < S && (uint32_t)lane != crank)
           mbar_arrive_remote(map_to_cta(smem_u32(&ps->xfree[crank]), (uint32_t)lane));
+        if (warp == 0 && lane == 0) {
+          const uint32_t real_groups = (uint32_t)min(groups, (p.n_total - n_tile * p.bn + 15) >> 4);
+          const uint32_t owned = real_groups > crank ? (real_groups - crank + S - 1u) / S : 0u;
+          mbar_arrive_expect_tx(smem_u32(&ps->xfull), (S - 1u) * owned * (uint32_t)(kTileM * 64));
+        }
         uint32_t peer_ready = 0u;  // bit r: CTA r's ring is known to be free
         bool xok = true;
         for (int g = g_begin; g < g_stop && xok; ++g) {
@@ -1236,18 +1255,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             peer_ready |= 1u << owner;
             if (!xok) break;
           }
-          // slot of this CTA among the owner's S - 1 senders; 64 bytes per (group, row)
+          // slot of this CTA among the owner's S - 1 senders.  A (sender, group) block is stored as
+          // four planes of 128 rows x 16 bytes, so that one warp instruction writes 512 contiguous
+          // bytes of the owner's shared memory (rows 64 bytes apart were ten times slower)
           const uint32_t sender = crank - (crank > owner ? 1u : 0u);
-          const uint32_t local = smem_base + ((sender * n_own + (uint32_t)g / S) * (uint32_t)kTileM + r) * 64u;
+          const uint32_t local = smem_base + (sender * n_own + (uint32_t)g / S) * (uint32_t)(kTileM * 64) + r * 16u;
           const uint32_t remote = map_to_cta(local, owner);
+          const uint32_t remote_bar = map_to_cta(smem_u32(&ps->xfull), owner);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) st_cluster_v4(remote + 16u * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          for (int q = 0; q < 4; ++q)
+            st_async_v4(remote + (uint32_t)(q * kTileM * 16), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3], remote_bar);
         }
-        // every warp tells every peer that its share has been written (also when it had nothing for it)
-        fence_cluster();
-        __syncwarp();
-        if ((uint32_t)lane < S && (uint32_t)lane != crank) mbar_arrive_remote(map_to_cta(smem_u32(&ps->xfull), (uint32_t)lane));
-        if (xok) xok = mbar_wait_warp(smem_u32(&ps->xfull), 0u, wc, kErrWaitPeer, true);
+        if (xok && S > 1u) xok = mbar_wait_warp(smem_u32(&ps->xfull), 0u, wc, kErrWaitPeer, true);
         if (xok) {
           for (int g = g_begin; g < g_stop; ++g) {
             if ((uint32_t)g % S != crank) continue;
@@ -1255,10 +1274,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             tmem_ld16(t_row + (uint32_t)g * 16u, v);
             tmem_ld_wait();
             for (uint32_t sdr = 0; sdr + 1u < S; ++sdr) {
-              const uint4 *src = reinterpret_cast<const uint4 *>(smem + ((size_t)(sdr * n_own + (uint32_t)g / S) * kTileM + r) * 64u);
+              const uint4 *src = reinterpret_cast<const uint4 *>(smem + (size_t)(sdr * n_own + (uint32_t)g / S) * (kTileM * 64) + r * 16u);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const uint4 t = src[q];
+                const uint4 t = src[q * kTileM];
                 if constexpr (F16) {
                   v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + __uint_as_float(t.x));
                   v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + __uint_as_float(t.y));

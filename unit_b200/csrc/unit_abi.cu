@@ -657,6 +657,45 @@ static int prepare_mt(PlanImpl &pl, const TileCfg &c, int sms, int ksplit) {
   return UNIT_OK;
 }
 
+// How many clusters of `ks` CTAs of the split-K kernel the current device holds at once (cached per
+// kernel variant, size and shared-memory request).
+template <int AMODE, int EPI, bool F16>
+static int max_active_clusters(const TileCfg &c, int ks) {
+  static std::mutex mu;
+  static int cached[64][9][kMaxStages + 1] = {};
+  size_t smem_bytes = 0;
+  const int stages = stages_for(c, 1, &smem_bytes);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || ks < 2 || ks > 8) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  int &slot = cached[dev][ks][stages];
+  if (slot == 0) {
+    auto kern = igemm_kernel<AMODE, EPI, F16, 1, true>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)ks * 64);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = 227 * 1024 - 1024;  // the largest request of any tile shape: a lower bound for smaller ones
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    slot = n > 0 ? n : -1;
+  }
+  return slot > 0 ? slot : 0;
+}
+
 // Split-K factor for grids that would leave most SMs idle: S CTAs (one thread-block cluster)
 // share a tile, each accumulating a slice of the reduction, and exchange partial sums through
 // distributed shared memory (integer sums do not depend on the order, so the int8 results stay
@@ -667,6 +706,10 @@ static int choose_ksplit(const TileCfg &c, long long m_total, int sms) {
   if (forced == 0 || forced == 1) return 1;
   const long long tiles = (m_total + kTileM - 1) / kTileM * c.n_tiles;
   if (tiles * 2 > sms || c.k_stages < 4) return 1;
+  // The exchange costs about 5 us (two hops between SMs and the transfer).  A CTA streams its operands
+  // at roughly 100 GB/s, so splitting pays once a tile's operands exceed some 600 KB (measured at
+  // batch 32: reductions of 2048 bytes and more gain 1-6 us per layer, shorter ones lose).
+  if ((size_t)c.k_stages * c.kc * 16 * (kTileM + c.bn) < (640u << 10) && forced < 2) return 1;
   int s = (int)(sms / tiles);
   if (s > 8) s = 8;                          // the portable cluster size
   if (s > c.k_stages / 2) s = c.k_stages / 2;  // at least two pipeline stages per CTA
@@ -725,8 +768,19 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
     if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
   if constexpr (a_mode_uses_tma(AMODE)) {
-    const int ks = choose_ksplit(c, p.m_total, sms);
+    int ks = choose_ksplit(c, p.m_total, sms);
+    // all clusters must be resident at once: a cluster needs its CTAs on SMs of one GPC, so fewer
+    // clusters fit than SMs / size suggests (measured: 49 clusters of 3 ran in two rounds)
+    const long long tiles1 = (p.m_total + kTileM - 1) / kTileM * c.n_tiles;
+    while (ks > 1) {
+      const int per = (c.k_stages + ks - 1) / ks;
+      if ((c.k_stages + per - 1) / per == ks && tiles1 <= max_active_clusters<AMODE, EPI, F16>(c, ks)) break;
+      --ks;
+    }
     if (ks > 1) return prepare_mt<AMODE, EPI, F16, 1, true>(pl, c, sms, ks);
+    // experiment builds: the split-K kernel with clusters of one CTA
+    static const int force1 = tuning_int("UNIT_B200_KSPLIT_ONE", 0);
+    if (force1 && (long long)((p.m_total + kTileM - 1) / kTileM) * c.n_tiles <= sms) return prepare_mt<AMODE, EPI, F16, 1, true>(pl, c, sms, 1);
   }
   return prepare_mt<AMODE, EPI, F16, 1, false>(pl, c, sms, 1);
 }
