@@ -416,6 +416,29 @@ def side_configs(torch, U, R, dev, peaks, local_rank):
                                         'launch_mode': 'cuda graph replay'}
         del inst, g
 
+    # int8 conv3d: the reference's workload list (apps/cpu/kernel/conv3d.py:13-25, depth 16, valid
+    # convolution on pre-padded sizes; the 4-channel stem of that list needs NCDHW4c and is left out),
+    # one launch each, L2 flushed; the reference's own CPU log beside it (apps/cpu/kernel/res, GOPS
+    # counted as in conv3d.py:92: one operation per 4-byte group multiply-accumulate)
+    workloads = [(256, 16, 16, 256, 3, 1), (512, 9, 9, 512, 3, 1), (128, 30, 30, 128, 3, 1), (64, 56, 56, 128, 1, 2),
+                 (64, 58, 58, 64, 3, 1), (128, 28, 28, 256, 1, 2), (256, 16, 16, 512, 3, 2), (64, 58, 58, 128, 3, 2),
+                 (128, 30, 30, 256, 3, 2), (256, 14, 14, 512, 1, 2)]
+    rows, t_sum, ops_sum = [], 0.0, 0.0
+    for ic, h, w_, oc, k, st in workloads:
+        x3 = torch.randint(0, 256, (1, ic // 16, 16, h, w_, 16), dtype=torch.uint8, device=dev)
+        w3 = torch.randint(-128, 128, (oc // 16, ic // 16, k, k, k, 4, 16, 4), dtype=torch.int8, device=dev)
+        pw3 = U.pack_conv3d_weights_int8(w3, st)
+        o3 = U.conv3d_NCDHWc_int8(x3, pw3, stride=st)
+        ms3 = flushed(lambda: U.conv3d_NCDHWc_int8(x3, pw3, stride=st, out=o3), reps=10)
+        ops3 = 2.0 * o3.numel() * ic * k ** 3
+        rows.append([f'{ic}x16x{h}x{w_}->{oc} k{k} s{st}', round(ms3 * 1e3, 2), round(ops3 / ms3 / 1e9, 1)])
+        t_sum += ms3
+        ops_sum += ops3
+        del x3, w3, pw3, o3
+    out['conv3d_reference_workloads'] = {'value': ops_sum / t_sum / 1e9, 'unit': 'TOPS over the ten workloads', 'ms': t_sum,
+                                         'rows': rows, 'row_format': '[workload, us, TOPS]',
+                                         'reference_log': 'apps/cpu/kernel/res: 797-1170 us for the 3x3x3 stride-1 workloads on its CPU'}
+
     # layout kernels (NCHW <-> NCHW16c): GB/s of bytes read + written
     xl = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device=dev)
     yl = U.pack_data_nchwc(xl)

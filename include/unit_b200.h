@@ -89,6 +89,18 @@ typedef struct unit_epilogue {
   int32_t x_signed;
 } unit_epilogue;
 
+/* Geometry of one three-dimensional convolution (apps/cpu/kernel/conv3d.py:39-64).
+ * Data   [n][c_in/16][d][h][w][16] u8 (or s8), weights [c_out/16][c_in/16][kd][kh][kw][4][16][4] s8,
+ * output [n][c_out/16][od][oh][ow][16].  The reference convolves pre-padded inputs without padding
+ * (conv3d.py:60); pad_* here is implicit zero padding with the same result. */
+typedef struct unit_conv3d_desc {
+  int32_t n, c_in, d, h, w;
+  int32_t c_out;
+  int32_t kd, kh, kw;
+  int32_t stride_d, stride_h, stride_w;
+  int32_t pad_d, pad_h, pad_w;
+} unit_conv3d_desc;
+
 /* A prepared launch (see unit_conv2d_plan_int8): plain bytes owned by the caller, valid in this
  * process for the device that was current when it was made, until the buffers it names are freed.
  * May be copied; holds no resource. */
@@ -219,6 +231,19 @@ int unit_conv2d_plan_int8(const unit_conv_desc *desc, const void *d_x, const voi
                           const unit_epilogue *epilogue, void *d_out, void *d_workspace,
                           size_t workspace_bytes, unit_conv_plan *plan);
 int unit_conv2d_run(const unit_conv_plan *plan, void *stream);
+
+/* Three-dimensional int8 convolution on NCDHW16c (replaces the compute of
+ * apps/cpu/kernel/conv3d.py:58-64, scheduled by INTRINSICS['vnni'] like the two-dimensional one).
+ * Same contraction kernel: the depth axis takes the place of the batch axis (a tile runs over
+ * (od, oh, ow) of one image, one launch per image), the kernel depth adds a third tap index.
+ * Epilogue as for unit_conv2d_int8_nchwc; the reference's form is the plain s32 output
+ * {NULL, 1, 0, 0, NULL, 0}.  The packed weights depend on c_in, c_out, the kernel size and the
+ * strides. */
+size_t unit_packed_weights_bytes_conv3d_i8(const unit_conv3d_desc *desc);
+int unit_pack_weights_conv3d_i8(const unit_conv3d_desc *desc, const int8_t *d_w, void *d_packed,
+                                void *stream);
+int unit_conv3d_int8_ncdhwc(const unit_conv3d_desc *desc, const void *d_x, const void *d_packed_w,
+                            const unit_epilogue *epilogue, void *d_out, void *stream);
 
 /* Requantising convolution for callers that may not allocate.  No counterpart in the
  * reference.  It is unit_conv2d_u8s8_requant_nchwc with the scratch taken from a fixed array

@@ -61,6 +61,8 @@ def lib() -> ctypes.CDLL:
         fn.restype = ci
     L.oracle_conv2d_i8_ex.argtypes = [vp, ci, vp, vp, ci, vp, vp, vp, ci] + [ci] * 12
     L.oracle_conv2d_i8_ex.restype = ci
+    L.oracle_conv3d_u8s8.argtypes = [vp, vp, vp, vp] + [ci] * 15
+    L.oracle_conv3d_u8s8.restype = ci
     for fn in (L.oracle_dense_u8s8s32, L.vnni_dense_u8s8s32):
         fn.argtypes = [vp, vp, vp, ci, ci, ci, ci]
         fn.restype = ci
@@ -178,6 +180,28 @@ def conv2d_s8s8_relay_flow(x_s8, w, stride=(1, 1), pad=(0, 0), bias=None, mul=1)
         t = t + np.asarray(bias, np.int64).reshape(1, -1, 1, 1, 16)
     t = (t * int(mul)) & 0xFFFFFFFF
     return t.astype(np.uint32).view(np.int32)   # wrapping s32, as the reference's int32 arithmetic
+
+
+def conv3d_u8s8(x, w, stride=(1, 1, 1), pad=(0, 0, 0), bias=None):
+    """x [N][Cc][D][H][W][16] u8, w [Oc][Cc][KD][KH][KW][4][16][4] s8 -> s32 [N][Oc][OD][OH][OW][16]
+    (apps/cpu/kernel/conv3d.py:58-64), bias added if given."""
+    x = _c(x, np.uint8)
+    w = _c(w, np.int8)
+    n, cc, d, h, wd, cb = x.shape
+    oc, cc2, kd, kh, kw, c4, l16, r4 = w.shape
+    assert cb == 16 and cc2 == cc and c4 == 4 and l16 == 16 and r4 == 4
+    od = (d + 2 * pad[0] - kd) // stride[0] + 1
+    oh = (h + 2 * pad[1] - kh) // stride[1] + 1
+    ow = (wd + 2 * pad[2] - kw) // stride[2] + 1
+    if bias is not None:
+        bias = _c(bias, np.int32)
+        assert bias.size == oc * 16
+    out = np.empty((n, oc, od, oh, ow, 16), np.int32)
+    rc = lib().oracle_conv3d_u8s8(_p(x), _p(w), _p(bias), _p(out), n, cc, d, h, wd, oc, kd, kh, kw,
+                                  stride[0], stride[1], stride[2], pad[0], pad[1], pad[2])
+    if rc == 1:
+        raise OverflowError('oracle: an accumulator left the s32 range')
+    return out
 
 
 def dense_u8s8s32(a, bp, vnni=False):

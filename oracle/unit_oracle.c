@@ -23,6 +23,8 @@
  *   - fp16 conv, data [N][C/16][H][W][16], weights [O/16][C/16][KH][KW][16i][16o],
  *     fp32 accumulate: python/tensorizer/ops/gpu.py:8-53.
  *   - fp16 GEMM A [M][K] * B [K][N] -> fp32: apps/gpu/gemm.py:6-19.
+ *   - int8 conv3d, data [N][C/16][D][H][W][16], weights [O/16][C/16][KD][KH][KW][4][16][4]:
+ *     apps/cpu/kernel/conv3d.py:39-64.
  *
  * Parity pin: the int8 definitions are exact integer sums and are pinned by
  * the reference's known-answer vector (poc/vnni/poc.cc, a[i]=i+1, b[i]=64-i)
@@ -216,6 +218,55 @@ int oracle_conv2d_i8_ex(const void *xv, int x_signed, const int8_t *w, const int
             }
           }
         }
+  return overflow;
+}
+
+/*
+ * Three-dimensional int8 convolution, the index expression of apps/cpu/kernel/conv3d.py:60-64:
+ *   out[n][oc/16][z][y][x][oc%16] = sum a[n][ci][s*z+kd][s*y+kh][s*x+kw][4m+r] * b[oc/16][ci][kd][kh][kw][m][oc%16][r]
+ *   x   [N][Cc][D][H][W][16] u8,  w [Oc][Cc][KD][KH][KW][4][16][4] s8,  out [N][Oc][OD][OH][OW][16] s32 (+ bias).
+ * Explicit zero padding equals convolving the pre-padded input, which is how the reference runs it.
+ */
+int oracle_conv3d_u8s8(const uint8_t *x, const int8_t *w, const int32_t *bias, int32_t *out,
+                       int N, int Cc, int D, int H, int W, int Oc, int KD, int KH, int KW,
+                       int sd, int sh, int sw, int pd, int ph, int pw) {
+  const int OD = (D + 2 * pd - KD) / sd + 1;
+  const int OH = (H + 2 * ph - KH) / sh + 1;
+  const int OW = (W + 2 * pw - KW) / sw + 1;
+  int overflow = 0;
+#pragma omp parallel for collapse(3) reduction(| : overflow) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oc = 0; oc < Oc; ++oc)
+      for (int od = 0; od < OD; ++od)
+        for (int oh = 0; oh < OH; ++oh)
+          for (int ow = 0; ow < OW; ++ow) {
+            int64_t acc[16];
+            for (int l = 0; l < 16; ++l) acc[l] = 0;
+            for (int ic = 0; ic < Cc; ++ic)
+              for (int kd = 0; kd < KD; ++kd) {
+                const int id = od * sd + kd - pd;
+                if (id < 0 || id >= D) continue;
+                for (int kh = 0; kh < KH; ++kh) {
+                  const int ih = oh * sh + kh - ph;
+                  if (ih < 0 || ih >= H) continue;
+                  for (int kw = 0; kw < KW; ++kw) {
+                    const int iw = ow * sw + kw - pw;
+                    if (iw < 0 || iw >= W) continue;
+                    const uint8_t *xp = x + (((((size_t)n * Cc + ic) * D + id) * H + ih) * W + iw) * 16;
+                    const int8_t *wp = w + (((((size_t)oc * Cc + ic) * KD + kd) * KH + kh) * KW + kw) * (size_t)256;
+                    for (int m = 0; m < 4; ++m)
+                      for (int l = 0; l < 16; ++l)
+                        for (int r = 0; r < 4; ++r)
+                          acc[l] += (int32_t)xp[m * 4 + r] * (int32_t)wp[(m * 16 + l) * 4 + r];
+                  }
+                }
+              }
+            const size_t o = (((((size_t)n * Oc + oc) * OD + od) * OH + oh) * OW + ow) * 16;
+            for (int l = 0; l < 16; ++l) {
+              if (acc[l] > INT32_MAX || acc[l] < INT32_MIN) overflow |= 1;
+              out[o + l] = (int32_t)((uint32_t)(uint64_t)acc[l] + (uint32_t)(bias ? bias[oc * 16 + l] : 0));
+            }
+          }
   return overflow;
 }
 

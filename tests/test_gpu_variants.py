@@ -304,6 +304,32 @@ def test_bounded_wait_reports_device_wait_and_the_library_recovers(U, oracle):
         U.device_status()
 
 
+@pytest.mark.parametrize('n,c,d,h,w,co,k,s,p', [
+    (1, 64, 10, 18, 18, 64, 3, 1, 0),      # valid, as the reference runs it: box copies over (depth, rows)
+    (1, 64, 10, 18, 18, 64, 3, 1, 1),      # padded in all three dimensions
+    (2, 64, 11, 19, 19, 32, 3, 2, 1),      # stride 2: im2col copies with three tap offsets; two images
+    (1, 128, 8, 20, 20, 32, 1, 2, 0),      # 1x1x1, stride 2
+    (1, 16, 5, 6, 7, 16, 3, 1, 1),         # small: the cp.async gather
+    (1, 256, 8, 14, 14, 256, 3, 1, 0),     # long reduction (27 taps x 16 chunks), few tiles: split-K
+    (1, 32, 30, 40, 24, 48, 3, 1, 1),      # depth tiles that straddle rows and slices
+])
+def test_conv3d_int8_bit_exact(U, oracle, n, c, d, h, w, co, k, s, p):
+    """Three-dimensional convolution on NCDHW16c (apps/cpu/kernel/conv3d.py:39-64): the depth axis runs
+    through the same kernel in place of the batch axis.  Bit-exact, s32 with bias and requantised."""
+    rng = np.random.default_rng(n + c + d + h + co + k + s)
+    x = rng.integers(0, 256, (n, c // 16, d, h, w, 16), dtype=np.uint8)
+    wt = rng.integers(-128, 128, (co // 16, c // 16, k, k, k, 4, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 15, 2 ** 15, co, dtype=np.int32)
+    ref = oracle.conv3d_u8s8(x, wt, (s, s, s), (p, p, p), bias=b)
+    got = U.conv3d_NCDHWc_int8(dev(x), dev(wt), stride=s, padding=p, bias=dev(b))
+    U.device_status()
+    assert np.array_equal(got.cpu().numpy(), ref)
+    gotq = U.conv3d_NCDHWc_int8(dev(x), dev(wt), stride=s, padding=p, bias=dev(b), requant_shift=10)
+    want = np.clip((ref.astype(np.int64) + 512) >> 10, 0, 255).astype(np.uint8)
+    assert np.array_equal(gotq.cpu().numpy(), want)
+    U.device_status()
+
+
 def test_zz_every_compiled_variant_was_launched(U):
     """Runs after the cases above (same module, definition order): no compiled variant is left
     that no parity case reaches."""

@@ -185,3 +185,24 @@ def test_layout_round_trips():
     wp = no.pack_oihw_to_int8_weights(w)
     oc, ic, kh, kw = 21, 37, 2, 1
     assert wp[oc // 16, ic // 16, kh, kw, (ic % 16) // 4, oc % 16, ic % 4] == w[oc, ic, kh, kw]
+
+
+@pytest.mark.parametrize('c,d,h,w,co,k,s,p', [(16, 5, 6, 7, 16, 3, 1, 1), (32, 6, 7, 5, 32, 2, 2, 0), (16, 4, 9, 9, 16, 1, 2, 0)])
+def test_conv3d_oracle_is_a_sum_of_2d_convolutions_over_the_depth_taps(oracle, c, d, h, w, co, k, s, p):
+    """The 3-D definition (apps/cpu/kernel/conv3d.py:60-64) against the 2-D one: output slice od is the
+    sum over kd of the 2-D convolution of input slice od*s + kd - p with the kd-th slice of the kernel."""
+    rng = np.random.default_rng(c + d + k)
+    x = rng.integers(0, 256, (2, c // 16, d, h, w, 16), dtype=np.uint8)
+    wt = rng.integers(-128, 128, (co // 16, c // 16, k, k, k, 4, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 15, 2 ** 15, co, dtype=np.int32)
+    got = oracle.conv3d_u8s8(x, wt, (s, s, s), (p, p, p), bias=b)
+    od = (d + 2 * p - k) // s + 1
+    assert got.shape[2] == od
+    for z in range(od):
+        acc = np.zeros(got[:, :, z].shape, np.int64)
+        for kd in range(k):
+            iz = z * s + kd - p
+            if 0 <= iz < d:
+                acc += oracle.conv2d_u8s8(np.ascontiguousarray(x[:, :, iz]), np.ascontiguousarray(wt[:, :, kd]), (s, s), (p, p))
+        acc += b.reshape(1, -1, 1, 1, 16)
+        assert np.array_equal(got[:, :, z], acc.astype(np.int32))

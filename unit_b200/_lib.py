@@ -29,6 +29,13 @@ class ConvDesc(ctypes.Structure):
                 ('n', 'c_in', 'h', 'w', 'c_block', 'c_out', 'kh', 'kw', 'stride_h', 'stride_w', 'pad_h', 'pad_w')]
 
 
+class Conv3dDesc(ctypes.Structure):
+    """Mirror of ``unit_conv3d_desc``."""
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ('n', 'c_in', 'd', 'h', 'w', 'c_out', 'kd', 'kh', 'kw', 'stride_d', 'stride_h', 'stride_w',
+                 'pad_d', 'pad_h', 'pad_w')]
+
+
 class Epilogue(ctypes.Structure):
     """Mirror of ``unit_epilogue``."""
     _fields_ = [('d_bias', ctypes.c_void_p), ('mul', ctypes.c_int32), ('shift', ctypes.c_int32),
@@ -46,6 +53,7 @@ DEBUG_STALL_WEIGHT_COPIES = 2
 _dp = ctypes.POINTER(ConvDesc)
 _ep = ctypes.POINTER(Epilogue)
 _pp = ctypes.POINTER(ConvPlan)
+_d3 = ctypes.POINTER(Conv3dDesc)
 SIGNATURES = {
     'unit_version': (_ci, []),
     'unit_status_string': (ctypes.c_char_p, [_ci]),
@@ -71,6 +79,9 @@ SIGNATURES = {
     'unit_conv2d_int8_nchwc': (_ci, [_dp, _vp, _vp, _ep, _vp, _vp, _sz, _vp]),
     'unit_conv2d_plan_int8': (_ci, [_dp, _vp, _vp, _ep, _vp, _vp, _sz, _pp]),
     'unit_conv2d_run': (_ci, [_pp, _vp]),
+    'unit_packed_weights_bytes_conv3d_i8': (_sz, [_d3]),
+    'unit_pack_weights_conv3d_i8': (_ci, [_d3, _vp, _vp, _vp]),
+    'unit_conv3d_int8_ncdhwc': (_ci, [_d3, _vp, _vp, _ep, _vp, _vp]),
     'unit_noalloc_scratch_capacity': (_sz, []),
     'unit_conv2d_u8s8_requant_nchwc_noalloc': (_ci, [_dp, _vp, _vp, _vp, _ci, _vp, _vp]),
     'unit_dense_u8s8s32': (_ci, [_ci, _ci, _ci, _vp, _i64, _vp, _vp, _i64, _vp]),

@@ -155,6 +155,15 @@ struct IgemmParams {
   // share one tile; CTA `rank` accumulates pipeline stages [rank * ks_per, (rank + 1) * ks_per) and the
   // partial accumulators are exchanged through distributed shared memory (see the kernel)
   int ksplit, ks_per;
+  // Convolution in three dimensions (one image, [c/16][D][H][W][16]): the depth axis takes the place of
+  // the image axis of the two-dimensional kernel (a 128-row tile then runs over (od, oh, ow)), kernel
+  // depth KD adds a third tap index, and the output strides below place (od, channel group).
+  // Two-dimensional calls use KD = 1, sd = 1, pd = 0, out_img_stride = (c_out / 16) * OH * OW,
+  // out_grp_stride = OH * OW, src_img_bytes = img_bytes, src_chunk_bytes = H * W * (bytes per chunk pixel).
+  int KD, sd, pd;
+  long long out_img_stride, out_grp_stride;  // in units of 16 output elements
+  long long src_img_bytes, src_chunk_bytes;  // gather paths: bytes between images (depth slices) and channel chunks
+  int src_imgs;                              // images (depth slices) of the input
   unsigned long long *trace;  // optional: 8 timestamps (ns) per tile of CTA 0, see unit_trace_attach
   int trace_cap;              // tiles the trace buffer holds
 };
@@ -305,11 +314,11 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
 // im2col-mode tensor copy: `pixelsPerColumn` consecutive output positions, starting at the
 // filter-window origin (w, h, d) of the first one, tap offset (woff, hoff), channel c of chunk n.
 __device__ __forceinline__ void tma_im2col_5d(uint32_t dst, const CUtensorMap *tmap, int c, int w, int h, int d, int n,
-                                              uint16_t woff, uint16_t hoff, uint32_t bar) {
+                                              uint16_t woff, uint16_t hoff, uint16_t doff, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
       "%5, %6}], [%7], {%8, %9, %10};" ::"r"(dst),
-      "l"(tmap), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "r"(bar), "h"(woff), "h"(hoff), "h"((uint16_t)0)
+      "l"(tmap), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "r"(bar), "h"(woff), "h"(hoff), "h"(doff)
       : "memory");
 }
 // tiled-mode tensor copy of one box of the 4-D tensor (x, y, z, w) = (16-byte units of a pixel row,
@@ -775,7 +784,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       int row[RPT];
       bool rvalid[MT][RPT];
       const uint8_t *rbase[MT][RPT];
-      int ih0[MT][RPT], iw0[MT][RPT];
+      int ih0[MT][RPT], iw0[MT][RPT], id0[MT][RPT];
 #pragma unroll
       for (int i = 0; i < RPT; ++i) {
         if constexpr (AMODE == A_CONV_I8 || AMODE == A_STEM_I8) row[i] = pw * 32 + lane;
@@ -787,7 +796,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           rvalid[t][i] = m < p.m_total;
           if constexpr (AMODE == A_DENSE) {
             rbase[t][i] = p.a + (rvalid[t][i] ? m : 0) * p.lda;
-            ih0[t][i] = iw0[t][i] = 0;
+            ih0[t][i] = iw0[t][i] = id0[t][i] = 0;
           } else {
             // m_total < 2^31 is checked on the host: 32-bit divisions
             const unsigned mm = rvalid[t][i] ? (unsigned)m : 0u;
@@ -797,13 +806,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             const int oh = rem / p.OW, ow = rem - oh * p.OW;
             ih0[t][i] = oh * p.sh - p.ph;
             iw0[t][i] = ow * p.sw - p.pw;
-            rbase[t][i] = p.a + (long long)n_img * p.img_bytes;
+            // (three dimensions: n_img is the output depth; the first input slice is n_img * sd - pd)
+            id0[t][i] = n_img * p.sd - p.pd;
+            rbase[t][i] = p.a + (long long)id0[t][i] * p.src_img_bytes;
           }
         }
       }
 
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 0);
-      int ci = 0, kh = 0, kw = 0;  // position of the next K column (conv modes)
+      int ci = 0, kh = 0, kw = 0, kd = 0;  // position of the next K column (conv modes)
       for (int ks = 0; ks < p.k_stages; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
@@ -816,12 +827,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
               const int ih = ih0[t][0] + kh, iw = iw0[t][0] + kw;
-              const bool ok = rvalid[t][0] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-              const uint8_t *src = ok ? rbase[t][0] + ((long long)(ci * p.H + ih) * p.W + iw) * 16 : p.a;
+              const bool ok = rvalid[t][0] && j < p.cols && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W &&
+                              (unsigned)(id0[t][0] + kd) < (unsigned)p.src_imgs;
+              const uint8_t *src = ok ? rbase[t][0] + (long long)kd * p.src_img_bytes + (long long)ci * p.src_chunk_bytes +
+                                            ((long long)ih * p.W + iw) * 16
+                                      : p.a;
               cp_async16(a_dst + (uint32_t)t * a_sub_bytes + (uint32_t)jj * kSubBytes + (uint32_t)row[0] * 16u, src,
                          ok ? 16u : 0u);
             }
-            if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; ++kh; } }
+            if (++ci == p.Cc) { ci = 0; if (++kw == p.KW) { kw = 0; if (++kh == p.KH) { kh = 0; ++kd; } } }
           }
         } else if constexpr (AMODE == A_CONV_F16) {
           const int half = (lane >> 3) & 1;
@@ -916,7 +930,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
         c0 = ((int)wb * p.box_w - p.pw) * (F16 ? 1 : 2);  // u8: 8-byte units of a pixel row; fp16: pixels
         c1 = (int)hb * p.box_h - p.ph;
-        c2 = (int)nb * p.box_n;
+        c2 = (int)nb * p.box_n - p.pd;
       } else {
         long long m = ((long long)m_tile * MT + t) * kTileM;
         if (m >= p.m_total) m = 0;  // a sub-tile past the end: fetch valid data, nothing of it is stored
@@ -926,7 +940,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t ow = rem - oh * (uint32_t)p.OW;
         c0 = (int)ow * p.sw - p.pw;
         c1 = (int)oh * p.sh - p.ph;
-        c2 = (int)n_img;
+        c2 = (int)n_img * p.sd - p.pd;
       }
       // sub-tiles that exist in this tile, and the bytes one copy delivers
       int nsub = MT;
@@ -942,11 +956,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const int half = jj % cpc;
       const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
       int q0 = jj / cpc + ks_begin * chunk_step;  // chunk index along K of this lane's first column
-      int kh = 0, kw = 0, ci = 0;
+      int kh = 0, kw = 0, ci = 0, kd = 0;
       if constexpr (AMODE != A_DENSE_TMA) {
-        kh = q0 / (p.Cc * p.KW);
-        kw = (q0 / p.Cc) % p.KW;
-        ci = q0 % p.Cc;
+        const int tap = q0 / p.Cc;  // taps run (kd, kh, kw), kw fastest
+        ci = q0 - tap * p.Cc;
+        kw = tap % p.KW;
+        kh = (tap / p.KW) % p.KH;
+        kd = tap / (p.KW * p.KH);
       }
       // row form: jj counts kernel rows of the stage, each copied once into the slot of its first column
       const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
@@ -975,7 +991,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           __syncwarp();
           if (jj < steps && sub_ok) {
             const uint32_t dst = smem_base + s * stage_bytes + (uint32_t)t * a_sub_bytes + (uint32_t)jj * 2u * kSubBytes;
-            tma_tile_5d(dst, &tmap, 0, c0 + kw, c1 + kh, ci, c2, bar);
+            tma_tile_5d(dst, &tmap, 0, c0 + kw, c1 + kh, ci, c2 + kd, bar);
           }
         } else if (row_form) {
           if (tx_poster) mbar_arrive_expect_tx(bar, (uint32_t)(rows_per_stage * nsub) * (uint32_t)p.row_bytes);
@@ -993,15 +1009,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             if constexpr (AMODE == A_DENSE_TMA)
               tma_tile_3d(dst, &tmap, 0, ks * p.kc + jj, c0, bar);
             else if constexpr (AMODE == A_CONV_BOX)
-              tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2, bar);
+              tma_tile_4d(dst, &tmap, c0 + kw * 2, c1 + kh, ci, c2 + kd, bar);
             else
-              tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, bar);
+              tma_im2col_5d(dst, &tmap, half * 8, c0, c1, c2, ci, (uint16_t)kw, (uint16_t)kh, (uint16_t)kd, bar);
           }
         }
         // advance this lane's column by one stage
         if constexpr (AMODE != A_DENSE_TMA) {
           ci += chunk_step;
-          while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; ++kh; } }
+          while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; if (++kh == p.KH) { kh = 0; ++kd; } } }
         }
         if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
       }
@@ -1171,7 +1187,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       dh = fast_div(rr, p.div_box_w);
       dw = rr - dh * (uint32_t)p.box_w;
     }
-    const long long gstride = (EPI == EPI_RAW_ROWS) ? 16 : (long long)ohw * 16;  // between 16-column groups
+    const long long gstride = (EPI == EPI_RAW_ROWS) ? 16 : p.out_grp_stride * 16;  // between 16-column groups
     const int tile_step = (int)nslots * tstep;  // from one tile of this group to its next
     // The set's bias: the column block it is prepared for, the verdict, and which of the two
     // integer buffers holds the values (it flips at every preparation, so that a warp preparing
@@ -1208,15 +1224,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t hb = q - nb * (uint32_t)p.blocks_h;
         const int n_i = (int)nb * p.box_n + (int)dn, oh = (int)hb * p.box_h + (int)dh, ow = (int)wb * p.box_w + (int)dw;
         mvalid = st < p.sub_tiles && (int)dn < p.box_n && n_i < p.n_img && oh < p.OH && ow < p.OW;
-        obase = (((long long)n_i * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + (long long)oh * p.OW + ow) * 16;
+        obase = ((long long)n_i * p.out_img_stride + (long long)n_tile * (p.bn >> 4) * p.out_grp_stride + (long long)oh * p.OW + ow) * 16;
       } else if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
       } else {
         const unsigned mm = mvalid ? (unsigned)m : 0u;
         const long long n_img = (long long)(mm / (unsigned)ohw);
         const long long rem = (long long)mm - n_img * ohw;
-        // [n][oc/16][ohw][16]: column group g of this tile adds g * ohw * 16
-        obase = ((n_img * (p.n_total >> 4) + (long long)n_tile * (p.bn >> 4)) * ohw + rem) * 16;
+        // [n][oc/16][ohw][16] (or [oc/16][od][ohw][16]): column group g of this tile adds g * out_grp_stride * 16
+        obase = (n_img * p.out_img_stride + (long long)n_tile * (p.bn >> 4) * p.out_grp_stride + rem) * 16;
       }
       const int32_t *tile_bias = &ps->bias[slot][ver][0];
       if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, wc, kErrWaitTmemFull)) break;

@@ -910,6 +910,38 @@ static bool make_im2col_map(CUtensorMap *map, const unit_conv_desc *d, const voi
   return r == CUDA_SUCCESS;
 }
 
+// The same for one three-dimensional image [c/16][D][H][W][16] (u8): the depth axis is the map's fourth
+// dimension (where the two-dimensional map has the image), the channel chunk the fifth.
+static bool make_im2col_map_3d(CUtensorMap *map, const unit_conv3d_desc *d, const void *x) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  if (!tensor_map_allowed((long long)d->c_in * d->d * d->h * d->w)) return false;
+  if (d->pad_w > 15 || d->pad_h > 15 || d->pad_d > 15 || d->kw > 16 || d->kh > 16 || d->kd > 16 || d->stride_w > 8 ||
+      d->stride_h > 8 || d->stride_d > 8)
+    return false;
+  const cuuint64_t cc = (cuuint64_t)d->c_in / 16;
+  const cuuint64_t dims[5] = {16, (cuuint64_t)d->w, (cuuint64_t)d->h, (cuuint64_t)d->d, cc};
+  const cuuint64_t plane = (cuuint64_t)d->h * d->w * 16;
+  const cuuint64_t strides[4] = {16, (cuuint64_t)d->w * 16, plane, plane * d->d};
+  const int lower[3] = {-d->pad_w, -d->pad_h, -d->pad_d};
+  const int upper[3] = {d->pad_w - (d->kw - 1), d->pad_h - (d->kh - 1), d->pad_d - (d->kd - 1)};
+  const cuuint32_t estr[5] = {1, (cuuint32_t)d->stride_w, (cuuint32_t)d->stride_h, (cuuint32_t)d->stride_d, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void *>(x), dims, strides, lower, upper, 16,
+                            kTileM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // Box geometry for A_CONV_BOX: a 128-row sub-tile covers box_n images x box_h output rows x box_w
 // output columns.  Picks the split with the fewest sub-tiles (least idle MMA rows), preferring
 // taller boxes (longer contiguous runs per image).
@@ -942,8 +974,10 @@ static BoxGeom choose_box(int n, int oh, int ow) {
 // Tiled-mode tensor map over u8 NCHW16c activations seen as (8-byte units of a pixel row, image
 // row, channel chunk, image): one copy fetches box_n x box_h row segments of box_w pixels, and
 // out-of-range coordinates (the zero padding) are filled with zeros by the copy engine.
+// (depth > 0: one three-dimensional image [c/16][depth][h][w][16]; the map's fourth dimension is then the
+// depth axis and `n` is ignored.)
 static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g,
-                         int extra_w = 0) {
+                         int extra_w = 0, int depth = 0) {
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -955,11 +989,11 @@ static bool make_box_map(CUtensorMap *map, int n, int c_in, int h, int w, const 
       fn = nullptr;
     return reinterpret_cast<EncodeFn>(fn);
   }();
-  if (!encode || !tensor_map_allowed((long long)n * c_in * h * w)) return false;
+  if (!encode || !tensor_map_allowed((long long)(depth > 0 ? depth : n) * c_in * h * w)) return false;
   const cuuint64_t cc = (cuuint64_t)c_in / 16;
-  const cuuint64_t dims[4] = {(cuuint64_t)w * 2, (cuuint64_t)h, cc, (cuuint64_t)n};
+  const cuuint64_t dims[4] = {(cuuint64_t)w * 2, (cuuint64_t)h, cc, (cuuint64_t)(depth > 0 ? depth : n)};
   const cuuint64_t row = (cuuint64_t)w * 16;
-  const cuuint64_t strides[3] = {row, row * h, row * h * cc};
+  const cuuint64_t strides[3] = {row, depth > 0 ? row * h * depth : row * h, depth > 0 ? row * h : row * h * cc};
   const cuuint32_t box[4] = {(cuuint32_t)(g.bw + extra_w) * 2, (cuuint32_t)g.bh, 1, (cuuint32_t)g.bn};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void *>(x), dims, strides, box, estr,
@@ -1077,6 +1111,13 @@ static void fill_conv(IgemmParams &p, const unit_conv_desc *d, int elem_bytes) {
   p.div_ohw = make_fast_div((uint32_t)(p.OH * p.OW));
   p.div_ow = make_fast_div((uint32_t)p.OW);
   p.cols_per_chunk = elem_bytes;
+  // the two-dimensional case of the fields that three-dimensional convolutions set differently
+  p.KD = 1; p.sd = 1; p.pd = 0;
+  p.out_grp_stride = (long long)p.OH * p.OW;
+  p.out_img_stride = (long long)(d->c_out / 16) * p.OH * p.OW;
+  p.src_img_bytes = p.img_bytes;
+  p.src_chunk_bytes = (long long)d->h * d->w * d->c_block * elem_bytes;
+  p.src_imgs = d->n;
 }
 
 static void set_box(IgemmParams &p, const BoxGeom &g, int n) {
@@ -1149,6 +1190,8 @@ static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, co
     q.p.b = static_cast<const uint8_t *>(pw) + generic_bytes;
     q.p.H = f.h2; q.p.W = f.w2; q.p.Cc = 1; q.p.KH = f.th; q.p.KW = f.tw; q.p.sh = q.p.sw = 1; q.p.ph = f.pad_h; q.p.pw = f.pad_w;
     q.p.img_bytes = (long long)f.h2 * f.w2 * 16;
+    q.p.src_img_bytes = q.p.img_bytes;
+    q.p.src_chunk_bytes = q.p.img_bytes;
     const BoxGeom g = choose_box(d->n, q.p.OH, q.p.OW);
     // row form (one copy per kernel row instead of one per tap) when a sub-tile is a single row
     // segment, the kernel width is even (column pairs stay inside a kernel row) and the stages
@@ -1173,6 +1216,69 @@ static int conv_i8(const unit_conv_desc *d, const void *x, const void *pw, const
   PlanImpl pl;
   const int rc = plan_conv_i8(pl, d, x, pw, e, out, workspace, workspace_bytes);
   return rc ? rc : run_plan(pl, st);
+}
+
+// ---- three-dimensional int8 convolution (one image per launch) ----
+static int check_conv3d(const unit_conv3d_desc *d) {
+  if (!d) return UNIT_ERR_NULL;
+  if (d->n < 1 || d->c_in < 1 || d->d < 1 || d->h < 1 || d->w < 1 || d->c_out < 1 || d->kd < 1 || d->kh < 1 || d->kw < 1 ||
+      d->stride_d < 1 || d->stride_h < 1 || d->stride_w < 1 || d->pad_d < 0 || d->pad_h < 0 || d->pad_w < 0)
+    return UNIT_ERR_SHAPE;
+  if (d->c_in % 16 || d->c_out % 16) return UNIT_ERR_LAYOUT;
+  if (d->d + 2 * d->pad_d < d->kd || d->h + 2 * d->pad_h < d->kh || d->w + 2 * d->pad_w < d->kw) return UNIT_ERR_SHAPE;
+  if (d->kd > 16 || d->kh > 16 || d->kw > 16) return UNIT_ERR_SHAPE;
+  const long long img = (long long)d->c_in * d->d * d->h * d->w;
+  if (img >= (1ll << 31)) return UNIT_ERR_TOO_LARGE;
+  const long long od = (d->d + 2 * d->pad_d - d->kd) / d->stride_d + 1, oh = (d->h + 2 * d->pad_h - d->kh) / d->stride_h + 1,
+                  ow = (d->w + 2 * d->pad_w - d->kw) / d->stride_w + 1;
+  if (od * oh * ow >= (1ll << 31) - 512 || od * oh * ow * d->c_out >= (1ll << 31)) return UNIT_ERR_TOO_LARGE;
+  return UNIT_OK;
+}
+static TileCfg conv3d_cfg(const unit_conv3d_desc *d) {
+  const bool cheap = d->stride_d == 1 && d->stride_h == 1 && d->stride_w == 1;
+  return make_cfg(d->c_out, d->kd * d->kh * d->kw * (d->c_in / 16), cheap);
+}
+
+// Plan for image `img` of the batch.  The depth axis takes the place of the two-dimensional kernel's
+// image axis: a 128-row tile runs over (od, oh, ow) of one image.
+static int plan_conv3d_i8(PlanImpl &pl, const unit_conv3d_desc *d, const uint8_t *x, const void *pw, const EpilogueArgs &e,
+                          void *out) {
+  const TileCfg c = conv3d_cfg(d);
+  const int epi = e.out_u8 ? (e.residual ? EPI_RES_NCHWC : EPI_REQ_NCHWC) : (e.mul != 1 ? EPI_MUL_NCHWC : EPI_RAW_NCHWC);
+  pl = PlanImpl{};
+  IgemmParams &p = pl.p;
+  p.a = x; p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = e.bias; p.shift = e.shift;
+  p.mul = e.mul; p.residual = e.residual; p.a_signed = e.x_signed ? 1 : 0;
+  p.H = d->h; p.W = d->w; p.Cc = d->c_in / 16;
+  p.KD = d->kd; p.KH = d->kh; p.KW = d->kw;
+  p.sd = d->stride_d; p.sh = d->stride_h; p.sw = d->stride_w;
+  p.pd = d->pad_d; p.ph = d->pad_h; p.pw = d->pad_w;
+  const int OD = (d->d + 2 * d->pad_d - d->kd) / d->stride_d + 1;
+  p.OH = (d->h + 2 * d->pad_h - d->kh) / d->stride_h + 1;
+  p.OW = (d->w + 2 * d->pad_w - d->kw) / d->stride_w + 1;
+  p.m_total = (long long)OD * p.OH * p.OW;
+  p.n_total = d->c_out;
+  p.div_ohw = make_fast_div((uint32_t)(p.OH * p.OW));
+  p.div_ow = make_fast_div((uint32_t)p.OW);
+  p.cols_per_chunk = 1;
+  p.out_img_stride = (long long)p.OH * p.OW;            // one output depth position further
+  p.out_grp_stride = (long long)OD * p.OH * p.OW;       // [c_out/16][OD][OH][OW][16]
+  p.src_img_bytes = (long long)d->h * d->w * 16;        // one depth slice of a chunk
+  p.src_chunk_bytes = p.src_img_bytes * d->d;
+  p.img_bytes = p.src_img_bytes;
+  p.src_imgs = d->d;
+  p.n_img = OD;
+  p.acc_bound = 255ll * 128ll * d->c_in * d->kd * d->kh * d->kw;
+  CUtensorMap map;
+  if (use_tma() && d->stride_d == 1 && d->stride_h == 1 && d->stride_w == 1) {
+    const BoxGeom g = choose_box(OD, p.OH, p.OW);
+    if (make_box_map(&map, 1, d->c_in, d->h, d->w, x, g, 0, d->d)) {
+      set_box(p, g, OD);
+      return prepare_conv_i8<A_CONV_BOX>(pl, c, epi, &map);
+    }
+  }
+  if (use_tma() && make_im2col_map_3d(&map, d, x)) return prepare_conv_i8<A_CONV_TMA>(pl, c, epi, &map);
+  return prepare_conv_i8<A_CONV_I8>(pl, c, epi);
 }
 
 // Device address of g_static_scratch on the current device.  In host code the array's name is
@@ -1445,6 +1551,57 @@ int unit_conv2d_run(const unit_conv_plan *plan, void *stream) {
   PlanImpl pl;
   memcpy(&pl, plan, sizeof(pl));
   return run_plan(pl, static_cast<cudaStream_t>(stream));
+}
+
+size_t unit_packed_weights_bytes_conv3d_i8(const unit_conv3d_desc *d) {
+  if (check_conv3d(d)) return 0;
+  const TileCfg c = conv3d_cfg(d);
+  return (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+}
+
+int unit_pack_weights_conv3d_i8(const unit_conv3d_desc *d, const int8_t *w, void *packed, void *stream) {
+  int rc = check_conv3d(d);
+  if (rc) return rc;
+  if (!w || !packed) return UNIT_ERR_NULL;
+  if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
+  const TileCfg c = conv3d_cfg(d);
+  PackParams pp{};
+  pp.src = reinterpret_cast<const uint8_t *>(w);
+  pp.dst = static_cast<uint4 *>(packed);
+  pp.mode = PACK_CONV_I8;
+  pp.n_total = d->c_out; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
+  // [c_out/16][c_in/16][kd][kh][kw][4][16][4]: the depth and height taps form one axis of kd * kh entries
+  pp.Cc = d->c_in / 16; pp.KH = d->kd * d->kh; pp.KW = d->kw;
+  return launch_pack(pp, static_cast<cudaStream_t>(stream));
+}
+
+int unit_conv3d_int8_ncdhwc(const unit_conv3d_desc *d, const void *x, const void *pw, const unit_epilogue *epi, void *out,
+                            void *stream) {
+  int rc = check_conv3d(d);
+  if (rc) return rc;
+  EpilogueArgs e;
+  if ((rc = epilogue_from(epi, &e))) return rc;
+  if (!x || !pw || !out) return UNIT_ERR_NULL;
+  if (!aligned16(x) || !aligned16(pw) || !aligned16(out) || (e.bias && !aligned16(e.bias)) || (e.residual && !aligned16(e.residual)))
+    return UNIT_ERR_ALIGN;
+  if (e.out_u8 && (e.shift < 1 || e.shift > 31 || e.mul != 1)) return UNIT_ERR_SHAPE;
+  if (!e.out_u8 && (e.residual != nullptr || e.shift != 0)) return UNIT_ERR_SHAPE;
+  if ((rc = check_arch())) return rc;
+  const long long in_bytes = (long long)d->c_in * d->d * d->h * d->w;
+  const long long od = (d->d + 2 * d->pad_d - d->kd) / d->stride_d + 1, oh = (d->h + 2 * d->pad_h - d->kh) / d->stride_h + 1,
+                  ow = (d->w + 2 * d->pad_w - d->kw) / d->stride_w + 1;
+  const long long out_elems = od * oh * ow * d->c_out;
+  for (int img = 0; img < d->n; ++img) {  // one launch per image
+    EpilogueArgs ei = e;
+    if (e.residual) ei.residual = e.residual + img * out_elems;
+    void *oi = e.out_u8 ? static_cast<void *>(static_cast<uint8_t *>(out) + img * out_elems)
+                        : static_cast<void *>(static_cast<int32_t *>(out) + img * out_elems);
+    PlanImpl pl;
+    rc = plan_conv3d_i8(pl, d, static_cast<const uint8_t *>(x) + img * in_bytes, pw, ei, oi);
+    if (rc == UNIT_OK) rc = run_plan(pl, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return UNIT_OK;
 }
 
 size_t unit_noalloc_scratch_capacity(void) { return kStaticScratchBytes; }

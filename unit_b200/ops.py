@@ -26,7 +26,7 @@ from typing import Optional, Sequence, Tuple, Union
 import torch
 
 from . import _lib
-from ._lib import ConvDesc, ConvPlan as _CPlan, Epilogue, check
+from ._lib import Conv3dDesc, ConvDesc, ConvPlan as _CPlan, Epilogue, check
 
 IntPair = Union[int, Sequence[int]]
 
@@ -379,6 +379,96 @@ def conv2d_NCHWc_int8_plan(data: torch.Tensor, kernel, stride: IntPair = 1, padd
     return ConvPlan(plan, out_t, tensors + (ws,))
 
 
+def _triple(v) -> Tuple[int, int, int]:
+    if isinstance(v, int):
+        return (v, v, v)
+    v = tuple(int(t) for t in v)
+    if len(v) != 3:
+        raise ValueError(f'expected one or three values, got {v}')
+    return v
+
+
+def pack_conv3d_weights_int8(kernel: torch.Tensor, stride=1) -> PackedWeights:
+    """kernel: s8 ``[O/16][I/16][KD][KH][KW][4][16][4]`` (apps/cpu/kernel/conv3d.py:41)."""
+    L = _require_cuda_lib()
+    kernel = _to_device(kernel, torch.int8, 'kernel')
+    if kernel.dim() != 8 or tuple(kernel.shape[5:]) != (4, 16, 4):
+        raise ValueError(f'kernel must be [O/16][I/16][KD][KH][KW][4][16][4], got {tuple(kernel.shape)}')
+    oc, icc, kd, kh, kw = (int(s) for s in kernel.shape[:5])
+    stride = _triple(stride)
+    key = ('conv3d_i8', oc * 16, icc * 16, kd, kh, kw, stride)
+
+    def make():
+        d = Conv3dDesc(1, icc * 16, kd + 32, kh + 32, kw + 32, oc * 16, kd, kh, kw, stride[0], stride[1], stride[2], 0, 0, 0)
+        nbytes = L.unit_packed_weights_bytes_conv3d_i8(ctypes.byref(d))
+        if nbytes == 0:
+            raise ValueError('unsupported convolution weights')
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=kernel.device)
+        check(L.unit_pack_weights_conv3d_i8(ctypes.byref(d), _ptr(kernel), _ptr(buf), _stream()), 'unit_pack_weights_conv3d_i8')
+        return PackedWeights('conv3d_i8', buf, key)
+
+    with torch.cuda.device(kernel.device):
+        return _cached(kernel, key, make)
+
+
+def conv3d_NCDHWc_int8(data: torch.Tensor, kernel, stride=1, padding=0, out_dtype: str = 'int32', *,
+                       bias: Optional[torch.Tensor] = None, requant_shift: Optional[int] = None, mul: int = 1,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """u8 (or s8) x s8 -> s32 three-dimensional convolution on ``[N][C/16][D][H][W][16]`` data with
+    ``[O/16][C/16][KD][KH][KW][4][16][4]`` weights (apps/cpu/kernel/conv3d.py:39-64); result
+    ``[N][O/16][OD][OH][OW][16]``.  Epilogue options as for ``conv2d_NCHWc_int8``."""
+    L = _require_cuda_lib()
+    stride, padding = _triple(stride), _triple(padding)
+    if out_dtype not in ('int32', 'uint8'):
+        raise ValueError("out_dtype must be 'int32' or 'uint8'")
+    host = not data.is_cuda
+    if data.dtype not in (torch.uint8, torch.int8):
+        raise TypeError(f'data: expected torch.uint8 (or torch.int8), got {data.dtype}')
+    signed = data.dtype == torch.int8
+    data = _to_device(data, data.dtype, 'data')
+    if data.dim() != 6 or data.shape[5] != 16:
+        raise ValueError(f'data must be [N][C/16][D][H][W][16], got {tuple(data.shape)}')
+    n, cc, dd, h, w, _ = (int(s) for s in data.shape)
+    with torch.cuda.device(data.device):
+        pw = kernel if isinstance(kernel, PackedWeights) else pack_conv3d_weights_int8(kernel, stride)
+        if pw.kind != 'conv3d_i8':
+            raise ValueError('kernel was packed for a different operator')
+        pw.sync_to_current_stream()
+        _, c_out, c_in, kd, kh, kw, pstride = pw.key
+        if c_in != cc * 16:
+            raise ValueError(f'channel mismatch: data has {cc * 16}, kernel expects {c_in}')
+        if pstride != stride:
+            raise ValueError('weights were packed for a different stride')
+        if dd + 2 * padding[0] < kd or h + 2 * padding[1] < kh or w + 2 * padding[2] < kw:
+            raise ValueError('kernel larger than padded input')
+        requant = out_dtype == 'uint8' or requant_shift is not None
+        shift = (8 if requant_shift is None else int(requant_shift)) if requant else 0
+        if requant and int(mul) != 1:
+            raise ValueError('mul applies to the int32 output only')
+        od = (dd + 2 * padding[0] - kd) // stride[0] + 1
+        oh = (h + 2 * padding[1] - kh) // stride[1] + 1
+        ow = (w + 2 * padding[2] - kw) // stride[2] + 1
+        if bias is not None:
+            bias = _to_device(bias, torch.int32, 'bias')
+            if bias.numel() != c_out:
+                raise ValueError(f'bias must have {c_out} elements')
+        oshape = (n, c_out // 16, od, oh, ow, 16)
+        odt = torch.uint8 if requant else torch.int32
+        if out is None:
+            out_t = torch.empty(oshape, dtype=odt, device=data.device)
+        else:
+            out_t = out
+            if tuple(out_t.shape) != oshape or out_t.dtype != odt or not out_t.is_cuda or not out_t.is_contiguous():
+                raise ValueError(f'out must be a contiguous CUDA {odt} tensor of shape {oshape}')
+        if n == 0:
+            return out_t.cpu() if (host and out is None) else out_t
+        d = Conv3dDesc(n, c_in, dd, h, w, c_out, kd, kh, kw, stride[0], stride[1], stride[2], padding[0], padding[1], padding[2])
+        epi = Epilogue(None if bias is None else bias.data_ptr(), int(mul), shift, 1 if requant else 0, None, 1 if signed else 0)
+        check(L.unit_conv3d_int8_ncdhwc(ctypes.byref(d), _ptr(data), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _stream()),
+              'unit_conv3d_int8_ncdhwc')
+    return out_t.cpu() if (host and out is None) else out_t
+
+
 def dense_dotprod(data: torch.Tensor, weight, bias: Optional[torch.Tensor] = None, out_dtype: str = 'int32', *,
                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[i][j] = sum_k u8 data[i][k] * s8 weight[j/T][k/4][j%T][k%4]  -> s32 [M][N]."""
@@ -579,6 +669,7 @@ INTRINSICS = {
     'vnni': {
         'pattern': {'out_lanes': 16, 'reduce_lanes': 4, 'a_dtype': 'uint8', 'b_dtype': 'int8', 'out_dtype': 'int32'},
         'conv2d': conv2d_NCHWc_int8,
+        'conv3d': conv3d_NCDHWc_int8,
         'dense': dense_dotprod,
     },
     'tensorcore': {
