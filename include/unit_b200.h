@@ -144,6 +144,25 @@ int unit_trace_attach(void *d_buf, int32_t capacity_tiles);
 int unit_tensor_peak(int32_t f16, int32_t n, int32_t issuers, int32_t iters, double *ops_per_second,
                      void *stream);
 
+/* Per-shape tile table, the counterpart of the reference's tuning logs (cpu-tune.log, gpu-tune.log:
+ * shape -> index of the best schedule, loaded by python/tensorizer/tune.py:20-51).  An entry names an
+ * int8 NCHW16c convolution by its weight-side geometry and, optionally, one input size (n > 0), and
+ * overrides what the library's heuristics would choose:
+ *   bn      width of a column block (multiple of 16, <= 256; 0 = heuristic), and
+ *   kc      16-byte K columns per pipeline stage (even, <= 16; 0 = heuristic): these two shape the
+ *           packed weights, so they are taken only from entries with n = 0 (every input size), and the
+ *           table must be the same when weights are packed and when they are used;
+ *   mt      sub-tiles per tile (1, 2; 0 = heuristic);
+ *   ksplit  largest split-K cluster (2-8), 1 = never split, 0 = heuristic.
+ * unit_tile_table_set replaces the process-wide table (n = 0 clears it).  unit_b200/tune.py fills a
+ * table by timing the candidates over the reference's shape corpus. */
+typedef struct unit_tile_entry {
+  int32_t c_in, c_block, c_out, kh, kw, stride_h, stride_w;
+  int32_t n, h, w; /* n = 0: any input size (h, w ignored) */
+  int32_t bn, kc, mt, ksplit;
+} unit_tile_entry;
+int unit_tile_table_set(const unit_tile_entry *entries, int32_t n);
+
 /* Which kernel variant ran: the contraction kernel exists in one compiled variant per (operand
  * path, epilogue, data type, sub-tiles per tile).  unit_variant_count() is the size of the index
  * space; unit_variant_name(i) is NULL for indices without a compiled variant, otherwise a static

@@ -330,6 +330,33 @@ def test_conv3d_int8_bit_exact(U, oracle, n, c, d, h, w, co, k, s, p):
     U.device_status()
 
 
+def test_tile_table_overrides_keep_results(U, oracle):
+    """Every override a tile-table entry can carry (column-block width, stage depth, sub-tiles, split-K
+    limit) changes how the work is cut, never the result; the tuner's own bit-exactness check in small."""
+    from unit_b200 import ops, tile_table
+    rng = np.random.default_rng(404)
+    x = rng.integers(0, 256, (8, 16, 14, 14, 16), dtype=np.uint8)          # 3x3 256 -> 256 @14^2: splits by default
+    wt = rng.integers(-128, 128, (16, 16, 3, 3, 4, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 15, 2 ** 15, 256, dtype=np.int32)
+    want = oracle.conv2d_u8s8(x, wt, (1, 1), (1, 1), bias=b, requant_shift=8, vnni=oracle.host_has_vnni())
+    key = dict(c_in=256, c_block=16, c_out=256, kh=3, kw=3, stride_h=1, stride_w=1)
+    try:
+        for over in ({}, dict(bn=64), dict(bn=128, kc=4), dict(bn=256, kc=6), dict(mt=2), dict(mt=1, ksplit=1), dict(ksplit=2),
+                     dict(bn=128, ksplit=8)):
+            entries = []
+            if 'bn' in over or 'kc' in over:
+                entries.append(dict(key, n=0, bn=over.get('bn', 0), kc=over.get('kc', 0)))
+            entries.append(dict(key, n=8, h=14, w=14, mt=over.get('mt', 0), ksplit=over.get('ksplit', 0)))
+            tile_table.set_table(entries if over else [])
+            ops._PACK_CACHE.clear()
+            got = U.conv2d_NCHWc_int8(dev(x), dev(wt), padding=1, bias=dev(b), out_dtype='uint8')
+            U.device_status()
+            assert np.array_equal(got.cpu().numpy(), want), over
+    finally:
+        tile_table.set_table([])
+        ops._PACK_CACHE.clear()
+
+
 def test_zz_every_compiled_variant_was_launched(U):
     """Runs after the cases above (same module, definition order): no compiled variant is left
     that no parity case reaches."""

@@ -146,3 +146,42 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert line['cpu_baseline']['kind'] == 'port' and line['cpu_baseline']['cores'] >= 1
     assert line['e2e']['h2d_bytes_per_step'] == 0 and line['e2e']['value'] == line['value']
     assert line['config']['workload'] == 'resnet50-int8-conv-sweep'
+
+
+def test_tile_table_overrides_are_host_side_and_reversible():
+    """unit_tile_table_set: an entry for every input size changes the column-block width (visible in the
+    packed size, a pure host function); clearing the table restores the heuristic; bad entries are refused."""
+    import ctypes
+    from unit_b200 import _lib, build, tile_table
+    build.build()
+    L = _lib.lib()
+    d = _lib.ConvDesc(1, 64, 30, 30, 16, 80, 3, 3, 1, 1, 0, 0)
+    base = L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d))
+    assert base == 36 * 80 * 16                       # one column block of 80
+    key = dict(c_in=64, c_block=16, c_out=80, kh=3, kw=3, stride_h=1, stride_w=1)
+    tile_table.set_table([dict(key, n=0, bn=64)])
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == 36 * 96 * 16     # two blocks of 48
+    tile_table.set_table([dict(key, n=4, h=30, w=30, bn=64)])                        # size-specific: weights untouched
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == base
+    tile_table.set_table([])
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == base
+    bad = (_lib.TileEntry * 1)()
+    bad[0].c_in, bad[0].c_block, bad[0].c_out, bad[0].kh, bad[0].kw, bad[0].stride_h, bad[0].stride_w = 64, 16, 80, 3, 3, 1, 1
+    bad[0].bn = 40                                                                    # not a multiple of 16
+    assert L.unit_tile_table_set(bad, 1) == -2
+    assert L.unit_tile_table_set(bad, 5000) == -8
+    assert L.unit_tile_table_set(None, 0) == 0
+
+
+def test_shape_corpus_parser_and_committed_corpus():
+    from unit_b200 import tile_table
+    lines = ['(1, 4, 58, 58, 16) (4, 4, 3, 3, 4, 16, 4) (1, 1) /some/model.json',
+             '(1, 4, 58, 58, 16) (4, 4, 3, 3, 4, 16, 4) (1, 1)',
+             '(1, 512) (8, 128, 128, 4) dense /some/model.json',
+             '(1, 2, 56, 56, 12) (9, 2, 1, 1, 3, 16, 4) (1, 1)',          # channel block of 12: skipped
+             '(1, 16, 14, 14, 16) (32, 16, 1, 1, 4, 16, 4) (2, 2) x', 'noise']
+    shapes = tile_table.parse_shape_log(lines)
+    assert shapes == [dict(n=1, c_in=64, h=58, w=58, c_out=64, kh=3, kw=3, stride_h=1, stride_w=1, count=2),
+                      dict(n=1, c_in=256, h=14, w=14, c_out=512, kh=1, kw=1, stride_h=2, stride_w=2, count=1)]
+    corpus = tile_table.load_corpus()
+    assert len(corpus) >= 100 and all(s['c_in'] % 16 == 0 and s['c_out'] % 16 == 0 for s in corpus)

@@ -36,6 +36,12 @@ class Conv3dDesc(ctypes.Structure):
                  'pad_d', 'pad_h', 'pad_w')]
 
 
+class TileEntry(ctypes.Structure):
+    """Mirror of ``unit_tile_entry``."""
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ('c_in', 'c_block', 'c_out', 'kh', 'kw', 'stride_h', 'stride_w', 'n', 'h', 'w', 'bn', 'kc', 'mt', 'ksplit')]
+
+
 class Epilogue(ctypes.Structure):
     """Mirror of ``unit_epilogue``."""
     _fields_ = [('d_bias', ctypes.c_void_p), ('mul', ctypes.c_int32), ('shift', ctypes.c_int32),
@@ -61,6 +67,7 @@ SIGNATURES = {
     'unit_launch_count': (ctypes.c_uint64, []),
     'unit_trace_attach': (_ci, [_vp, _ci]),
     'unit_tensor_peak': (_ci, [_ci, _ci, _ci, _ci, ctypes.POINTER(ctypes.c_double), _vp]),
+    'unit_tile_table_set': (_ci, [ctypes.POINTER(TileEntry), _ci]),
     'unit_variant_count': (_ci, []),
     'unit_variant_name': (ctypes.c_char_p, [_ci]),
     'unit_variant_launches': (ctypes.c_uint64, [_ci]),

@@ -55,7 +55,7 @@ static int tuning_int(const char *name, int dflt) {
 // Depends on the weight tensor only (never on the batch), so packed weights stay valid
 // for every input size.  kc is chosen so that four stages of the larger (two sub-tile)
 // CTA tile fit in shared memory.
-static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense = false) {
+static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense = false, int table_bn = 0, int table_kc = 0) {
   TileCfg c;
   c.cols = cols;
   c.cols_pad = round_up(cols, 2);
@@ -70,8 +70,9 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
   }();
   // (cheap_a = false: the A operand comes through the slower im2col copies, where fetching it
   // once more per extra column block costs more than the overlap gains: stride-2 layers lost 35-45 %)
-  const int bn_max = forced_bn ? forced_bn
-                               : ((cheap_a && n_total >= 256 && c.cols_pad >= 8 && c.cols_pad <= 64) ? 128 : 256);
+  const int bn_max = table_bn ? table_bn
+                     : forced_bn ? forced_bn
+                                 : ((cheap_a && n_total >= 256 && c.cols_pad >= 8 && c.cols_pad <= 64) ? 128 : 256);
   c.n_tiles = (n_total + bn_max - 1) / bn_max;
   c.bn = round_up((n_total + c.n_tiles - 1) / c.n_tiles, 16);
   const int kc_max = (int)(kSmemBudget / 4 / (16 * (2 * kTileM + c.bn)));
@@ -82,7 +83,8 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
   }();
   c.kc = 0;
   const int kc_max2 = (int)(kSmemBudget / 2 / (16 * (2 * kTileM + c.bn)));  // two stages still fit
-  if (forced_kc && forced_kc <= kc_max2 && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
+  if (table_kc && table_kc <= kc_max2 && table_kc % 2 == 0) c.kc = table_kc;
+  if (c.kc == 0 && forced_kc && forced_kc <= kc_max2 && c.cols_pad % forced_kc == 0) c.kc = forced_kc;
   // plain matrices: stages of 8 columns = 128 bytes of K per row, the width of a swizzled operand
   // row, which lets the A tile arrive as full cache lines (three stages still fit)
   if (c.kc == 0 && dense && c.cols_pad % 8 == 0 && 8 <= (int)(kSmemBudget / 3 / (16 * (2 * kTileM + c.bn)))) c.kc = 8;
@@ -133,13 +135,52 @@ static int stages_for(const TileCfg &c, int mt, size_t *smem_bytes) {
   return s;
 }
 
+// ---------------------------------------------------------------------------
+// tile table: per-shape overrides of the tile heuristics (unit_tile_table_set)
+// ---------------------------------------------------------------------------
+constexpr int kMaxTileEntries = 1024;
+static unit_tile_entry g_tile_table[kMaxTileEntries];
+static int g_tile_entries = 0;
+static std::mutex g_tile_mu;
+
+// The entry for this convolution: weight-side fields must match; an entry with n = 0 applies to
+// every input size, one with n > 0 only to that (n, h, w).  Exact-size entries win.
+static bool tile_lookup(const unit_conv_desc *d, unit_tile_entry *out) {
+  std::lock_guard<std::mutex> lock(g_tile_mu);
+  const unit_tile_entry *any = nullptr;
+  for (int i = 0; i < g_tile_entries; ++i) {
+    const unit_tile_entry &e = g_tile_table[i];
+    if (e.c_in != d->c_in || e.c_block != d->c_block || e.c_out != d->c_out || e.kh != d->kh || e.kw != d->kw ||
+        e.stride_h != d->stride_h || e.stride_w != d->stride_w)
+      continue;
+    if (e.n == d->n && e.h == d->h && e.w == d->w) { *out = e; return true; }
+    if (e.n == 0 && any == nullptr) any = &e;
+  }
+  if (any) { *out = *any; return true; }
+  return false;
+}
+
 static int conv_cols_i8(const unit_conv_desc *d) {
   if (d->c_block == 16) return d->kh * d->kw * (d->c_in / 16);
   return (d->c_in / 4) * d->kh * ((d->kw + 3) / 4);
 }
 // stride-1 NCHW16c int8 convolutions fetch A with whole-row box copies
 static bool conv_a_is_cheap(const unit_conv_desc *d) { return d->c_block == 16 && d->stride_h == 1 && d->stride_w == 1; }
+
 static int conv_cols_f16(const unit_conv_desc *d) { return d->kh * d->kw * (d->c_in / 16) * 2; }
+
+static bool conv_a_is_cheap(const unit_conv_desc *d);
+// Tile shape of an int8 convolution's weights.  Only the weight-side fields of a table entry (bn, kc)
+// enter here, and only from entries that apply to every input size, so that packed weights stay valid
+// for any batch.
+static TileCfg conv_cfg_i8(const unit_conv_desc *d) {
+  unit_tile_entry e;
+  unit_conv_desc any = *d;
+  any.n = 0; any.h = 0; any.w = 0;
+  if (d->c_block == 16 && tile_lookup(&any, &e) && e.n == 0 && e.bn >= 16 && e.bn <= 256 && e.bn % 16 == 0)
+    return make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d), false, e.bn, e.kc);
+  return make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
+}
 
 static int check_conv(const unit_conv_desc *d, bool f16) {
   if (!d) return UNIT_ERR_NULL;
@@ -614,6 +655,7 @@ struct PlanImpl {
   int32_t variant, device;
   uint32_t grid, smem_bytes;
   uint32_t cluster;                  // > 1: thread-block cluster size (split-K)
+  int32_t table_mt, table_ksplit;    // from the tile table: 0 = heuristics (ksplit 1 = do not split)
   int32_t fold_n, fold_h2, fold_w2;  // fold_n > 0: the stem's 2 x 2 fold into scratch runs first
   const void *fold_src;
   void *fold_dst;
@@ -701,8 +743,9 @@ static int max_active_clusters(const TileCfg &c, int ks) {
 // distributed shared memory (integer sums do not depend on the order, so the int8 results stay
 // bit-exact; the reference splits its reductions too: python/tensorizer/ops/gpu.py:83-87,134,
 // poc/tensorcore/gemm-prefetch.cu:29-64).  Returns 1 when the problem should not be split.
-static int choose_ksplit(const TileCfg &c, long long m_total, int sms) {
-  static const int forced = tuning_int("UNIT_B200_KSPLIT", -1);
+static int choose_ksplit(const TileCfg &c, long long m_total, int sms, int table_ksplit = 0) {
+  static const int forced_env = tuning_int("UNIT_B200_KSPLIT", -1);
+  const int forced = table_ksplit > 0 ? table_ksplit : forced_env;  // a tile-table entry: 1 = never, n = at most n
   if (forced == 0 || forced == 1) return 1;
   const long long tiles = (m_total + kTileM - 1) / kTileM * c.n_tiles;
   if (tiles * 2 > sms || c.k_stages < 4) return 1;
@@ -765,10 +808,11 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
   const int sms = sm_count();
   pl.magic = kPlanMagic;
   if constexpr (MAX_MT >= 2) {
-    if (choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA) == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
+    const int mt = (pl.table_mt == 1 || pl.table_mt == 2) ? pl.table_mt : choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA);
+    if (mt == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
   if constexpr (a_mode_uses_tma(AMODE)) {
-    int ks = choose_ksplit(c, p.m_total, sms);
+    int ks = choose_ksplit(c, p.m_total, sms, pl.table_ksplit);
     // all clusters must be resident at once: a cluster needs its CTAs on SMs of one GPC, so fewer
     // clusters fit than SMs / size suggests (measured: 49 clusters of 3 ran in two rounds)
     const long long tiles1 = (p.m_total + kTileM - 1) / kTileM * c.n_tiles;
@@ -1158,8 +1202,15 @@ static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, co
   if (!e.out_u8 && (e.residual != nullptr || e.shift != 0)) return UNIT_ERR_SHAPE;
   if ((rc = check_arch())) return rc;
   const int epi = e.out_u8 ? (e.residual ? EPI_RES_NCHWC : EPI_REQ_NCHWC) : (e.mul != 1 ? EPI_MUL_NCHWC : EPI_RAW_NCHWC);
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
+  const TileCfg c = conv_cfg_i8(d);
   pl = PlanImpl{};
+  {
+    unit_tile_entry te;
+    if (d->c_block == 16 && tile_lookup(d, &te)) {
+      pl.table_mt = te.mt;
+      pl.table_ksplit = te.ksplit;
+    }
+  }
   IgemmParams &p = pl.p;
   p.a = static_cast<const uint8_t *>(x); p.b = static_cast<const uint8_t *>(pw); p.out = out; p.bias = e.bias; p.shift = e.shift;
   p.mul = e.mul; p.residual = e.residual; p.a_signed = e.x_signed ? 1 : 0;
@@ -1364,6 +1415,22 @@ int unit_tensor_peak(int32_t f16, int32_t n, int32_t issuers, int32_t iters, dou
   return run_tensor_peak(f16 != 0, n, issuers, iters, err, ops_per_second, static_cast<cudaStream_t>(stream));
 }
 
+int unit_tile_table_set(const unit_tile_entry *entries, int32_t n) {
+  if (n < 0 || n > kMaxTileEntries) return UNIT_ERR_TOO_LARGE;
+  if (n > 0 && !entries) return UNIT_ERR_NULL;
+  for (int i = 0; i < n; ++i) {
+    const unit_tile_entry &e = entries[i];
+    if (e.c_block != 16 || e.c_in < 16 || e.c_in % 16 || e.c_out < 16 || e.c_out % 16 || e.kh < 1 || e.kw < 1 || e.stride_h < 1 ||
+        e.stride_w < 1 || e.n < 0 || (e.bn != 0 && (e.bn < 16 || e.bn > 256 || e.bn % 16)) || e.kc < 0 || e.kc > 16 || e.kc % 2 ||
+        e.mt < 0 || e.mt > 2 || e.ksplit < 0 || e.ksplit > 8)
+      return UNIT_ERR_SHAPE;
+  }
+  std::lock_guard<std::mutex> lock(g_tile_mu);
+  for (int i = 0; i < n; ++i) g_tile_table[i] = entries[i];
+  g_tile_entries = n;
+  return UNIT_OK;
+}
+
 int unit_variant_count(void) { return kMaxVariants; }
 
 const char *unit_variant_name(int index) {
@@ -1393,7 +1460,7 @@ int unit_debug_set(int key, long long value) {
 // ---- packed weights --------------------------------------------------------
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
   if (check_conv(d, false)) return 0;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
+  const TileCfg c = conv_cfg_i8(d);
   size_t bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
   const StemFold f = stem_fold(d, false);
   if (f.ok) {  // second copy for the folded stride-1 form of a stride-2 stem
@@ -1413,7 +1480,7 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
   if (rc) return rc;
   if (!w || !packed) return UNIT_ERR_NULL;
   if (!aligned16(w) || !aligned16(packed)) return UNIT_ERR_ALIGN;
-  const TileCfg c = make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
+  const TileCfg c = conv_cfg_i8(d);
   PackParams pp{};
   pp.src = reinterpret_cast<const uint8_t *>(w);
   pp.dst = static_cast<uint4 *>(packed);

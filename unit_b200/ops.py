@@ -54,10 +54,19 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_TABLE_LOADED = False
+
+
 def _require_cuda_lib():
+    global _TABLE_LOADED
     if not torch.cuda.is_available():
         raise RuntimeError('unit_b200 operators need a CUDA device (sm_100a); there is no CPU fallback')
-    return _lib.lib()
+    L = _lib.lib()
+    if not _TABLE_LOADED:
+        _TABLE_LOADED = True
+        from . import tile_table
+        tile_table.load_default_table()   # per-shape tile overrides found by unit_b200.tune, if the file exists
+    return L
 
 
 def _to_device(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
@@ -111,7 +120,8 @@ _PACK_CACHE: dict = {}
 
 
 def _cached(src: torch.Tensor, key: tuple, make) -> PackedWeights:
-    k = (id(src), src.data_ptr(), src._version, key)
+    from . import tile_table
+    k = (id(src), src.data_ptr(), src._version, key, tile_table.version())   # the table shapes the packed form
     hit = _PACK_CACHE.get(k)
     if hit is not None and hit[0]() is src:
         return hit[1]
