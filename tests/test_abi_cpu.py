@@ -51,8 +51,10 @@ def desc(**kw):
 
 
 def test_packed_weight_sizes_are_pure_host_functions(L):
-    # 3x3 64->64: 36 K columns of 16 B, one 64-wide N tile
-    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc())) == 36 * 64 * 16
+    # 3x3 64->64: 36 K columns of 16 B, one 64-wide N tile; stride 1 with several taps and an even chunk
+    # count carries a second copy in the window form's column order (the same size)
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc())) == 2 * 36 * 64 * 16
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(stride_h=2, stride_w=2))) == 36 * 64 * 16
     # 1x1 512->2048: 32 columns, 8 N tiles of 256
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=512, c_out=2048, kh=1, kw=1))) == 32 * 2048 * 16
     # stem: 7 kh x 2 groups of 4 kw taps = 14 columns in one stage, plus the 16 columns of the folded form

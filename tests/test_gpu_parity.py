@@ -110,6 +110,14 @@ def test_vnni_known_answer_through_the_gpu(U):
     (6, 32, 31, 29, 80, 3, 3, 2, 1),      # im2col copies, odd sizes
     (4, 48, 33, 35, 64, 5, 5, 3, 2),      # stride 3
     (3, 80, 30, 30, 64, 1, 1, 2, 0),      # strided 1x1 with five chunks
+    # window form (stride 1, several taps, even chunk count, enough tiles): ragged widths and heights,
+    # rectangular kernels, valid and padded, wide column blocks, tiles that end inside an image
+    (10, 32, 61, 47, 48, 3, 3, 1, 1),
+    (6, 64, 50, 90, 320, 3, 3, 1, 1),
+    (16, 32, 40, 40, 32, 1, 3, 1, 0),
+    (16, 32, 40, 40, 32, 3, 1, 1, 1),
+    (20, 64, 33, 35, 64, 2, 2, 1, 0),
+    (12, 32, 70, 110, 16, 3, 3, 1, 1),
 ])
 def test_conv_int8_bit_exact(U, oracle, n, ci, h, w, co, kh, kw, s, p):
     rng = np.random.default_rng(hash((n, ci, h, w, co, kh, kw, s, p)) % 2 ** 32)

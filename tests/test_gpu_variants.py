@@ -59,6 +59,10 @@ INT8_CASES = {
     'gather_mt2': (32, 16, 225, 225, 16, 1, 9, 0, 16),
     'stem_gather_mt1': (2, 4, 33, 35, 32, 7, 2, 3, 4),
     'stem_gather_mt2': (8, 4, 227, 227, 16, 3, 2, 1, 4),
+    # stride 1, 3x3, even chunk count, wide images, enough tiles: the window form (rows copied once per chunk,
+    # every tap a shifted window); one and two sub-tiles per tile
+    'win_mt1': (8, 32, 56, 56, 32, 3, 1, 1, 16),
+    'win_mt2': (24, 32, 56, 56, 16, 3, 1, 1, 16),
     # few tiles and a long reduction: split-K over a thread-block cluster
     'box_splitk': (1, 256, 24, 24, 256, 3, 1, 1, 16),
     'im2col_splitk': (1, 256, 24, 24, 256, 3, 2, 1, 16),
@@ -68,6 +72,7 @@ INT8_VARIANTS = {
     'im2col_mt1': 'A_CONV_TMA, {}, i8, MT=1', 'im2col_mt2': 'A_CONV_TMA, {}, i8, MT=2',
     'gather_mt1': 'A_CONV_I8, {}, i8, MT=1', 'gather_mt2': 'A_CONV_I8, {}, i8, MT=2',
     'stem_gather_mt1': 'A_STEM_I8, {}, i8, MT=1', 'stem_gather_mt2': 'A_STEM_I8, {}, i8, MT=2',
+    'win_mt1': 'A_CONV_WIN, {}, i8, MT=1', 'win_mt2': 'A_CONV_WIN, {}, i8, MT=2',
     'box_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K', 'im2col_splitk': 'A_CONV_TMA, {}, i8, MT=1, split-K',
 }
 

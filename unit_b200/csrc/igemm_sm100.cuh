@@ -71,9 +71,14 @@ enum AMode : int {
   A_CONV_TMA = 4,  // NCHW16c (u8 or fp16) fetched by im2col-mode TMA: one bulk tensor copy per K column
   A_CONV_BOX = 5,  // u8 NCHW16c, stride 1: each sub-tile is a box of (images x output rows x
                    // row segment) fetched by tiled-mode TMA, whole pixel rows at a time
-  A_DENSE_TMA = 6  // plain row-major matrix fetched by tiled-mode TMA: one copy = 128 rows x 16 bytes
+  A_DENSE_TMA = 6, // plain row-major matrix fetched by tiled-mode TMA: one copy = 128 rows x 16 bytes
+  A_CONV_WIN = 7   // u8 NCHW16c, stride 1, kernels larger than 1x1: a tile is a run of consecutive positions of
+                   // the zero-padded image; the rows it touches are copied ONCE per channel chunk and every tap
+                   // of the kernel reads them as a shifted window (see the kernel)
 };
-__host__ __device__ constexpr bool a_mode_uses_tma(int m) { return m == A_CONV_TMA || m == A_CONV_BOX || m == A_DENSE_TMA; }
+__host__ __device__ constexpr bool a_mode_uses_tma(int m) {
+  return m == A_CONV_TMA || m == A_CONV_BOX || m == A_DENSE_TMA || m == A_CONV_WIN;
+}
 enum EpiMode : int {
   EPI_RAW_NCHWC = 0,  // 32-bit accumulator (+ s32 bias) -> [n][oc/16][oh][ow][16]
   EPI_REQ_NCHWC = 1,  // + bias, round-shift, clamp -> u8 [n][oc/16][oh][ow][16]
@@ -155,6 +160,14 @@ struct IgemmParams {
   // share one tile; CTA `rank` accumulates pipeline stages [rank * ks_per, (rank + 1) * ks_per) and the
   // partial accumulators are exchanged through distributed shared memory (see the kernel)
   int ksplit, ks_per;
+  // A_CONV_WIN.  Positions q = oh * win_wp + ow' run over the padded width win_wp = W + 2 pw (the last
+  // KW - 1 positions of a row are not outputs); a tile is MT x 128 consecutive positions of one image
+  // (win_tpi tiles per image).  For one channel chunk the tile's operand for tap (kh, kw) is the 16-byte
+  // pixels q + kh * win_wp + kw of the padded image, so one box copy of win_rows rows of win_wp pixels
+  // (zero fill outside the image) serves all taps.  A pipeline stage holds the windows of two chunks
+  // (win_bytes each); an MMA K step pairs the same tap of both chunks.
+  int win_wp, win_rows, win_bytes, win_tpi;
+  FastDiv div_wp, div_tpi;
   // Convolution in three dimensions (one image, [c/16][D][H][W][16]): the depth axis takes the place of
   // the image axis of the two-dimensional kernel (a 128-row tile then runs over (od, oh, ow)), kernel
   // depth KD adds a third tap index, and the output strides below place (od, channel group).
@@ -695,15 +708,17 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
 template <int AMODE, int EPI, bool F16, int MT, bool SPLITK = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
-  static_assert(!SPLITK || (MT == 1 && a_mode_uses_tma(AMODE)), "split-K: single sub-tiles, tensor-copy-fed A operand");
+  static_assert(!SPLITK || (MT == 1 && a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN),
+                "split-K: single sub-tiles, tensor-copy-fed A operand, not the window form");
   extern __shared__ __align__(1024) uint8_t smem[];  // (1 KB: a swizzled operand atom is 8 rows x 128 bytes)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   trace_mark_ns(p, 8);
 
   constexpr uint32_t kSubBytes = kTileM * 16u;                       // one K column of one 128-row sub-tile
-  const uint32_t a_sub_bytes = (uint32_t)p.kc * kSubBytes;           // one sub-tile of one stage
-  const uint32_t a_stage_bytes = (uint32_t)MT * a_sub_bytes;
+  // (window form: a stage's A part is the two chunk windows; the sub-tiles are 128-row slices of them)
+  const uint32_t a_sub_bytes = AMODE == A_CONV_WIN ? kSubBytes : (uint32_t)p.kc * kSubBytes;  // one sub-tile of one stage
+  const uint32_t a_stage_bytes = AMODE == A_CONV_WIN ? 2u * (uint32_t)p.win_bytes : (uint32_t)MT * a_sub_bytes;
   const uint32_t b_stage_bytes = (uint32_t)p.kc * (uint32_t)p.bn * 16u;
   const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
   PipeShared *ps = reinterpret_cast<PipeShared *>(smem + (size_t)p.stages * stage_bytes + kFoldBytes);
@@ -915,6 +930,27 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     bool alive = true;
     for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
       const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
+      if constexpr (AMODE == A_CONV_WIN) {
+        // two box copies per stage (one per channel chunk), issued by lane 0 of the first two producer warps
+        const uint32_t img = fast_div((uint32_t)m_tile, p.div_tpi);
+        const uint32_t q0 = ((uint32_t)m_tile - img * (uint32_t)p.win_tpi) * (uint32_t)(kTileM * MT);
+        const int y0 = (int)fast_div(q0, p.div_wp) - p.ph;
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
+          if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
+            alive = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&ps->full[s]);
+          if (tx_poster) mbar_arrive_expect_tx(bar, 2u * (uint32_t)p.win_bytes);
+          __syncwarp();
+          if (lane == 0 && copy_id < 2)
+            tma_tile_4d(smem_base + s * stage_bytes + (uint32_t)copy_id * (uint32_t)p.win_bytes, &tmap, -2 * p.pw, y0,
+                        2 * ks + copy_id, (int)img, bar);
+          if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
+        }
+        if (tx_poster) trace_mark(p, lt, 1);
+        continue;
+      }
       // origin of this lane's sub-tile
       int c0 = 0, c1 = 0, c2 = 0;  // BOX: x (8-byte units), y, first image; TMA: w, h, image
       bool sub_ok = true;
@@ -1090,6 +1126,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (my_t == 0u) trace_mark(p, lt, 3);
         const uint32_t d_tmem = tmem_base + (slot * (uint32_t)MT + my_t) * (uint32_t)p.bn;  // this thread's accumulator
         uint32_t started = 0u;
+        uint32_t win_off0 = 0u;  // window form: this sub-tile's first position inside the stage's windows
+        if constexpr (AMODE == A_CONV_WIN) {
+          const uint32_t m_t = fast_div((uint32_t)tile, p.div_n_tiles);
+          const uint32_t img = fast_div(m_t, p.div_tpi);
+          const uint32_t q0 = (m_t - img * (uint32_t)p.win_tpi) * (uint32_t)(kTileM * MT);
+          win_off0 = q0 - fast_div(q0, p.div_wp) * (uint32_t)p.win_wp + my_t * (uint32_t)kTileM;
+        }
+        const uint64_t a_desc_win = make_smem_desc(0u, (uint32_t)p.win_bytes, 128u);
         for (int ks = ks_begin; ks < ks_end; ++ks) {
           if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull)) {
             alive = false;
@@ -1102,7 +1146,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint32_t a_enc = stage_enc + my_t * a_sub_enc;  // this thread's sub-tile of the stage
           const uint32_t b_enc = stage_enc + (a_stage_bytes >> 4);
           const int nk = (ks == p.k_stages - 1) ? p.last_ksteps : (p.kc >> 1);
-          if (AMODE == A_DENSE_TMA && p.a_sw128 != 0) {
+          if constexpr (AMODE == A_CONV_WIN) {
+            // K step = one tap of the two chunks of this stage: both columns are the tile's 128 positions
+            // shifted by the tap, win_bytes apart (the second chunk's window)
+            int kh = 0, kw = 0;
+            for (int k = 0; k < nk; ++k) {
+              const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
+              const uint64_t adesc = a_desc_win | (uint64_t)(stage_enc + win_off0 + (uint32_t)(kh * p.win_wp + kw));
+              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              started = 1u;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
+          } else if (AMODE == A_DENSE_TMA && p.a_sw128 != 0) {
             // swizzled A: K step k is 32 bytes further inside its 128-byte atom; atoms are 16 KB apart
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
@@ -1225,6 +1280,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const int n_i = (int)nb * p.box_n + (int)dn, oh = (int)hb * p.box_h + (int)dh, ow = (int)wb * p.box_w + (int)dw;
         mvalid = st < p.sub_tiles && (int)dn < p.box_n && n_i < p.n_img && oh < p.OH && ow < p.OW;
         obase = ((long long)n_i * p.out_img_stride + (long long)n_tile * (p.bn >> 4) * p.out_grp_stride + (long long)oh * p.OW + ow) * 16;
+      } else if constexpr (AMODE == A_CONV_WIN) {
+        // row -> position of the padded image -> (oh, ow); the last KW - 1 positions of a row are no outputs
+        const uint32_t img = fast_div((uint32_t)m_tile, p.div_tpi);
+        const uint32_t q = ((uint32_t)m_tile - img * (uint32_t)p.win_tpi) * (uint32_t)(kTileM * MT) + (uint32_t)sub * kTileM + r;
+        const uint32_t oh = fast_div(q, p.div_wp);
+        const uint32_t ow = q - oh * (uint32_t)p.win_wp;
+        mvalid = (int)ow < p.OW && (int)oh < p.OH && (int)img < p.n_img;
+        obase = ((long long)img * p.out_img_stride + (long long)n_tile * (p.bn >> 4) * p.out_grp_stride + (long long)oh * p.OW + ow) * 16;
       } else if constexpr (EPI == EPI_RAW_ROWS) {
         obase = m * p.ldc + (long long)n_tile * p.bn;
       } else {

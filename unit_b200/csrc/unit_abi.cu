@@ -33,6 +33,7 @@ static std::atomic<int> g_trace_cap{0};
 struct TileCfg {
   int bn = 0, kc = 0, cols = 0, cols_pad = 0, k_stages = 0, last_ksteps = 0, n_tiles = 0;
   size_t b_stage_bytes = 0;
+  size_t a_stage_bytes = 0;  // window form: bytes of a stage's A part (0: kc columns x 128 rows per sub-tile)
 };
 
 constexpr size_t kSmemBudget = 200 * 1024;
@@ -127,7 +128,7 @@ static int choose_mt(const TileCfg &c, long long m_total, int sms, bool slow_a) 
 }
 
 static int stages_for(const TileCfg &c, int mt, size_t *smem_bytes) {
-  const size_t stage = (size_t)c.kc * 16 * ((size_t)mt * kTileM + c.bn);
+  const size_t stage = c.a_stage_bytes ? c.a_stage_bytes + c.b_stage_bytes : (size_t)c.kc * 16 * ((size_t)mt * kTileM + c.bn);
   int s = (int)(kSmemBudget / stage);
   if (s > kMaxStages) s = kMaxStages;
   if (s < 2) s = 2;
@@ -182,6 +183,47 @@ static TileCfg conv_cfg_i8(const unit_conv_desc *d) {
   return make_cfg(d->c_out, conv_cols_i8(d), conv_a_is_cheap(d));
 }
 
+// ---- window form (A_CONV_WIN) ----
+// Weight-side eligibility: u8 NCHW16c, stride 1, kernels of 2 to 9 taps, an even number of channel chunks.
+static bool win_weights_ok(const unit_conv_desc *d) {
+  static const int enabled = tuning_int("UNIT_B200_WIN", 1);
+  const int taps = d->kh * d->kw;
+  return enabled && d->c_block == 16 && d->stride_h == 1 && d->stride_w == 1 && taps >= 2 && taps <= 9 && (d->c_in / 16) % 2 == 0;
+}
+// Tile shape of the window-form copy of the weights: same column blocks as the generic form, one
+// stage per pair of chunks with 2 x taps columns.
+static TileCfg win_cfg(const unit_conv_desc *d) {
+  TileCfg c = conv_cfg_i8(d);
+  const int taps = d->kh * d->kw;
+  c.kc = 2 * taps;
+  c.cols_pad = c.cols;
+  c.k_stages = (d->c_in / 16) / 2;
+  c.last_ksteps = taps;
+  c.b_stage_bytes = (size_t)c.kc * c.bn * 16;
+  return c;
+}
+struct WinGeom {
+  bool ok = false;
+  int mt = 0, wp = 0, rows = 0, bytes = 0, tpi = 0;
+};
+// Input-side geometry for `mt` sub-tiles per tile; ok only if enough of the computed positions are outputs
+// (the padded columns and the ragged last tile of every image are not) and the stage ring holds two stages.
+static WinGeom win_geom(const unit_conv_desc *d, int mt, const TileCfg &wc) {
+  WinGeom g;
+  if (!win_weights_ok(d)) return g;
+  const int oh = d->h + 2 * d->pad_h - d->kh + 1, ow = d->w + 2 * d->pad_w - d->kw + 1;
+  g.mt = mt;
+  g.wp = d->w + 2 * d->pad_w;
+  const int span = kTileM * mt;
+  g.tpi = (oh * g.wp + span - 1) / span;
+  g.rows = (g.wp - 1 + span + (d->kh - 1) * g.wp + (d->kw - 1) + g.wp - 1) / g.wp;
+  g.bytes = g.rows * g.wp * 16;
+  const double eff = (double)oh * ow / ((double)g.tpi * span);
+  const size_t stage = 2 * (size_t)g.bytes + wc.b_stage_bytes;
+  g.ok = g.wp * 2 <= 256 && g.rows <= 256 && eff >= 0.85 && 2 * stage <= kSmemBudget;
+  return g;
+}
+
 static int check_conv(const unit_conv_desc *d, bool f16) {
   if (!d) return UNIT_ERR_NULL;
   if (d->n < 1 || d->c_in < 1 || d->h < 1 || d->w < 1 || d->c_out < 1 || d->kh < 1 || d->kw < 1 ||
@@ -229,7 +271,7 @@ static int sm_count() {
 // ---------------------------------------------------------------------------
 // weight packing: reference layouts -> [n_tile][k_stage][kc][bn][16 B] blocks
 // ---------------------------------------------------------------------------
-enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4, PACK_STEM_S2D = 5 };
+enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4, PACK_STEM_S2D = 5, PACK_CONV_WIN = 6 };
 
 struct PackParams {
   const uint8_t *src;
@@ -258,6 +300,12 @@ __global__ void pack_weights_kernel(const PackParams p) {
         const int tap = j / p.Cc, ci = j % p.Cc;
         const int kh = tap / p.KW, kw = tap % p.KW;
         // [oc/16][ci][kh][kw][m][oc%16][r]
+        const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15) * 4;
+        for (int m = 0; m < 4; ++m) w[m] = *reinterpret_cast<const uint32_t *>(s + m * 64);
+      } else if (p.mode == PACK_CONV_WIN) {
+        // window form: stage = pair of channel chunks; within it, columns (tap, chunk 2 ks) and (tap, chunk 2 ks + 1)
+        const int tap = jj >> 1, ci = 2 * ks + (jj & 1);
+        const int kh = tap / p.KW, kw = tap % p.KW;
         const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15) * 4;
         for (int m = 0; m < 4; ++m) w[m] = *reinterpret_cast<const uint32_t *>(s + m * 64);
       } else if (p.mode == PACK_STEM_I8) {
@@ -611,7 +659,7 @@ static bool use_fold() {
 // ---------------------------------------------------------------------------
 // kernel variants: one slot per instantiated igemm_kernel<AMODE, EPI, F16, MT>
 // ---------------------------------------------------------------------------
-constexpr int kNumAModes = 7, kNumEpis = 5;
+constexpr int kNumAModes = 8, kNumEpis = 5;
 constexpr int kMaxVariants = kNumAModes * kNumEpis * 2 * 2 * 2;
 struct VariantSlot {
   char name[72];
@@ -624,7 +672,7 @@ static VariantSlot *variant_table() {
   return table;
 }
 static bool register_variant(int index, int amode, int epi, bool f16, int mt, bool splitk) {
-  static const char *const amodes[kNumAModes] = {"A_CONV_I8", "A_CONV_F16", "A_STEM_I8", "A_DENSE", "A_CONV_TMA", "A_CONV_BOX", "A_DENSE_TMA"};
+  static const char *const amodes[kNumAModes] = {"A_CONV_I8", "A_CONV_F16", "A_STEM_I8", "A_DENSE", "A_CONV_TMA", "A_CONV_BOX", "A_DENSE_TMA", "A_CONV_WIN"};
   static const char *const epis[kNumEpis] = {"EPI_RAW_NCHWC", "EPI_REQ_NCHWC", "EPI_RAW_ROWS", "EPI_MUL_NCHWC", "EPI_RES_NCHWC"};
   VariantSlot &v = variant_table()[index];
   snprintf(v.name, sizeof(v.name), "igemm_kernel<%s, %s, %s, MT=%d%s>", amodes[amode], epis[epi], f16 ? "f16" : "i8", mt,
@@ -811,7 +859,7 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
     const int mt = (pl.table_mt == 1 || pl.table_mt == 2) ? pl.table_mt : choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA);
     if (mt == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
-  if constexpr (a_mode_uses_tma(AMODE)) {
+  if constexpr (a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN) {  // (the window form is used on full grids only)
     int ks = choose_ksplit(c, p.m_total, sms, pl.table_ksplit);
     // all clusters must be resident at once: a cluster needs its CTAs on SMs of one GPC, so fewer
     // clusters fit than SMs / size suggests (measured: 49 clusters of 3 ran in two rounds)
@@ -1218,6 +1266,32 @@ static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, co
   p.acc_bound = 255ll * 128ll * d->c_in * d->kh * d->kw;
   CUtensorMap map;
   if (d->c_block == 16) {
+    if (use_tma() && win_weights_ok(d) && pl.table_mt == 0) {
+      // stride 1, kernels of several taps: window form when its tiling of the padded image wastes little.
+      // Two sub-tiles per tile if that still fills the SMs, else one; grids too small for either go on
+      // to the box form below (which can split the reduction).
+      const TileCfg wc = win_cfg(d);
+      const int sms = sm_count();
+      for (int mt = 2; mt >= 1; --mt) {
+        const WinGeom g = win_geom(d, mt, wc);
+        const long long tiles = (long long)d->n * g.tpi * wc.n_tiles;
+        if (!g.ok || tiles < (mt == 2 ? 2 : 1) * (long long)sms) continue;
+        BoxGeom bg{};
+        bg.bw = g.wp; bg.bh = g.rows; bg.bn = 1;
+        if (!make_box_map(&map, d->n, d->c_in, d->h, d->w, x, bg)) break;
+        p.b = static_cast<const uint8_t *>(pw) + (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;  // the second packed copy
+        p.win_wp = g.wp; p.win_rows = g.rows; p.win_bytes = g.bytes; p.win_tpi = g.tpi;
+        p.div_wp = make_fast_div((uint32_t)g.wp);
+        p.div_tpi = make_fast_div((uint32_t)g.tpi);
+        p.n_img = d->n;
+        p.m_total = (long long)d->n * g.tpi * kTileM * mt;
+        pl.table_mt = mt;
+        pl.table_ksplit = 1;
+        TileCfg wcm = wc;
+        wcm.a_stage_bytes = 2 * (size_t)g.bytes;
+        return prepare_conv_i8<A_CONV_WIN>(pl, wcm, epi, &map);
+      }
+    }
     if (use_tma() && d->stride_h == 1 && d->stride_w == 1) {
       // stride 1: whole pixel rows per copy
       const BoxGeom g = choose_box(d->n, p.OH, p.OW);
@@ -1462,6 +1536,10 @@ size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
   if (check_conv(d, false)) return 0;
   const TileCfg c = conv_cfg_i8(d);
   size_t bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;
+  if (win_weights_ok(d)) {  // second copy in the window form's column order
+    const TileCfg wc = win_cfg(d);
+    bytes += (size_t)wc.n_tiles * wc.k_stages * wc.b_stage_bytes;
+  }
   const StemFold f = stem_fold(d, false);
   if (f.ok) {  // second copy for the folded stride-1 form of a stride-2 stem
     const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
@@ -1488,6 +1566,14 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
   pp.n_total = d->c_out; pp.bn = c.bn; pp.kc = c.kc; pp.cols = c.cols; pp.k_stages = c.k_stages; pp.n_tiles = c.n_tiles;
   pp.Cc = d->c_in / d->c_block; pp.KH = d->kh; pp.KW = d->kw; pp.kwg = (d->kw + 3) / 4;
   rc = launch_pack(pp, static_cast<cudaStream_t>(stream));
+  if (rc == UNIT_OK && win_weights_ok(d)) {
+    const TileCfg wc = win_cfg(d);
+    PackParams pwn = pp;
+    pwn.dst = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(packed) + (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes);
+    pwn.mode = PACK_CONV_WIN;
+    pwn.bn = wc.bn; pwn.kc = wc.kc; pwn.cols = wc.cols; pwn.k_stages = wc.k_stages; pwn.n_tiles = wc.n_tiles;
+    rc = launch_pack(pwn, static_cast<cudaStream_t>(stream));
+  }
   const StemFold f = stem_fold(d, false);
   if (rc == UNIT_OK && f.ok) {
     const size_t generic_bytes = (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;

@@ -49,12 +49,12 @@ def _time_case(x_sets, w, stride, pad=0, reps=16):
     return a.elapsed_time(b) * 1e3 / (3 * reps * len(plans)), plans[0].out.clone()
 
 
-def candidates(shape):
+def candidates(shape, weight_side=True):
     c_out = shape['c_out']
     bns = sorted({min(256, (c_out + 15) // 16 * 16), 128, 64} & set(range(16, 257, 16)))
     bns = [b for b in bns if b <= max(64, (c_out + 15) // 16 * 16)]
     out = []
-    for bn in bns + [0]:
+    for bn in (bns if weight_side else []) + [0]:
         for mt in (0, 1, 2):
             for ks in (0, 1, 4, 8):
                 if bn == 0 and mt == 0 and ks == 0:
@@ -63,7 +63,7 @@ def candidates(shape):
     return out
 
 
-def tune_shape(shape, batch, sets=4):
+def tune_shape(shape, batch, sets=4, weight_side=True):
     dev = torch.device('cuda')
     g = torch.Generator(device=dev).manual_seed(shape['c_in'] * 131 + shape['c_out'])
     cc = shape['c_in'] // 16
@@ -78,7 +78,7 @@ def tune_shape(shape, batch, sets=4):
     key = {k: shape[k] for k in ('c_in', 'c_out', 'kh', 'kw', 'stride_h', 'stride_w')}
     key['c_block'] = 16
     best = (base_us, None)
-    for cand in candidates(shape):
+    for cand in candidates(shape, weight_side):
         # the weight-side fields (bn, kc) must sit in an entry for every input size; mt / ksplit in one for this size
         entries = []
         if cand['bn'] or cand['kc']:
@@ -106,6 +106,9 @@ def main(argv=None) -> int:
     ap.add_argument('--only-resnet50', action='store_true', help='the ResNet-50 sweep shapes alone')
     ap.add_argument('--out', default=tile_table.TABLE_PATH)
     ap.add_argument('--min-gain', type=float, default=0.03)
+    ap.add_argument('--size-specific-only', action='store_true',
+                    help='only overrides bound to one input size (sub-tiles, split-K): packed weights keep their shape')
+    ap.add_argument('--merge', default=None, help='an existing table whose entries are kept (new entries for the same key win)')
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit('the tuner needs a B200')
@@ -122,7 +125,9 @@ def main(argv=None) -> int:
     t0 = time.time()
     for i, sh in enumerate(shapes):
         for b in batches:
-            base_us, (best_us, best_entries) = tune_shape(sh, b)
+            # shapes of the ResNet-50 sweep run at many batch sizes: their weight-side choice stays with the heuristic
+            in_sweep = any(l.c_in == sh['c_in'] and l.c_out == sh['c_out'] and l.k == sh['kh'] and l.stride == sh['stride_h'] for l in LAYERS)
+            base_us, (best_us, best_entries) = tune_shape(sh, b, weight_side=not (args.size_specific_only or in_sweep))
             gain = base_us / best_us - 1.0
             row = {'shape': {k: sh[k] for k in sh if k != 'count'}, 'batch': b, 'default_us': round(base_us, 2),
                    'best_us': round(best_us, 2), 'gain': round(gain, 3)}
@@ -137,9 +142,20 @@ def main(argv=None) -> int:
             report.append(row)
         if (i + 1) % 10 == 0:
             print(f'[tune] {i + 1}/{len(shapes)} shapes, {len(entries)} entries, {time.time() - t0:.0f} s', file=sys.stderr, flush=True)
-    with open(args.out, 'w') as f:
-        json.dump({'device': torch.cuda.get_device_name(0), 'min_gain': args.min_gain, 'entries': entries, 'report': report}, f, indent=0)
+    if args.merge:
+        with open(args.merge) as f:
+            old = json.load(f).get('entries', [])
+        keyf = lambda e: tuple(e.get(k, 0) for k in ('c_in', 'c_out', 'kh', 'kw', 'stride_h', 'stride_w', 'n', 'h', 'w'))
+        new_keys = {keyf(e) for e in entries}
+        entries = [e for e in old if keyf(e) not in new_keys] + entries
     gains = [r['gain'] for r in report]
+    with open(args.out, 'w') as f:
+        json.dump({'device': torch.cuda.get_device_name(0), 'min_gain': args.min_gain,
+                   'summary': {'cases': len(report), 'mean_gain': sum(gains) / max(1, len(gains)), 'max_gain': max(gains) if gains else 0.0,
+                               'default_us': sum(r['default_us'] for r in report), 'best_us': sum(r['best_us'] for r in report)},
+                   'entries': entries}, f, indent=0)
+    with open(args.out + '.report.json', 'w') as f:
+        json.dump(report, f, indent=0)
     print(json.dumps({'shapes': len(shapes), 'cases': len(report), 'entries': len(entries),
                       'mean_gain': sum(gains) / max(1, len(gains)), 'max_gain': max(gains) if gains else 0.0, 'out': args.out}))
     return 0
