@@ -166,7 +166,8 @@ struct IgemmParams {
   // pixels q + kh * win_wp + kw of the padded image, so one box copy of win_rows rows of win_wp pixels
   // (zero fill outside the image) serves all taps.  A pipeline stage holds the windows of two chunks
   // (win_bytes each); an MMA K step pairs the same tap of both chunks.
-  int win_wp, win_rows, win_bytes, win_tpi;
+  int win_wp, win_rows, win_bytes, win_tpi;  // win_bytes: distance between the two windows of a stage (a multiple of 128)
+  int win_box_bytes;                         // bytes one window copy delivers: win_rows * win_wp * 16
   FastDiv div_wp, div_tpi;
   // Convolution in three dimensions (one image, [c/16][D][H][W][16]): the depth axis takes the place of
   // the image axis of the two-dimensional kernel (a 128-row tile then runs over (od, oh, ow)), kernel
@@ -941,7 +942,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             break;
           }
           const uint32_t bar = smem_u32(&ps->full[s]);
-          if (tx_poster) mbar_arrive_expect_tx(bar, 2u * (uint32_t)p.win_bytes);
+          if (tx_poster) mbar_arrive_expect_tx(bar, 2u * (uint32_t)p.win_box_bytes);
           __syncwarp();
           if (lane == 0 && copy_id < 2)
             tma_tile_4d(smem_base + s * stage_bytes + (uint32_t)copy_id * (uint32_t)p.win_bytes, &tmap, -2 * p.pw, y0,

@@ -204,7 +204,7 @@ static TileCfg win_cfg(const unit_conv_desc *d) {
 }
 struct WinGeom {
   bool ok = false;
-  int mt = 0, wp = 0, rows = 0, bytes = 0, tpi = 0;
+  int mt = 0, wp = 0, rows = 0, bytes = 0, box_bytes = 0, tpi = 0;
 };
 // Input-side geometry for `mt` sub-tiles per tile; ok only if enough of the computed positions are outputs
 // (the padded columns and the ragged last tile of every image are not) and the stage ring holds two stages.
@@ -217,10 +217,13 @@ static WinGeom win_geom(const unit_conv_desc *d, int mt, const TileCfg &wc) {
   const int span = kTileM * mt;
   g.tpi = (oh * g.wp + span - 1) / span;
   g.rows = (g.wp - 1 + span + (d->kh - 1) * g.wp + (d->kw - 1) + g.wp - 1) / g.wp;
-  g.bytes = g.rows * g.wp * 16;
+  g.box_bytes = g.rows * g.wp * 16;
+  g.bytes = round_up(g.box_bytes, 128);  // a tensor copy's destination in shared memory must be 128-byte aligned
   const double eff = (double)oh * ow / ((double)g.tpi * span);
   const size_t stage = 2 * (size_t)g.bytes + wc.b_stage_bytes;
-  g.ok = g.wp * 2 <= 256 && g.rows <= 256 && eff >= 0.85 && 2 * stage <= kSmemBudget;
+  // a single sub-tile per tile re-reads the weights for every 128 positions: only where they are small
+  const bool weights_small = mt == 2 || (size_t)wc.k_stages * wc.b_stage_bytes <= (64u << 10);
+  g.ok = g.wp * 2 <= 256 && g.rows <= 256 && eff >= 0.85 && 2 * stage <= kSmemBudget && weights_small;
   return g;
 }
 
@@ -1280,7 +1283,7 @@ static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, co
         bg.bw = g.wp; bg.bh = g.rows; bg.bn = 1;
         if (!make_box_map(&map, d->n, d->c_in, d->h, d->w, x, bg)) break;
         p.b = static_cast<const uint8_t *>(pw) + (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;  // the second packed copy
-        p.win_wp = g.wp; p.win_rows = g.rows; p.win_bytes = g.bytes; p.win_tpi = g.tpi;
+        p.win_wp = g.wp; p.win_rows = g.rows; p.win_bytes = g.bytes; p.win_box_bytes = g.box_bytes; p.win_tpi = g.tpi;
         p.div_wp = make_fast_div((uint32_t)g.wp);
         p.div_tpi = make_fast_div((uint32_t)g.tpi);
         p.n_img = d->n;
