@@ -297,20 +297,35 @@ def build_instances(torch, U, R, dev, layer_set, batch, rank, config=5):
     return instances, per_layer
 
 
-def capture_graph(torch, U, fn, warm: int = 1):
+def capture_graph(torch, U, fn, warm: int = 1, branches=None):
     """Captures fn() (library launches on the current stream) into a CUDA graph; returns
     (graph, launches per replay).  fn runs once on the capture stream first (one-off set-up of the
-    library and of the operators' per-stream scratch must not fall inside a capture)."""
+    library and of the operators' per-stream scratch must not fall inside a capture).
+    `branches`: a list of callables instead of fn, captured as parallel branches of the graph (work
+    without data dependencies between the branches)."""
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
+
+    def body():
+        if not branches:
+            fn()
+            return
+        streams = [torch.cuda.Stream() for _ in branches]
+        for st, work in zip(streams, branches):
+            st.wait_stream(side)
+            with torch.cuda.stream(st):
+                work()
+        for st in streams:
+            side.wait_stream(st)
+
     with torch.cuda.stream(side):
-        fn()
+        body()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     c0 = U.launch_count()
     with torch.cuda.graph(graph, stream=side):
-        fn()
+        body()
     n = U.launch_count() - c0
     for _ in range(warm):
         graph.replay()
@@ -509,9 +524,17 @@ def run_unit(args):
     # the host's per-call work is not what is measured.
     graph = None
     launches_per_step = None
+    n_branches = max(1, args.branches)
     if not args.no_graph and not args.kernels_only:
         try:
-            graph, launches_per_step = capture_graph(torch, U, step, warm=args.warmup)
+            branches = None
+            if n_branches > 1:
+                # the step's convolutions are independent of one another (own buffers each): deal them to
+                # parallel branches of the graph, so that one kernel's launch, prologue and tail overlap
+                # another's main loop
+                lanes = [instances[k::n_branches] for k in range(n_branches)]
+                branches = [(lambda ls=ls: [i[5].run() for i in ls]) for ls in lanes]
+            graph, launches_per_step = capture_graph(torch, U, step, warm=args.warmup, branches=branches)
         except Exception as exc:  # keep measuring, say how
             print(f'[bench] CUDA graph capture failed ({exc!r}); timing eager launches', file=sys.stderr)
             graph, launches_per_step = None, None
@@ -542,6 +565,13 @@ def run_unit(args):
             torch.cuda.synchronize()
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     U.device_status()
+    # the same step as one chain of launches (no parallel branches), for comparison
+    ms_chain = None
+    if graph is not None and n_branches > 1:
+        g1, _ = capture_graph(torch, U, step, warm=args.warmup)
+        barrier()
+        ms_chain = max_over_ranks(time_ms(torch, g1.replay, args.steps))
+        del g1
     total_ops = sum(l.ops(args.total_batch) * l.count for l in layer_set)
     value = total_ops / (ms_step * 1e-3) / 1e12
     clocks = cs_.summary()
@@ -689,7 +719,11 @@ def run_unit(args):
             'e2e': {'value': e2e_value, 'unit': 'TOPS', 'h2d_bytes_per_step': h2d * world, 'd2h_bytes_per_step': d2h * world,
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': gpu_launches,
-            'launch_mode': ('cuda graph: one captured step (%d kernel launches) replayed per timed step' % launches_per_step)
+            'single_chain': None if ms_chain is None else {'ms_per_step': ms_chain, 'value': total_ops / (ms_chain * 1e-3) / 1e12,
+                                                            'note': 'the same 54 launches captured as one chain'},
+            'launch_mode': ('cuda graph: one captured step (%d kernel launches%s) replayed per timed step'
+                            % (launches_per_step, '' if n_branches == 1 else
+                               ', dealt to %d parallel branches: the convolutions of the sweep do not depend on one another' % n_branches))
             if launches_per_step is not None else 'eager launches of prepared plans',
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
                          'frac': kernel_tops / int8_peak,
@@ -802,6 +836,8 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-side-configs', action='store_true', help='skip the `configs` records (single-GPU runs)')
     ap.add_argument('--no-graph', action='store_true', help='time eager launches instead of replaying a captured step')
+    ap.add_argument('--branches', type=int, default=2,
+                    help='deal the step\'s (mutually independent) convolutions to this many parallel branches of the captured graph')
     ap.add_argument('--layer', action='append', default=None,
                     help='restrict the sweep to the named layer(s) of unit_b200.resnet50.LAYERS (diagnostic runs; '
                          'the JSON line then describes that subset)')
