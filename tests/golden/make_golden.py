@@ -86,11 +86,28 @@ def small():
     gb = (rng.standard_normal((64, 32)) * 0.05).astype(np.float16)
     g['g_a'], g['g_b'], g['g_c'] = ga, gb, no.gemm_f32(ga, gb)
     np.savez_compressed(os.path.join(HERE, 'golden_small.npz'), **g)
+    # The reference's fused graph operator on signed activations (apps/cpu/relay/conv2d.py:16-23,
+    # apps/cpu/relay/result.log:3-24): multiply(add(conv2d(x s8, w s8), bias), 11) in wrapping s32, here
+    # straight from the signed definition (no +128 shift), with the script's value distributions.
+    r = {}
+    rs = np.random.default_rng(11)
+    xs8 = np.clip(rs.standard_normal((2, 32, 10, 9)) * 128, -128, 127).astype(np.int8)
+    ws8 = np.clip(rs.standard_normal((48, 32, 3, 3)) * 128, -128, 127).astype(np.int8)
+    bs = (rs.standard_normal(48) * 128).astype(np.int32)
+    for tag, pad in (('valid', (0, 0)), ('padded', (1, 1))):
+        acc = no.conv2d_int_nchw(xs8, ws8, (1, 1), pad) + bs.astype(np.int64)[None, :, None, None]
+        out = ((acc * 11) & 0xFFFFFFFF).astype(np.uint32).view(np.int32)
+        r['out_' + tag] = no.pack_nchw_to_nchwc(out)
+    r['x'] = no.pack_nchw_to_nchwc(xs8)
+    r['w'] = no.pack_oihw_to_int8_weights(ws8)
+    r['bias'] = bs
+    np.savez_compressed(os.path.join(HERE, 'golden_relay_flow.npz'), **r)
 
 
 if __name__ == '__main__':
-    ref = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
-    if os.path.exists(os.path.join(ref, 'poc', 'vnni', 'poc.cc')):
+    # the reference checkout: first argument, else $UNIT_REFERENCE (without either only the second fixture is made)
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('UNIT_REFERENCE', '')
+    if ref and os.path.exists(os.path.join(ref, 'poc', 'vnni', 'poc.cc')):
         kat(ref)
     small()
     print('wrote fixtures')

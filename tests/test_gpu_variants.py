@@ -238,6 +238,11 @@ def test_signed_activations_match_the_reference_graph_flow(U, oracle):
     """s8 activations: the reference shifts them to u8, convolves, subtracts 128 * sum(w), adds the
     bias and multiplies by 11 (apps/cpu/relay/result.log:3-24 on x (1, 1024, 16, 16), w (2048, 1024, 1, 1));
     the library multiplies s8 x s8 directly.  Same numbers, with and without padding."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), 'golden', 'golden_relay_flow.npz'))   # committed vectors
+    for tag, p in (('valid', 0), ('padded', 1)):
+        got = U.conv2d_NCHWc_int8(dev(g['x']), dev(g['w']), padding=p, bias=dev(g['bias']), mul=11)
+        assert np.array_equal(got.cpu().numpy(), g['out_' + tag]), tag
     rng = np.random.default_rng(11)
     cases = [((1, 1024, 16, 16), (2048, 1024, 1, 1), 1, 0),      # the logged shape
              ((3, 64, 30, 31), (96, 64, 3, 3), 1, 1), ((2, 32, 17, 19), (32, 32, 3, 3), 2, 1),

@@ -206,3 +206,14 @@ def test_conv3d_oracle_is_a_sum_of_2d_convolutions_over_the_depth_taps(oracle, c
                 acc += oracle.conv2d_u8s8(np.ascontiguousarray(x[:, :, iz]), np.ascontiguousarray(wt[:, :, kd]), (s, s), (p, p))
         acc += b.reshape(1, -1, 1, 1, 16)
         assert np.array_equal(got[:, :, z], acc.astype(np.int32))
+
+
+def test_relay_flow_restatement_matches_the_signed_definition(oracle):
+    """The reference's graph for s8 activations shifts them to u8, convolves, subtracts 128 * sum(w),
+    adds the bias and multiplies by 11 (apps/cpu/relay/result.log:3-24).  Its restatement must equal the
+    committed vectors, which were computed from the signed definition directly; so must the general
+    epilogue function the GPU kernels are compared with."""
+    g = np.load(os.path.join(HERE, 'golden', 'golden_relay_flow.npz'))
+    for tag, pad in (('valid', (0, 0)), ('padded', (1, 1))):
+        assert np.array_equal(oracle.conv2d_s8s8_relay_flow(g['x'], g['w'], (1, 1), pad, bias=g['bias'], mul=11), g['out_' + tag])
+        assert np.array_equal(oracle.conv2d_i8_ex(g['x'], g['w'], (1, 1), pad, bias=g['bias'], mul=11), g['out_' + tag])
