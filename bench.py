@@ -184,30 +184,30 @@ def run_reference(args):
 # --warmup 3 --kernels-only` per layer (profiles/igemm_resnet50_dram_traffic_b256.md).  Writes still
 # in L2 when the kernel ends are not in the write figure.
 NCU_DRAM_B256 = {
-    'stem_7x7s2_3_64': (51.48e6, 147.61e6),
-    's1_1x1_64_64': (51.44e6, 8.61e6),
-    's1_1x1_256_64': (205.61e6, 31.44e6),
-    's1_3x3_64_64': (51.48e6, 10.88e6),
-    's1_1x1_64_256': (51.46e6, 144.63e6),
-    's1_proj_64_256': (51.46e6, 144.88e6),
-    's2_1x1_256_128': (205.62e6, 65.81e6),
-    's2_3x3s2_128_128': (102.97e6, 9.61e6),
-    's2_1x1_512_128': (102.89e6, 6.13e6),
-    's2_3x3_128_128': (25.90e6, 0.0),
-    's2_1x1_128_512': (25.82e6, 42.98e6),
-    's2_proj_s2_256_512': (102.95e6, 53.64e6),
-    's3_1x1_512_256': (102.95e6, 21.19e6),
-    's3_3x3s2_256_256': (52.03e6, 0.33e6),
-    's3_1x1_1024_256': (51.70e6, 0.36e6),
-    's3_3x3_256_256': (13.49e6, 0.0),
-    's3_1x1_256_1024': (13.17e6, 1.00e6),
-    's3_proj_s2_512_1024': (59.31e6, 11.33e6),
-    's4_1x1_1024_512': (51.97e6, 1.43e6),
-    's4_3x3s2_512_512': (28.11e6, 0.0),
-    's4_1x1_2048_512': (26.80e6, 0.0),
-    's4_3x3_512_512': (8.84e6, 0.0),
-    's4_1x1_512_2048': (7.54e6, 0.0),
-    's4_proj_s2_1024_2048': (38.86e6, 0.50e6),
+    'stem_7x7s2_3_64': (51.5e6, 145.6e6),
+    's1_1x1_64_64': (51.5e6, 7.2e6),
+    's1_1x1_256_64': (205.6e6, 32.4e6),
+    's1_3x3_64_64': (51.5e6, 8.3e6),
+    's1_1x1_64_256': (51.5e6, 144.5e6),
+    's1_proj_64_256': (51.5e6, 144.6e6),
+    's2_1x1_256_128': (205.6e6, 67.3e6),
+    's2_3x3s2_128_128': (103.0e6, 10.3e6),
+    's2_1x1_512_128': (102.9e6, 5.7e6),
+    's2_3x3_128_128': (25.9e6, 0.0e6),
+    's2_1x1_128_512': (25.8e6, 42.4e6),
+    's2_proj_s2_256_512': (103.0e6, 53.4e6),
+    's3_1x1_512_256': (103.0e6, 21.0e6),
+    's3_3x3s2_256_256': (52.0e6, 0.2e6),
+    's3_1x1_1024_256': (51.7e6, 0.1e6),
+    's3_3x3_256_256': (13.5e6, 0.0e6),
+    's3_1x1_256_1024': (13.2e6, 1.1e6),
+    's3_proj_s2_512_1024': (59.3e6, 9.7e6),
+    's4_1x1_1024_512': (52.0e6, 1.6e6),
+    's4_3x3s2_512_512': (28.1e6, 0.0e6),
+    's4_1x1_2048_512': (26.8e6, 0.0e6),
+    's4_3x3_512_512': (8.8e6, 0.0e6),
+    's4_1x1_512_2048': (7.5e6, 0.0e6),
+    's4_proj_s2_1024_2048': (38.9e6, 0.5e6),
 }
 
 
