@@ -929,6 +929,26 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint32_t s = 0, ring_phase = 0;
     uint32_t lt = 0;
     bool alive = true;
+    // What does not depend on the tile is computed once (a short-reduction layer has thousands of tiles per
+    // CTA, and the integer divisions below cost this warp more than issuing a tile's copies does).
+    // This lane's K column: chunk position (ci, kw, kh, kd) of its first column and, for fp16, which 16-byte
+    // half (box mode: jj counts chunks, which for fp16 are whole K steps of two columns).
+    // Row form: jj counts kernel rows of the stage, each copied once into the slot of its first column.
+    const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
+    const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
+    const int cpc = (AMODE == A_CONV_BOX || AMODE == A_DENSE_TMA || AMODE == A_CONV_WIN) ? 1 : p.cols_per_chunk;
+    const int half = jj % cpc;
+    const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
+    int kh0 = 0, kw0 = 0, ci0 = 0, kd0 = 0;
+    if (AMODE != A_DENSE_TMA && AMODE != A_CONV_WIN && !row_form) {
+      const int q0 = jj / cpc + ks_begin * chunk_step;  // chunk index along K of this lane's first column
+      const int tap = q0 / p.Cc;                        // taps run (kd, kh, kw), kw fastest
+      ci0 = q0 - tap * p.Cc;
+      kw0 = tap % p.KW;
+      kh0 = (tap / p.KW) % p.KH;
+      kd0 = tap / (p.KW * p.KH);
+    }
+    const uint32_t box_copy_bytes = AMODE == A_CONV_BOX ? (uint32_t)(p.box_n * p.box_h * p.box_w) * 16u : kSubBytes;
     for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
       const int m_tile = (int)fast_div((uint32_t)tile, p.div_n_tiles);
       if constexpr (AMODE == A_CONV_WIN) {
@@ -981,29 +1001,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       }
       // sub-tiles that exist in this tile, and the bytes one copy delivers
       int nsub = MT;
-      uint32_t copy_bytes = kSubBytes;
+      const uint32_t copy_bytes = box_copy_bytes;
       if constexpr (AMODE == A_CONV_BOX) {
         const long long left = p.sub_tiles - (long long)m_tile * MT;
         nsub = left < MT ? (int)left : MT;
-        copy_bytes = (uint32_t)(p.box_n * p.box_h * p.box_w) * 16u;
       }
-      // this lane's K column: chunk position (ci, kw, kh) and, for fp16, which 16-byte half
-      // (box mode: jj counts chunks, which for fp16 are whole K steps of two columns)
-      const int cpc = (AMODE == A_CONV_BOX) ? 1 : p.cols_per_chunk;
-      const int half = jj % cpc;
-      const int chunk_step = (AMODE == A_CONV_BOX && F16) ? p.kc / 2 : p.kc / cpc;
-      int q0 = jj / cpc + ks_begin * chunk_step;  // chunk index along K of this lane's first column
-      int kh = 0, kw = 0, ci = 0, kd = 0;
-      if constexpr (AMODE != A_DENSE_TMA) {
-        const int tap = q0 / p.Cc;  // taps run (kd, kh, kw), kw fastest
-        ci = q0 - tap * p.Cc;
-        kw = tap % p.KW;
-        kh = (tap / p.KW) % p.KH;
-        kd = tap / (p.KW * p.KH);
-      }
-      // row form: jj counts kernel rows of the stage, each copied once into the slot of its first column
-      const bool row_form = AMODE == A_CONV_BOX && p.row_kw > 0;
-      const int rows_per_stage = row_form ? p.kc / p.row_kw : 0;
+      int kh = kh0, kw = kw0, ci = ci0, kd = kd0;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
@@ -1052,7 +1055,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           }
         }
         // advance this lane's column by one stage
-        if constexpr (AMODE != A_DENSE_TMA) {
+        if (AMODE != A_DENSE_TMA && !row_form) {
           ci += chunk_step;
           while (ci >= p.Cc) { ci -= p.Cc; if (++kw == p.KW) { kw = 0; if (++kh == p.KH) { kh = 0; ++kd; } } }
         }
