@@ -439,6 +439,12 @@ __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, uint32_t c
   asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0u;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- thread-block cluster / distributed shared memory (split-K) ----
@@ -1104,7 +1110,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const uint32_t desc_base = smem_base & 0x3FFFFu;
     const uint32_t fold_base = desc_base + (uint32_t)p.stages * stage_bytes;  // [B digits set 0][set 1][A constants]
     const uint32_t my_t = warp == kMmaWarp ? 0u : 1u;  // the sub-tile this thread issues for
-    if (lane == 0) {
+#ifndef UNIT_MMA_CONVERGED
+#define UNIT_MMA_CONVERGED 1
+#endif
+    // UNIT_MMA_CONVERGED: all 32 lanes run the issue loop together (waits are warp-collective, addresses are
+    // warp-uniform) and one elected lane executes the MMA, commit and arrive instructions.
+    constexpr bool kConv = UNIT_MMA_CONVERGED != 0;
+    const bool one = kConv ? elect_one() : true;
+    if (kConv || lane == 0) {
       const uint32_t idesc = make_idesc<F16>(p.bn, p.a_signed);
       const uint64_t a_desc0 = make_smem_desc(0u, kSubBytes, 128u);
       const uint64_t a_desc_row = make_smem_desc(0u, 16u, 128u);  // row form: K columns 16 bytes apart
@@ -1122,12 +1135,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
         const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
         // the drain warps arrive on "empty" after every drain of the set: its first use needs no wait
-        if (use > 0u && !mbar_wait(smem_u32(&ps->tempty[slot]), (use - 1u) & 1u, wc, kErrWaitTmemEmpty)) {
+        if (use > 0u && !(kConv ? mbar_wait_warp(smem_u32(&ps->tempty[slot]), (use - 1u) & 1u, wc, kErrWaitTmemEmpty)
+                                 : mbar_wait(smem_u32(&ps->tempty[slot]), (use - 1u) & 1u, wc, kErrWaitTmemEmpty))) {
           alive = false;
           break;
         }
         tc_fence_after();
-        if (my_t == 0u) trace_mark(p, lt, 3);
+        if (one && my_t == 0u) trace_mark(p, lt, 3);
         const uint32_t d_tmem = tmem_base + (slot * (uint32_t)MT + my_t) * (uint32_t)p.bn;  // this thread's accumulator
         uint32_t started = 0u;
         uint32_t win_off0 = 0u;  // window form: this sub-tile's first position inside the stage's windows
@@ -1139,12 +1153,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         }
         const uint64_t a_desc_win = make_smem_desc(0u, (uint32_t)p.win_bytes, 128u);
         for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!mbar_wait(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull)) {
+          if (!(kConv ? mbar_wait_warp(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull)
+                      : mbar_wait(smem_u32(&ps->full[s]), ring_phase, wc, kErrWaitFull))) {
             alive = false;
             break;
           }
           tc_fence_after();
-          if (ks == 0 && my_t == 0u) trace_mark(p, lt, 4);
+          if (one && ks == 0 && my_t == 0u) trace_mark(p, lt, 4);
           // descriptors differ only in the start-address field (address >> 4, 14 bits)
           const uint32_t stage_enc = (desc_base + s * stage_bytes) >> 4;
           const uint32_t a_enc = stage_enc + my_t * a_sub_enc;  // this thread's sub-tile of the stage
@@ -1157,7 +1172,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
               const uint64_t adesc = a_desc_win | (uint64_t)(stage_enc + win_off0 + (uint32_t)(kh * p.win_wp + kw));
-              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
               started = 1u;
               if (++kw == p.KW) { kw = 0; ++kh; }
             }
@@ -1166,7 +1181,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
               const uint64_t adesc = a_desc_sw | (uint64_t)(a_enc + (uint32_t)(k >> 2) * (16384u >> 4) + (uint32_t)(k & 3) * 2u);
-              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
               started = 1u;
             }
           } else if (AMODE == A_CONV_BOX && p.row_kw > 0) {
@@ -1176,7 +1191,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
               const uint64_t adesc = a_desc_row | (uint64_t)(a_row + (uint32_t)pr * 2u);
-              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
               started = 1u;
               if (++pr == (p.row_kw >> 1)) { pr = 0; a_row += ((uint32_t)p.row_kw * kSubBytes) >> 4; }
             }
@@ -1184,11 +1199,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             for (int k = 0; k < nk; ++k) {
               const uint64_t bdesc = b_desc0 | (uint64_t)(b_enc + (uint32_t)k * b_step);
               const uint64_t adesc = a_desc_std | (uint64_t)(a_enc + (uint32_t)k * a_step);
-              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
               started = 1u;
             }
           }
-          tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
+          if (one) tc_commit(smem_u32(&ps->empty[s]));  // frees the stage when these MMAs have read it
           if (++s == (uint32_t)p.stages) { s = 0; ring_phase ^= 1u; }
         }
         if (alive) {
@@ -1196,7 +1211,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             // The bias step comes last: the drain warps stage the set's bias while the main loop
             // runs (for a CTA's first tiles that is the whole of global-memory latency), and integer
             // sums do not depend on the order of their terms.
-            if (!mbar_wait(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias)) {
+            if (!(kConv ? mbar_wait_warp(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias)
+                        : mbar_wait(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias))) {
               alive = false;
               break;
             }
@@ -1205,15 +1221,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0 && (!SPLITK || crank == 0u)) {
               const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
               const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
-              tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
+              if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
             }
           }
           // "accumulators ready" completes with every issuer's commit plus one plain arrival (a
           // release that passes the drain warps' bias integers on to whichever warp reads them)
-          if (my_t == 0u) mbar_arrive(smem_u32(&ps->tfull[slot]));
-          tc_commit(smem_u32(&ps->tfull[slot]));
+          if (one && my_t == 0u) mbar_arrive(smem_u32(&ps->tfull[slot]));
+          if (one) tc_commit(smem_u32(&ps->tfull[slot]));
         }
-        if (my_t == 0u) trace_mark(p, lt, 5);
+        if (one && my_t == 0u) trace_mark(p, lt, 5);
       }
     }
   } else if (warp < kDrainWarps) {
