@@ -184,8 +184,9 @@ int unit_debug_set(int key, long long value);
  * generated kernel (apps/cpu/kernel/conv2d.py:26,30).  Source layout
  * [c_out/16][c_in/c_block][kh][kw][c_block/4][16][4] s8.  The packed form depends on
  * c_in, c_block, c_out, kh, kw and the strides (the column-block width is chosen per stride) and,
- * for c_block == 4, on the padding too: pack with the descriptor fields the convolution will use
- * (n, h and w may differ). */
+ * for c_block == 4 and for strides other than 1, on the padding too (a stride-2 kernel carries a
+ * copy for pixel-pair rows, whose taps sit by the parity of the horizontal padding): pack with
+ * the descriptor fields the convolution will use (n, h and w may differ). */
 size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *desc);
 int unit_pack_weights_conv_i8(const unit_conv_desc *desc, const int8_t *d_w,
                               void *d_packed, void *stream);

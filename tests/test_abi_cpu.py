@@ -54,7 +54,12 @@ def test_packed_weight_sizes_are_pure_host_functions(L):
     # 3x3 64->64: 36 K columns of 16 B, one 64-wide N tile; stride 1 with several taps and an even chunk
     # count carries a second copy in the window form's column order (the same size)
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc())) == 2 * 36 * 64 * 16
-    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(stride_h=2, stride_w=2))) == 36 * 64 * 16
+    # stride 2 with several taps per kernel row carries a second copy in the pair form's order: 3 kernel rows x
+    # 2 pair offsets x 4 chunks x 2 half-columns = 48 columns (the 12 half-columns that are no tap hold zeros),
+    # whatever the input size (the pack call does not know it; odd widths simply do not use the copy)
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(stride_h=2, stride_w=2))) == 36 * 64 * 16 + 48 * 64 * 16
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(stride_h=2, stride_w=2, w=55))) == 36 * 64 * 16 + 48 * 64 * 16
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(stride_h=2, stride_w=2, kh=1, kw=1))) == 4 * 64 * 16
     # 1x1 512->2048: 32 columns, 8 N tiles of 256
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(desc(c_in=512, c_out=2048, kh=1, kw=1))) == 32 * 2048 * 16
     # stem: 7 kh x 2 groups of 4 kw taps = 14 columns in one stage, plus the 16 columns of the folded form

@@ -118,6 +118,16 @@ def test_vnni_known_answer_through_the_gpu(U):
     (16, 32, 40, 40, 32, 3, 1, 1, 1),
     (20, 64, 33, 35, 64, 2, 2, 1, 0),
     (12, 32, 70, 110, 16, 3, 3, 1, 1),
+    # pair form (stride 2 on an even width, several taps per kernel row): padded and valid, odd heights,
+    # kernels of 2 to 7 taps per row (1 to 4 pair offsets), rectangular kernels, ragged boxes, two column blocks
+    (6, 32, 56, 56, 48, 3, 3, 2, 1),
+    (5, 48, 31, 30, 320, 3, 3, 2, 0),
+    (4, 32, 41, 58, 32, 5, 5, 2, 2),
+    (8, 16, 64, 64, 16, 2, 2, 2, 0),
+    (3, 32, 50, 52, 32, 4, 4, 2, 1),
+    (2, 16, 100, 100, 64, 7, 7, 2, 3),
+    (9, 64, 23, 22, 80, 1, 3, 2, 0),
+    (3, 16, 30, 300, 32, 3, 3, 2, 1),     # output rows wider than a 128-row sub-tile
 ])
 def test_conv_int8_bit_exact(U, oracle, n, ci, h, w, co, kh, kw, s, p):
     rng = np.random.default_rng(hash((n, ci, h, w, co, kh, kw, s, p)) % 2 ** 32)

@@ -47,14 +47,15 @@ def variant_counts():
 
 
 # (operand path, sub-tiles) -> geometry (n, c_in, h, w, c_out, k, stride, pad, c_block).  The selection
-# rules: stride 1 on tensors >= 128 KB -> whole-row box copies; other strides -> im2col copies; tensors
+# rules: stride 1 on tensors >= 128 KB -> whole-row box copies; stride 2 with several taps per kernel row on an
+# even width -> box copies of pixel pairs; other strides -> im2col copies; tensors
 # below 128 KB, or strides the im2col descriptor cannot express (> 8) -> cp.async gather; NCHW4c
 # images of odd size -> the 4-byte gather; two sub-tiles per tile once 2 x tiles >= SMs.
 INT8_CASES = {
     'box_mt1': (9, 32, 23, 21, 48, 3, 1, 1, 16),
     'box_mt2': (8, 16, 56, 56, 16, 3, 1, 1, 16),
-    'im2col_mt1': (4, 32, 40, 40, 32, 3, 2, 1, 16),
-    'im2col_mt2': (8, 16, 112, 112, 16, 3, 2, 1, 16),
+    'im2col_mt1': (4, 32, 41, 41, 32, 3, 2, 1, 16),
+    'im2col_mt2': (8, 16, 113, 113, 16, 3, 2, 1, 16),
     'gather_mt1': (2, 32, 13, 11, 32, 3, 2, 1, 16),
     'gather_mt2': (32, 16, 225, 225, 16, 1, 9, 0, 16),
     'stem_gather_mt1': (2, 4, 33, 35, 32, 7, 2, 3, 4),
@@ -65,7 +66,11 @@ INT8_CASES = {
     'win_mt2': (24, 32, 56, 56, 16, 3, 1, 1, 16),
     # few tiles and a long reduction: split-K over a thread-block cluster
     'box_splitk': (1, 256, 24, 24, 256, 3, 1, 1, 16),
-    'im2col_splitk': (1, 256, 24, 24, 256, 3, 2, 1, 16),
+    'im2col_splitk': (1, 256, 25, 25, 256, 3, 2, 1, 16),
+    # stride 2 on an even width, 3x3: the pair form (dense rows of pixel pairs through the box-copy kernel)
+    'pair_mt1': (4, 32, 40, 40, 32, 3, 2, 1, 16),
+    'pair_mt2': (8, 16, 112, 112, 16, 3, 2, 1, 16),
+    'pair_splitk': (1, 256, 24, 24, 256, 3, 2, 1, 16),
 }
 INT8_VARIANTS = {
     'box_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'box_mt2': 'A_CONV_BOX, {}, i8, MT=2',
@@ -74,6 +79,7 @@ INT8_VARIANTS = {
     'stem_gather_mt1': 'A_STEM_I8, {}, i8, MT=1', 'stem_gather_mt2': 'A_STEM_I8, {}, i8, MT=2',
     'win_mt1': 'A_CONV_WIN, {}, i8, MT=1', 'win_mt2': 'A_CONV_WIN, {}, i8, MT=2',
     'box_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K', 'im2col_splitk': 'A_CONV_TMA, {}, i8, MT=1, split-K',
+    'pair_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'pair_mt2': 'A_CONV_BOX, {}, i8, MT=2', 'pair_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K',
 }
 
 
@@ -167,18 +173,19 @@ def test_dense_and_gemm_variants(U, oracle, case):
 
 def test_tensor_map_size_boundary(U, oracle):
     """Tensors below 128 KB take the cp.async gather, tensors from 128 KB on the tensor copies: both
-    sides of the boundary, stride 1 (box copies) and stride 2 (im2col copies), same results."""
+    sides of the boundary, for stride 1 (box copies), stride 2 with a 3x3 kernel (box copies of pixel
+    pairs) and stride 2 with a 1x1 kernel (im2col copies), same results."""
     rng = np.random.default_rng(131072)
-    for s, at in ((1, 'A_CONV_BOX'), (2, 'A_CONV_TMA')):
-        for (h, w, path) in ((64, 63, 'A_CONV_I8'), (64, 64, at)):   # 32 x 64 x 64 bytes = 131072 exactly
+    for s, k, at in ((1, 3, 'A_CONV_BOX'), (2, 3, 'A_CONV_BOX'), (2, 1, 'A_CONV_TMA')):
+        for (h, w, path) in ((64, 62, 'A_CONV_I8'), (64, 64, at)):   # 32 x 64 x 64 bytes = 131072 exactly
             x = rng.integers(0, 256, (1, 2, h, w, 16), dtype=np.uint8)
-            wt = rng.integers(-128, 128, (2, 2, 3, 3, 4, 16, 4), dtype=np.int8)
+            wt = rng.integers(-128, 128, (2, 2, k, k, 4, 16, 4), dtype=np.int8)
             before = variant_counts()
-            got = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=s, padding=1)
+            got = U.conv2d_NCHWc_int8(dev(x), dev(wt), stride=s, padding=k // 2)
             U.device_status()
-            assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (s, s), (1, 1)))
+            assert np.array_equal(got.cpu().numpy(), oracle.conv2d_u8s8(x, wt, (s, s), (k // 2, k // 2)))
             name = f'igemm_kernel<{path}, EPI_RAW_NCHWC, i8, MT=1>'
-            assert variant_counts()[name] > before[name], (h, w, s, name)
+            assert variant_counts()[name] > before[name], (h, w, s, k, name)
 
 
 @pytest.mark.parametrize('n,ci,hw,co,k,s', [

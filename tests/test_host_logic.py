@@ -155,18 +155,18 @@ def test_tile_table_overrides_are_host_side_and_reversible():
     from unit_b200 import _lib, build, tile_table
     build.build()
     L = _lib.lib()
-    d = _lib.ConvDesc(1, 64, 30, 30, 16, 80, 3, 3, 2, 2, 0, 0)     # (stride 2: one packed copy only)
+    d = _lib.ConvDesc(1, 64, 31, 31, 16, 80, 1, 1, 2, 2, 0, 0)     # (1x1 with stride 2: one packed copy only)
     base = L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d))
-    assert base == 36 * 80 * 16                       # one column block of 80
-    key = dict(c_in=64, c_block=16, c_out=80, kh=3, kw=3, stride_h=2, stride_w=2)
+    assert base == 4 * 80 * 16                        # one column block of 80
+    key = dict(c_in=64, c_block=16, c_out=80, kh=1, kw=1, stride_h=2, stride_w=2)
     tile_table.set_table([dict(key, n=0, bn=64)])
-    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == 36 * 96 * 16     # two blocks of 48
-    tile_table.set_table([dict(key, n=4, h=30, w=30, bn=64)])                        # size-specific: weights untouched
+    assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == 4 * 96 * 16      # two blocks of 48
+    tile_table.set_table([dict(key, n=4, h=31, w=31, bn=64)])                        # size-specific: weights untouched
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == base
     tile_table.set_table([])
     assert L.unit_packed_weights_bytes_conv_i8(ctypes.byref(d)) == base
     bad = (_lib.TileEntry * 1)()
-    bad[0].c_in, bad[0].c_block, bad[0].c_out, bad[0].kh, bad[0].kw, bad[0].stride_h, bad[0].stride_w = 64, 16, 80, 3, 3, 2, 2
+    bad[0].c_in, bad[0].c_block, bad[0].c_out, bad[0].kh, bad[0].kw, bad[0].stride_h, bad[0].stride_w = 64, 16, 80, 1, 1, 2, 2
     bad[0].bn = 40                                                                    # not a multiple of 16
     assert L.unit_tile_table_set(bad, 1) == -2
     assert L.unit_tile_table_set(bad, 5000) == -8

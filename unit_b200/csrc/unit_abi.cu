@@ -202,6 +202,41 @@ static TileCfg win_cfg(const unit_conv_desc *d) {
   c.b_stage_bytes = (size_t)c.kc * c.bn * 16;
   return c;
 }
+// ---- pair form: stride 2 on u8 NCHW16c ----
+// With horizontal stride 2, tap kw of output column ow reads input column 2 ow + kw - pad = 2 (ow + q) + r:
+// pixel r (0 or 1) of the input row's pixel PAIR ow + q.  Consecutive outputs read consecutive pairs, so the
+// A operand can be fetched as dense rows of 32-byte pairs (whole cache sectors; the im2col copies fetch every
+// other 16-byte pixel as its own request) and one K step = one pair = 32 bytes: both pixels' 16 channels of a
+// chunk, against weights that hold tap (kh, 2 q + r + pad) in half r, or zeros where that is no tap.  A kernel
+// row then takes G K steps per chunk (G = number of distinct q: 2 for a 3 x 3 kernel with pad 1, instead of 3
+// taps).  Vertical stride 2 is the box copy's traversal stride.
+struct PairGeom {
+  bool ok = false;
+  int G = 0, qmin = 0, cols = 0;
+};
+static int floor_div2(int v) { return v >= 0 ? v / 2 : -((-v + 1) / 2); }
+static PairGeom pair_geom(const unit_conv_desc *d) {
+  static const int enabled = tuning_int("UNIT_B200_PAIR", 1);
+  PairGeom g;
+  // (weight-side conditions only: the packed copy must not depend on the input size, which the pack call does not
+  // know; the convolution call uses the copy when the width is even)
+  if (!enabled || d->c_block != 16 || d->stride_h != 2 || d->stride_w != 2 || d->kw < 2) return g;
+  g.qmin = floor_div2(0 - d->pad_w);
+  g.G = floor_div2(d->kw - 1 - d->pad_w) - g.qmin + 1;
+  g.cols = d->kh * g.G * (d->c_in / 16) * 2;
+  // at least two thirds of the half-columns must carry a tap (3 x 3: 9 of 12)
+  g.ok = 3 * d->kw >= 2 * 2 * g.G;
+  return g;
+}
+// Tile shape of the pair-form copy of the weights.
+static TileCfg pair_cfg(const unit_conv_desc *d, const PairGeom &g) {
+  unit_tile_entry e;
+  unit_conv_desc any = *d;
+  any.n = 0; any.h = 0; any.w = 0;
+  const bool hit = tile_lookup(&any, &e) && e.n == 0 && e.bn >= 16 && e.bn <= 256 && e.bn % 16 == 0;
+  return make_cfg(d->c_out, g.cols, true, false, hit ? e.bn : 0, hit ? e.kc : 0);
+}
+
 struct WinGeom {
   bool ok = false;
   int mt = 0, wp = 0, rows = 0, bytes = 0, box_bytes = 0, tpi = 0;
@@ -274,7 +309,7 @@ static int sm_count() {
 // ---------------------------------------------------------------------------
 // weight packing: reference layouts -> [n_tile][k_stage][kc][bn][16 B] blocks
 // ---------------------------------------------------------------------------
-enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4, PACK_STEM_S2D = 5, PACK_CONV_WIN = 6 };
+enum PackMode : int { PACK_CONV_I8 = 0, PACK_STEM_I8 = 1, PACK_CONV_F16 = 2, PACK_DENSE_I8 = 3, PACK_GEMM_F16 = 4, PACK_STEM_S2D = 5, PACK_CONV_WIN = 6, PACK_CONV_PAIR = 7 };
 
 struct PackParams {
   const uint8_t *src;
@@ -282,6 +317,7 @@ struct PackParams {
   int mode, n_total, bn, kc, cols, k_stages, n_tiles;
   int Cc, KH, KW, kwg;  // conv
   int tw, sft_h, sft_w;  // PACK_STEM_S2D: taps per row of the 2x2-folded kernel, tap shifts
+  int pair_g, pair_qmin, pair_pad;  // PACK_CONV_PAIR: pair offsets per kernel row, the first offset, the horizontal padding
   int K, T;             // dense / gemm (K in elements)
 };
 
@@ -311,6 +347,15 @@ __global__ void pack_weights_kernel(const PackParams p) {
         const int kh = tap / p.KW, kw = tap % p.KW;
         const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15) * 4;
         for (int m = 0; m < 4; ++m) w[m] = *reinterpret_cast<const uint32_t *>(s + m * 64);
+      } else if (p.mode == PACK_CONV_PAIR) {
+        // column = (K step, half r); K step = ((kh, pair offset g), chunk): tap kw = 2 (qmin + g) + r + pad or none
+        const int r = j & 1, step = j >> 1;
+        const int tg = step / p.Cc, ci = step % p.Cc;
+        const int kh = tg / p.pair_g, kw = 2 * (p.pair_qmin + tg % p.pair_g) + r + p.pair_pad;
+        if (kw >= 0 && kw < p.KW) {
+          const uint8_t *s = p.src + ((((size_t)(oc >> 4) * p.Cc + ci) * p.KH + kh) * p.KW + kw) * 256 + (oc & 15) * 4;
+          for (int m = 0; m < 4; ++m) w[m] = *reinterpret_cast<const uint32_t *>(s + m * 64);
+        }
       } else if (p.mode == PACK_STEM_I8) {
         const int g = j % p.kwg;
         const int t2 = j / p.kwg;
@@ -1154,6 +1199,35 @@ static bool make_box_map_f16(CUtensorMap *map, int n, int c_in, int h, int w, co
   return r == CUDA_SUCCESS;
 }
 
+// Tiled-mode tensor map over u8 NCHW16c activations seen as (8-byte quarters of a pixel pair, pair, image
+// row, chunk, image): one copy fetches box_n x box_h x box_w pairs, taking every second image row, and
+// writes them as 32-byte-swizzled rows (one K step of the pair form).
+static bool make_pair_map(CUtensorMap *map, int n, int c_in, int h, int w, const void *x, const BoxGeom &g) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode || (w & 1) || !tensor_map_allowed((long long)n * c_in * h * w)) return false;
+  if (2 * g.bh - 1 > 256) return false;
+  const cuuint64_t cc = (cuuint64_t)c_in / 16;
+  const cuuint64_t dims[5] = {4, (cuuint64_t)w / 2, (cuuint64_t)h, cc, (cuuint64_t)n};
+  const cuuint64_t row = (cuuint64_t)w * 16;
+  const cuuint64_t strides[4] = {32, row, row * h, row * h * cc};
+  const cuuint32_t box[5] = {4, (cuuint32_t)g.bw, (cuuint32_t)(2 * g.bh - 1), 1, (cuuint32_t)g.bn};
+  const cuuint32_t estr[5] = {1, 1, 2, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 5, const_cast<void *>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // Tiled-mode tensor map over a row-major byte matrix for the 128-byte-swizzled operand layout:
 // one copy fetches 128 bytes of K of 128 consecutive rows (full cache lines) and writes them as
 // 1 KB atoms of 8 rows with the 16-byte chunks permuted by the row number.  Bytes and rows past
@@ -1301,6 +1375,20 @@ static int plan_conv_i8(PlanImpl &pl, const unit_conv_desc *d, const void *x, co
       if (make_box_map(&map, d->n, d->c_in, d->h, d->w, x, g)) {
         set_box(p, g, d->n);
         return prepare_conv_i8<A_CONV_BOX>(pl, c, epi, &map);
+      }
+    }
+    const PairGeom pg = pair_geom(d);
+    if (use_tma() && pg.ok && d->w % 2 == 0) {
+      // stride 2, several taps per kernel row, even width: dense rows of pixel pairs, one K step per pair
+      const BoxGeom g = choose_box(d->n, p.OH, p.OW);
+      if (make_pair_map(&map, d->n, d->c_in, d->h, d->w, x, g)) {
+        const TileCfg pc = pair_cfg(d, pg);
+        set_box(p, g, d->n);
+        p.a_sw32 = 1;
+        p.KW = pg.G;       // the producer walks (kh, pair offset, chunk)
+        p.pw = -pg.qmin;   // first pair of a box row = first output column + qmin
+        p.b = static_cast<const uint8_t *>(pw) + (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes;  // the second packed copy
+        return prepare_conv_i8<A_CONV_BOX>(pl, pc, epi, &map);
       }
     }
     if (use_tma() && make_im2col_map(&map, d, x, false)) return prepare_conv_i8<A_CONV_TMA>(pl, c, epi, &map);
@@ -1543,6 +1631,11 @@ size_t unit_packed_weights_bytes_conv_i8(const unit_conv_desc *d) {
     const TileCfg wc = win_cfg(d);
     bytes += (size_t)wc.n_tiles * wc.k_stages * wc.b_stage_bytes;
   }
+  const PairGeom pg = pair_geom(d);
+  if (pg.ok) {  // second copy in the pair form's column order (stride 2)
+    const TileCfg pc = pair_cfg(d, pg);
+    bytes += (size_t)pc.n_tiles * pc.k_stages * pc.b_stage_bytes;
+  }
   const StemFold f = stem_fold(d, false);
   if (f.ok) {  // second copy for the folded stride-1 form of a stride-2 stem
     const TileCfg cf = make_cfg(d->c_out, f.th * f.tw);
@@ -1576,6 +1669,16 @@ int unit_pack_weights_conv_i8(const unit_conv_desc *d, const int8_t *w, void *pa
     pwn.mode = PACK_CONV_WIN;
     pwn.bn = wc.bn; pwn.kc = wc.kc; pwn.cols = wc.cols; pwn.k_stages = wc.k_stages; pwn.n_tiles = wc.n_tiles;
     rc = launch_pack(pwn, static_cast<cudaStream_t>(stream));
+  }
+  const PairGeom pg = pair_geom(d);
+  if (rc == UNIT_OK && pg.ok) {
+    const TileCfg pc = pair_cfg(d, pg);
+    PackParams ppr = pp;
+    ppr.dst = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(packed) + (size_t)c.n_tiles * c.k_stages * c.b_stage_bytes);
+    ppr.mode = PACK_CONV_PAIR;
+    ppr.bn = pc.bn; ppr.kc = pc.kc; ppr.cols = pc.cols; ppr.k_stages = pc.k_stages; ppr.n_tiles = pc.n_tiles;
+    ppr.pair_g = pg.G; ppr.pair_qmin = pg.qmin; ppr.pair_pad = d->pad_w;
+    rc = launch_pack(ppr, static_cast<cudaStream_t>(stream));
   }
   const StemFold f = stem_fold(d, false);
   if (rc == UNIT_OK && f.ok) {

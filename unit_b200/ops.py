@@ -140,7 +140,8 @@ def pack_conv_weights_int8(kernel: torch.Tensor, stride: IntPair = 1, padding: I
     """kernel: s8 ``[O/16][I/cb][KH][KW][cb/4][16][4]`` (apps/cpu/kernel/conv2d.py:26,30).
 
     The packed form depends on the stride the convolution will use (the column-block width is
-    chosen per stride) and, for NCHW4c kernels (cb = 4), on the padding as well.
+    chosen per stride) and, for NCHW4c kernels (cb = 4) and for strided kernels (whose pair form
+    places the taps by the parity of the horizontal padding), on the padding as well.
     """
     L = _require_cuda_lib()
     kernel = _to_device(kernel, torch.int8, 'kernel')
@@ -149,7 +150,7 @@ def pack_conv_weights_int8(kernel: torch.Tensor, stride: IntPair = 1, padding: I
     oc, icc, kh, kw, c4 = (int(s) for s in kernel.shape[:5])
     cb = c4 * 4
     stride = _pair(stride)
-    padding = _pair(padding) if cb == 4 else (0, 0)
+    padding = _pair(padding) if (cb == 4 or stride != (1, 1)) else (0, 0)
     key = ('conv_i8', oc * 16, icc * cb, cb, kh, kw, stride, padding)
 
     def make():
@@ -306,8 +307,8 @@ def _conv_int8_prepare(data, kernel, stride, padding, dilation, out_layout, out_
         _, c_out, c_in, pcb, kh, kw, pstride, ppad = pw.key
         if c_in != cc * cb or pcb != cb:
             raise ValueError(f'channel mismatch: data has {cc}x{cb}, kernel expects {c_in} in blocks of {pcb}')
-        if pstride != stride or (cb == 4 and ppad != padding):
-            raise ValueError('weights were packed for a different stride (or, NCHW4c, padding)')
+        if pstride != stride or ((cb == 4 or stride != (1, 1)) and ppad != padding):
+            raise ValueError('weights were packed for a different stride (or, NCHW4c and strided kernels, padding)')
         requant = out_dtype == 'uint8' or requant_shift is not None or residual is not None
         shift = (8 if requant_shift is None else int(requant_shift)) if requant else 0
         if requant and int(mul) != 1:
