@@ -464,14 +464,11 @@ def side_configs(torch, U, R, dev, peaks, local_rank):
     # layout kernels (NCHW <-> NCHW16c): GB/s of bytes read + written
     xl = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device=dev)
     yl = U.pack_data_nchwc(xl)
-    for _ in range(3):  # the outputs come from torch's caching allocator: let it settle before timing
-        U.pack_data_nchwc(xl)
-        U.unpack_data_nchwc(yl)
-    torch.cuda.synchronize()
-    ms_p = min(time_ms(torch, lambda: U.pack_data_nchwc(xl), 10) for _ in range(3))
-    ms_u = min(time_ms(torch, lambda: U.unpack_data_nchwc(yl), 10) for _ in range(3))
+    # (L2 is flushed before every call: source and result together, 102 MB, would otherwise stay in it)
+    ms_p = flushed(lambda: U.pack_data_nchwc(xl), 10)
+    ms_u = flushed(lambda: U.unpack_data_nchwc(yl), 10)
     out['layout_kernels'] = {'nchw_to_nchw16c_gbs': 2 * xl.numel() / ms_p / 1e6, 'nchw16c_to_nchw_gbs': 2 * xl.numel() / ms_u / 1e6,
-                             'tensor': 'u8 (64, 256, 56, 56), 51 MB each way', 'hbm_peak_gbs': peaks['hbm_gbs']}
+                             'tensor': 'u8 (64, 256, 56, 56), 51 MB each way', 'l2': 'flushed before every call', 'hbm_peak_gbs': peaks['hbm_gbs']}
     del xl, yl, flush
 
     # tensor-core peak, measured
