@@ -71,6 +71,8 @@ INT8_CASES = {
     'pair_mt1': (4, 32, 40, 40, 32, 3, 2, 1, 16),
     'pair_mt2': (8, 16, 112, 112, 16, 3, 2, 1, 16),
     'pair_splitk': (1, 256, 24, 24, 256, 3, 2, 1, 16),
+    # a tensor below 128 KB with a long reduction and few tiles (a deep layer at batch 1): the gather, split over K
+    'gather_splitk': (1, 512, 7, 7, 512, 3, 1, 1, 16),
 }
 INT8_VARIANTS = {
     'box_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'box_mt2': 'A_CONV_BOX, {}, i8, MT=2',
@@ -80,6 +82,7 @@ INT8_VARIANTS = {
     'win_mt1': 'A_CONV_WIN, {}, i8, MT=1', 'win_mt2': 'A_CONV_WIN, {}, i8, MT=2',
     'box_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K', 'im2col_splitk': 'A_CONV_TMA, {}, i8, MT=1, split-K',
     'pair_mt1': 'A_CONV_BOX, {}, i8, MT=1', 'pair_mt2': 'A_CONV_BOX, {}, i8, MT=2', 'pair_splitk': 'A_CONV_BOX, {}, i8, MT=1, split-K',
+    'gather_splitk': 'A_CONV_I8, {}, i8, MT=1, split-K',
 }
 
 

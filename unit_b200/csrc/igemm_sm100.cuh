@@ -718,8 +718,8 @@ __device__ __forceinline__ void stage_bias(const IgemmParams &p, PipeShared *ps,
 template <int AMODE, int EPI, bool F16, int MT, bool SPLITK = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
     igemm_kernel(const IgemmParams p, const __grid_constant__ CUtensorMap tmap) {
-  static_assert(!SPLITK || (MT == 1 && a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN),
-                "split-K: single sub-tiles, tensor-copy-fed A operand, not the window form");
+  static_assert(!SPLITK || (MT == 1 && ((a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN) || AMODE == A_CONV_I8)),
+                "split-K: single sub-tiles; tensor-copy-fed A operand (not the window form) or the u8 gather");
   extern __shared__ __align__(1024) uint8_t smem[];  // (1 KB: a swizzled operand atom is 8 rows x 128 bytes)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -840,7 +840,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
       if (threadIdx.x == kFirstProducerWarp * 32) trace_mark(p, lt, 0);
       int ci = 0, kh = 0, kw = 0, kd = 0;  // position of the next K column (conv modes)
-      for (int ks = 0; ks < p.k_stages; ++ks) {
+      if constexpr (AMODE == A_CONV_I8) {
+        // (split-K: this CTA's part of the reduction starts at column ks_begin * kc)
+        const int col0 = ks_begin * p.kc, tap = col0 / p.Cc;
+        ci = col0 - tap * p.Cc;
+        kw = tap % p.KW;
+        kh = (tap / p.KW) % p.KH;
+        kd = tap / (p.KW * p.KH);
+      }
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         if (!mbar_wait_warp(smem_u32(&ps->empty[s]), ring_phase ^ 1u, wc, kErrWaitEmpty)) {
           alive = false;
           break;

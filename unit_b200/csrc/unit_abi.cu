@@ -907,7 +907,8 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
     const int mt = (pl.table_mt == 1 || pl.table_mt == 2) ? pl.table_mt : choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA);
     if (mt == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
-  if constexpr (a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN) {  // (the window form is used on full grids only)
+  if constexpr ((a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN) || AMODE == A_CONV_I8) {  // (the window form is used on full grids only;
+                                                                                        //  of the gathers, the u8 convolution's has a split-K form)
     int ks = choose_ksplit(c, p.m_total, sms, pl.table_ksplit);
     // all clusters must be resident at once: a cluster needs its CTAs on SMs of one GPC, so fewer
     // clusters fit than SMs / size suggests (measured: 49 clusters of 3 ran in two rounds)
