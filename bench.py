@@ -735,13 +735,15 @@ def run_unit(args):
             if launches_per_step is not None else 'eager launches of prepared plans',
             'roofline': {'bound': 'tensor', 'achieved': kernel_tops, 'peak': int8_peak, 'unit': 'TOPS',
                          'frac': kernel_tops / int8_peak,
+                         # the same fraction over the timed graph replays (the step's launches overlap their tails)
+                         'frac_of_step': total_ops / world / (ms_step * 1e-3) / 1e12 / int8_peak,
                          'traffic': (sum(ncu_traffic(l.name, batch) * l.count for l in layer_set) / n_launch)
                          if batch == TOTAL_BATCH else None,
                          'peak_source': f'2 x bf16_tflops_sustained of {peaks["source"]} peaks '
                                         '(dense int8 issues at twice the bf16 rate)',
                          'peak_measured': peak_measured,
                          'frac_of_peak_measured': (kernel_tops / peak_measured) if peak_measured else None,
-                         'kernel': 'igemm_kernel<A_CONV_BOX|A_CONV_TMA, EPI_REQ_NCHWC, i8> over the contraction launches '
+                         'kernel': 'igemm_kernel<A_CONV_BOX|A_CONV_WIN|A_CONV_TMA, EPI_REQ_NCHWC, i8> over the contraction launches '
                                    'of one step (2 x ops / summed per-layer launch time, CUDA events)',
                          'traffic_note': 'mean DRAM bytes per launch over the 53 launches of a step (ncu, one capture per '
                                          'layer shape at batch 256); algorithmic mean %.1f MB'
