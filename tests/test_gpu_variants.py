@@ -256,6 +256,8 @@ def test_signed_activations_match_the_reference_graph_flow(U, oracle):
     rng = np.random.default_rng(11)
     cases = [((1, 1024, 16, 16), (2048, 1024, 1, 1), 1, 0),      # the logged shape
              ((3, 64, 30, 31), (96, 64, 3, 3), 1, 1), ((2, 32, 17, 19), (32, 32, 3, 3), 2, 1),
+             ((4, 64, 40, 44), (64, 64, 3, 3), 2, 1),            # stride 2 on an even width: the pair form, signed
+             ((3, 32, 38, 40), (48, 32, 5, 5), 2, 2),
              ((2, 3, 34, 34), (32, 3, 7, 7), 2, 3)]              # NCHW4c stem, folded
     for xs, wsh, s, p in cases:
         x = np.clip(rng.standard_normal(xs) * 128, -128, 127).astype(np.int8)       # the script's distribution
