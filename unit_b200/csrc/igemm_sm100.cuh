@@ -1146,6 +1146,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t s = 0, ring_phase = 0;
       uint32_t lt = 0;  // tiles done by this CTA
       bool alive = true;
+      const bool bias_static = p.n_tiles == 1;  // every tile of this CTA has the same bias
+      int bias_flag0 = 0, bias_flag1 = 0;        // the sets' "bias goes in through an MMA" flags, once read
       for (int tile = tile0; tile < total_tiles && alive; tile += tstep, ++lt) {
         const uint32_t slot = nslots == 2u ? (lt & 1u) : 0u;
         const uint32_t use = nslots == 2u ? (lt >> 1) : lt;
@@ -1226,14 +1228,22 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             // The bias step comes last: the drain warps stage the set's bias while the main loop
             // runs (for a CTA's first tiles that is the whole of global-memory latency), and integer
             // sums do not depend on the order of their terms.
-            if (!(kConv ? mbar_wait_warp(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias)
-                        : mbar_wait(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias))) {
-              alive = false;
-              break;
+            // With one column block the set's bias is staged once, before its first tile, and never
+            // rewritten: later tiles reuse it without waiting (the drain warps' later arrivals
+            // complete phases nobody looks at).
+            int with_bias = slot == 0u ? bias_flag0 : bias_flag1;
+            if (!bias_static || use == 0u) {
+              if (!(kConv ? mbar_wait_warp(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias)
+                          : mbar_wait(smem_u32(&ps->bready[slot]), use & 1u, wc, kErrWaitBias))) {
+                alive = false;
+                break;
+              }
+              tc_fence_after();
+              with_bias = *reinterpret_cast<volatile int *>(&ps->bias_mma[slot]);
+              if (slot == 0u) bias_flag0 = with_bias; else bias_flag1 = with_bias;
             }
-            tc_fence_after();
             // (split-K: the bias enters the first CTA's partial sum only)
-            if (*reinterpret_cast<volatile int *>(&ps->bias_mma[slot]) != 0 && (!SPLITK || crank == 0u)) {
+            if (with_bias != 0 && (!SPLITK || crank == 0u)) {
               const uint64_t adesc = a_desc0 | (uint64_t)((fold_base + 2u * kFoldBBytes) >> 4);
               const uint64_t bdesc = b_desc0 | (uint64_t)((fold_base + slot * kFoldBBytes) >> 4);
               if (one) tc_mma<F16>(d_tmem, adesc, bdesc, idesc, started);
