@@ -593,6 +593,17 @@ __device__ __forceinline__ void finish_group16(const IgemmParams &p, const uint3
   }
 }
 
+// The requantising epilogue's commonest case in one piece: shift 8, bias and rounding constant
+// already inside the accumulator.  16 s32 sums -> 16 u8, clamp(x >> 8, 0, 255).
+__device__ __forceinline__ uint4 pack16_shift8(const uint32_t *t) {
+  uint32_t w[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    w[q] = __byte_perm(pack_sat_u16((int32_t)t[4 * q + 1], (int32_t)t[4 * q]),
+                       pack_sat_u16((int32_t)t[4 * q + 3], (int32_t)t[4 * q + 2]), 0x7531);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Epilogue for 16 consecutive columns of one row: v = accumulator words, bias_s = this
 // group's 16 staged bias values in shared memory (bias + rounding constant for the
 // requantising epilogues).
@@ -1418,6 +1429,45 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       } else {
       // software pipeline: the read of group g + 1 is in flight while group g is processed
       uint32_t va[16], vb[16];
+      // The common cases as a loop of their own, with no per-group decisions and one offset that
+      // advances: the accumulator is final (bias inside it, or none) and, when requantising, the
+      // shift is 8.  (Measured on the 1x1 64->256 layer at batch 256: 35 -> 19 instructions per
+      // group, 72 -> 52 us; the drain warps' instruction count is what bounds the write-heavy layers.)
+      bool drained = false;
+      if (EPI != EPI_RES_NCHWC && (EPI == EPI_RAW_ROWS || folded) && (!epi_requantises(EPI) || p.shift == 8)) {
+        long long o = obase + (long long)g_begin * gstride;
+        uint32_t taddr = t_row + (uint32_t)g_begin * 16u;
+        int left = g_stop - g_begin;
+        if (left > 0) {
+          tmem_ld16(taddr, va);
+          tmem_ld_wait();
+        }
+        while (left > 0) {
+          if (left > 1) tmem_ld16(taddr + 16u, vb);
+          if constexpr (EPI == EPI_REQ_NCHWC) {
+            const uint4 w = pack16_shift8(va);
+            if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = w;
+          } else {
+            if (mvalid) finish_group16<EPI>(p, va, o);
+          }
+          tmem_ld_wait();
+          if (left > 2) tmem_ld16(taddr + 32u, va);
+          if (left > 1) {
+            if constexpr (EPI == EPI_REQ_NCHWC) {
+              const uint4 w = pack16_shift8(vb);
+              if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) = w;
+            } else {
+              if (mvalid) finish_group16<EPI>(p, vb, o + gstride);
+            }
+          }
+          tmem_ld_wait();
+          taddr += 32u;
+          o += 2 * gstride;
+          left -= 2;
+        }
+        drained = true;
+      }
+      if (!drained) {
       if (g_begin < g_stop) {
         tmem_ld16(t_row + (uint32_t)g_begin * 16u, va);
         tmem_ld_wait();
@@ -1430,6 +1480,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         if (g + 2 < g_stop) tmem_ld16(t_row + (uint32_t)(g + 2) * 16u, va);
         if (has_b && mvalid) store_group16<EPI>(p, tile_bias + (g + 1) * 16, folded, wide, vb, obase + (g + 1) * gstride);
         tmem_ld_wait();
+      }
       }
       }
       // the accumulator set is free again: the MMA warp may start the set's next main loop
