@@ -593,6 +593,46 @@ __device__ __forceinline__ void finish_group16(const IgemmParams &p, const uint3
   }
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// The 32-bit epilogues' store of one 16-column group, regrouped through shared memory.  A thread
+// holds 64 bytes of its own row; stored as they are, one warp instruction would touch 32 separate
+// rows with 16 bytes each.  Instead the rows go through a 1 KB scratch block of the warp, sixteen
+// at a time, and come back so that four neighbouring lanes hold one row's 64 bytes: a warp
+// instruction then writes eight rows' 64-byte runs (a quarter of the cache lines touched).
+//   xs    : the warp's scratch block (shared-memory address)
+//   v     : this lane's 16 words;  o_k / ok_k: for k = half * 2 + j, the element offset in the output
+//           of row 16 * half + 8 * j + lane / 4 plus 4 * (lane % 4), and whether that row exists
+// The 16-byte chunks of a row are stored at chunk ^ ((row / 2) % 4), which keeps both the row-wise
+// writes and the regrouped reads free of bank conflicts.
+__device__ __forceinline__ void store_group16_regrouped(uint32_t *out, uint32_t xs, int lane, const uint32_t *v,
+                                                        const long long (&o_k)[4], const bool (&ok_k)[4], long long goff) {
+  const uint32_t wr = xs + (uint32_t)(lane & 15) * 64u;
+  const uint32_t wsw = (uint32_t)(lane >> 1) & 3u;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if ((lane >> 4) == half) {
+#pragma unroll
+      for (uint32_t c = 0; c < 4u; ++c) st_shared_v4(wr + ((c ^ wsw) << 4), v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t row = (uint32_t)(8 * j + (lane >> 2));
+      const uint4 t = ld_shared_v4(xs + row * 64u + ((((uint32_t)lane & 3u) ^ ((row >> 1) & 3u)) << 4));
+      if (ok_k[half * 2 + j]) *reinterpret_cast<uint4 *>(out + o_k[half * 2 + j] + goff) = t;
+    }
+    __syncwarp();
+  }
+}
+
 // The requantising epilogue's commonest case in one piece: shift 8, bias and rounding constant
 // already inside the accumulator.  16 s32 sums -> 16 u8, clamp(x >> 8, 0, 255).
 __device__ __forceinline__ uint4 pack16_shift8(const uint32_t *t) {
@@ -1434,6 +1474,23 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       // shift is 8.  (Measured on the 1x1 64->256 layer at batch 256: 35 -> 19 instructions per
       // group, 72 -> 52 us; the drain warps' instruction count is what bounds the write-heavy layers.)
       bool drained = false;
+      // 32-bit outputs of the kernels that keep no bias in shared memory (fp16, dense): regrouped stores
+      constexpr bool kRegroup = !kCanFold && (EPI == EPI_RAW_ROWS || EPI == EPI_RAW_NCHWC);
+      long long o_k[4] = {0, 0, 0, 0};
+      bool ok_k[4] = {false, false, false, false};
+      uint32_t xs = 0u;
+      if constexpr (kRegroup) {
+        // the warp's scratch block: the (unused) bias-digit region, and for the last four warps the
+        // (equally unused) bias integers of the pipeline state
+        xs = warp < 12 ? smem_u32(fold_mem) + (uint32_t)warp * 1024u
+                       : smem_u32(&ps->bias[0][0][0]) + (uint32_t)(warp - 12) * 1024u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int src = (k >> 1) * 16 + (k & 1) * 8 + (lane >> 2);
+          o_k[k] = __shfl_sync(0xffffffffu, obase, src) + 4 * (lane & 3);
+          ok_k[k] = __shfl_sync(0xffffffffu, mvalid ? 1 : 0, src) != 0;
+        }
+      }
       if (EPI != EPI_RES_NCHWC && (EPI == EPI_RAW_ROWS || folded) && (!epi_requantises(EPI) || p.shift == 8)) {
         long long o = obase + (long long)g_begin * gstride;
         uint32_t taddr = t_row + (uint32_t)g_begin * 16u;
@@ -1447,6 +1504,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if constexpr (EPI == EPI_REQ_NCHWC) {
             const uint4 w = pack16_shift8(va);
             if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = w;
+          } else if constexpr (kRegroup) {
+            store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, va, o_k, ok_k, o - obase);
           } else {
             if (mvalid) finish_group16<EPI>(p, va, o);
           }
@@ -1456,6 +1515,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             if constexpr (EPI == EPI_REQ_NCHWC) {
               const uint4 w = pack16_shift8(vb);
               if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) = w;
+            } else if constexpr (kRegroup) {
+              store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, vb, o_k, ok_k, o - obase + gstride);
             } else {
               if (mvalid) finish_group16<EPI>(p, vb, o + gstride);
             }
