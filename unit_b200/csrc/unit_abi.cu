@@ -112,6 +112,9 @@ static TileCfg make_cfg(int n_total, int cols, bool cheap_a = false, bool dense 
 // set in TMEM is worth more (wide blocks only: with MT x BN <= 256 both sets fit anyway).  When
 // the A operand is the bottleneck (im2col copies: slow_a) a single sub-tile costs nothing extra,
 // so it is taken when it fills the last round of tiles markedly better.  Measured at batch 256.
+// The fp16 kernels follow the same rule: their 32-bit drains are long, and with single sub-tiles a
+// second accumulator set hides them (3x3 256->256 at 14x14, batch 256: 196 tiles of two sub-tiles
+// need two rounds on 148 SMs, 392 single ones three half-sized rounds: 763 -> 857 TFLOP/s).
 static int choose_mt(const TileCfg &c, long long m_total, int sms, bool slow_a) {
   static const int forced = tuning_int("UNIT_B200_MT", 0);
   if (forced == 1 || forced == 2) return forced;
@@ -904,7 +907,7 @@ static int prepare(PlanImpl &pl, const TileCfg &c, const CUtensorMap *tmap_in = 
   const int sms = sm_count();
   pl.magic = kPlanMagic;
   if constexpr (MAX_MT >= 2) {
-    const int mt = (pl.table_mt == 1 || pl.table_mt == 2) ? pl.table_mt : choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA);
+    const int mt = (pl.table_mt == 1 || pl.table_mt == 2) ? pl.table_mt : choose_mt(c, p.m_total, sms, AMODE == A_CONV_TMA || F16);
     if (mt == 2) return prepare_mt<AMODE, EPI, F16, 2, false>(pl, c, sms, 1);
   }
   if constexpr ((a_mode_uses_tma(AMODE) && AMODE != A_CONV_WIN) || AMODE == A_CONV_I8) {  // (the window form is used on full grids only;
