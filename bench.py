@@ -219,24 +219,6 @@ def ncu_traffic(name, batch):
     return r + w
 
 
-def write_only_bandwidth(torch, dev):
-    """GB/s of a plain fill of 1 GiB, measured live: the ceiling for the share of a layer's bytes that are
-    writes (a copy, the roofline's denominator, moves half its bytes each way)."""
-    buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-    for _ in range(3):
-        buf.fill_(1)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(10):
-        buf.fill_(2)
-    b.record()
-    torch.cuda.synchronize()
-    gbs = buf.numel() * 10 / (a.elapsed_time(b) * 1e-3) / 1e9
-    del buf
-    return gbs
-
-
 def tensor_peak(torch, gpu_index, f16: bool, seconds: float = 0.6):
     """The tensor-core issue-rate probe (unit_tensor_peak), run back to back for `seconds` so that the
     figure is the sustained one under the power cap; clocks sampled beside it."""
@@ -591,7 +573,6 @@ def run_unit(args):
     # that every launch meets the cold L2 it meets in the timed step
     peaks = _peaks()
     int8_peak = 2.0 * peaks['bf16_sustained']
-    write_gbs = write_only_bandwidth(torch, dev) if not args.kernels_only else float(peaks['hbm_gbs'])
     layer_rows = []
     sum_kernel_ms = 0.0
     sum_roof_ms = 0.0
@@ -617,11 +598,9 @@ def run_unit(args):
             roof = max(t_tensor, t_hbm)
             sum_kernel_ms += ms * len(idxs)
             sum_roof_ms += roof * len(idxs)
-            out_bytes = float(batch) * l.c_out * l.out_hw * l.out_hw
-            t_write = out_bytes / (write_gbs * 1e9) * 1e3  # the output alone, at the measured write-only rate
             layer_rows.append({'layer': l.name, 'count': l.count, 'us': round(ms * 1e3, 2),
                                'tops': round(ops / ms / 1e9, 1), 'gbs': round(byts / ms / 1e6, 1), 'bound': bound,
-                               'frac': round(roof / ms, 3), 'frac_with_write_floor': round(max(roof, t_write) / ms, 3),
+                               'frac': round(roof / ms, 3),
                                'traffic': ncu_traffic(l.name, batch), 'algorithmic_bytes': byts})
     else:
         sum_kernel_ms, sum_roof_ms = ms_step, None
@@ -748,7 +727,6 @@ def run_unit(args):
                          'traffic_note': 'mean DRAM bytes per launch over the 53 launches of a step (ncu, one capture per '
                                          'layer shape at batch 256); algorithmic mean %.1f MB'
                                          % (sum(l.bytes(batch) * l.count for l in layer_set) / n_launch / 1e6),
-                         'hbm_write_only_gbs': write_gbs,
                          'mixed_bound_frac': (sum_roof_ms / sum_kernel_ms) if sum_roof_ms else None,
                          'hbm_peak_gbs': peaks['hbm_gbs'],
                          # per layer: [name, count, us per launch, bound, fraction of that bound's roofline]
