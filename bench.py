@@ -443,6 +443,32 @@ def side_configs(torch, U, R, dev, peaks, local_rank):
                                          'rows': rows, 'row_format': '[workload, us, TOPS]',
                                          'reference_log': 'apps/cpu/kernel/res: 797-1170 us for the 3x3x3 stride-1 workloads on its CPU'}
 
+    # a residual block chained in layout (u8 NCHW16c in, u8 NCHW16c out, no repack between the layers; the
+    # reference's graph flow, apps/cpu/relay/result.log:30-36): the first bottleneck of ResNet-50's stage 1 at
+    # batch 256: 1x1 256->64, 3x3 64->64, 1x1 64->256 with the block's input added before the clamp (ReLU);
+    # every layer reads the previous one's output; one captured graph of the three launches, L2 flushed
+    nb, hw = 256, 56
+    gen = torch.Generator(device=dev).manual_seed(77)
+    xb = torch.randint(0, 256, (nb, 16, hw, hw, 16), dtype=torch.uint8, device=dev, generator=gen)
+    ws = [(torch.randn(shape, device=dev, generator=gen) * 12).round_().clamp_(-128, 127).to(torch.int8)
+          for shape in ((4, 16, 1, 1, 4, 16, 4), (4, 4, 3, 3, 4, 16, 4), (16, 4, 1, 1, 4, 16, 4))]
+    bs = [torch.randint(-2 ** 12, 2 ** 12, (c,), dtype=torch.int32, device=dev, generator=gen) for c in (64, 64, 256)]
+    pws = [U.pack_conv_weights_int8(w_, 1, pad_) for w_, pad_ in zip(ws, (0, 1, 0))]
+    y1 = torch.empty((nb, 4, hw, hw, 16), dtype=torch.uint8, device=dev)
+    y2 = torch.empty_like(y1)
+    y3 = torch.empty_like(xb)
+    block = [U.conv2d_NCHWc_int8_plan(xb, pws[0], bias=bs[0], out_dtype='uint8', out=y1),
+             U.conv2d_NCHWc_int8_plan(y1, pws[1], padding=1, bias=bs[1], out_dtype='uint8', out=y2),
+             U.conv2d_NCHWc_int8_plan(y2, pws[2], bias=bs[2], out_dtype='uint8', residual=xb, out=y3)]
+    gb, _ = capture_graph(torch, U, lambda: [pl.run() for pl in block], warm=3)
+    ms_b = flushed(gb.replay, 10)
+    ops_b = 2.0 * nb * hw * hw * (256 * 64 + 64 * 64 * 9 + 64 * 256)
+    bytes_b = 2.0 * xb.numel() + y3.numel() + 4.0 * y1.numel()   # the input twice (conv and residual), the output, y1 and y2 written and read
+    out['residual_block_chained_b256'] = {'value': ops_b / ms_b / 1e9, 'unit': 'TOPS', 'ms': ms_b, 'gbs': bytes_b / ms_b / 1e6,
+                                          'layers': '1x1 256->64, 3x3 64->64, 1x1 64->256 + residual + ReLU, shift 8, 56x56, batch 256',
+                                          'hbm_peak_gbs': peaks['hbm_gbs']}
+    del gb, block, xb, y1, y2, y3, ws, pws
+
     # layout kernels (NCHW <-> NCHW16c): GB/s of bytes read + written
     xl = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device=dev)
     yl = U.pack_data_nchwc(xl)

@@ -643,6 +643,20 @@ __device__ __forceinline__ uint4 pack16_shift8(const uint32_t *t) {
                        pack_sat_u16((int32_t)t[4 * q + 3], (int32_t)t[4 * q + 2]), 0x7531);
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
+// The same with a u8 residual added after the shift: clamp((x >> 8) + r, 0, 255) = clamp((x + 256 r) >> 8, 0, 255),
+// so the residual byte joins its sum one byte up and the pack stays as it is.  (x + 256 r cannot leave s32: the
+// host bounds |x| below 2^30 on this path.)
+__device__ __forceinline__ uint4 pack16_shift8_res(const uint32_t *t, uint4 r) {
+  const uint32_t res[4] = {r.x, r.y, r.z, r.w};
+  uint32_t w[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t x0 = t[4 * q] + __byte_perm(res[q], 0u, 0x4404), x1 = t[4 * q + 1] + __byte_perm(res[q], 0u, 0x4414);
+    const uint32_t x2 = t[4 * q + 2] + __byte_perm(res[q], 0u, 0x4424), x3 = t[4 * q + 3] + __byte_perm(res[q], 0u, 0x4434);
+    w[q] = __byte_perm(pack_sat_u16((int32_t)x1, (int32_t)x0), pack_sat_u16((int32_t)x3, (int32_t)x2), 0x7531);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 // Epilogue for 16 consecutive columns of one row: v = accumulator words, bias_s = this
 // group's 16 staged bias values in shared memory (bias + rounding constant for the
@@ -1394,12 +1408,19 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         obase = (n_img * p.out_img_stride + (long long)n_tile * (p.bn >> 4) * p.out_grp_stride + rem) * 16;
       }
       const int32_t *tile_bias = &ps->bias[slot][ver][0];
+      const int g_stop = min(g_end, (p.n_total - n_tile * p.bn + 15) >> 4);  // groups that hold real columns
+      if constexpr (EPI == EPI_RES_NCHWC) {
+        // the residual values this thread will add: asked into L2 now, while the tile's MMAs still run
+        // (one lane per 128-byte line; read straight from HBM inside the loop they cost a group its whole latency)
+        if (mvalid && (lane & 7) == 0)
+          for (int g = g_begin; g < g_stop; ++g)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + obase + (long long)g * gstride));
+      }
       if (!mbar_wait_warp(smem_u32(&ps->tfull[slot]), use & 1u, wc, kErrWaitTmemFull)) break;
       tc_fence_after();
       if (wl == 0 && lane == 0) trace_mark(p, lt, 6);
       const uint32_t t_row =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (slot * (uint32_t)MT + (uint32_t)sub) * (uint32_t)p.bn;
-      const int g_stop = min(g_end, (p.n_total - n_tile * p.bn + 15) >> 4);  // groups that hold real columns
       if constexpr (SPLITK) {
         // ---- split-K: reduce-scatter of the cluster's partial accumulators through distributed
         // shared memory.  Column group g (16 columns) belongs to CTA g % S: every CTA sends the
@@ -1491,7 +1512,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           ok_k[k] = __shfl_sync(0xffffffffu, mvalid ? 1 : 0, src) != 0;
         }
       }
-      if (EPI != EPI_RES_NCHWC && (EPI == EPI_RAW_ROWS || folded) && (!epi_requantises(EPI) || p.shift == 8)) {
+      if ((EPI == EPI_RAW_ROWS || folded) && (!epi_requantises(EPI) || p.shift == 8)) {
         long long o = obase + (long long)g_begin * gstride;
         uint32_t taddr = t_row + (uint32_t)g_begin * 16u;
         int left = g_stop - g_begin;
@@ -1504,6 +1525,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if constexpr (EPI == EPI_REQ_NCHWC) {
             const uint4 w = pack16_shift8(va);
             if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = w;
+          } else if constexpr (EPI == EPI_RES_NCHWC) {
+            if (mvalid)
+              *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) =
+                  pack16_shift8_res(va, *reinterpret_cast<const uint4 *>(p.residual + o));
           } else if constexpr (kRegroup) {
             store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, va, o_k, ok_k, o - obase);
           } else {
@@ -1515,6 +1540,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             if constexpr (EPI == EPI_REQ_NCHWC) {
               const uint4 w = pack16_shift8(vb);
               if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) = w;
+            } else if constexpr (EPI == EPI_RES_NCHWC) {
+              if (mvalid)
+                *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) =
+                    pack16_shift8_res(vb, *reinterpret_cast<const uint4 *>(p.residual + o + gstride));
             } else if constexpr (kRegroup) {
               store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, vb, o_k, ok_k, o - obase + gstride);
             } else {
