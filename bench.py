@@ -443,6 +443,26 @@ def side_configs(torch, U, R, dev, peaks, local_rank):
                                          'rows': rows, 'row_format': '[workload, us, TOPS]',
                                          'reference_log': 'apps/cpu/kernel/res: 797-1170 us for the 3x3x3 stride-1 workloads on its CPU'}
 
+    # the reference's own fused graph operator on signed activations, multiply(add(conv2d(x s8, w s8), bias), 11)
+    # in s32 (apps/cpu/relay/conv2d.py:16-23), on its logged shape (apps/cpu/relay/result.log:3: 1x1 1024->2048
+    # at 16x16), at the logged batch 1 and at batch 256; one launch each (the tensor core takes s8 x s8 as it is)
+    gen = torch.Generator(device=dev).manual_seed(78)
+    wr = torch.randint(-128, 128, (128, 64, 1, 1, 4, 16, 4), dtype=torch.int8, device=dev, generator=gen)
+    br = torch.randint(-2 ** 14, 2 ** 14, (2048,), dtype=torch.int32, device=dev, generator=gen)
+    pwr = U.pack_conv_weights_int8(wr, 1, 0)
+    relay_rows = {}
+    for nb_ in (1, 256):
+        xr = torch.randint(-128, 128, (nb_, 64, 16, 16, 16), dtype=torch.int8, device=dev, generator=gen)
+        orr = torch.empty((nb_, 128, 16, 16, 16), dtype=torch.int32, device=dev)
+        plr = U.conv2d_NCHWc_int8_plan(xr, pwr, bias=br, mul=11, out=orr)
+        ms_r = flushed(plr.run, 10)
+        relay_rows[f'b{nb_}'] = {'us': ms_r * 1e3, 'tops': 2.0 * nb_ * 256 * 2048 * 1024 / ms_r / 1e9}
+        del plr, xr, orr
+    out['relay_flow_s8_1x1_1024_2048'] = {'value': relay_rows['b256']['tops'], 'unit': 'TOPS at batch 256', 'ms': relay_rows['b256']['us'] / 1e3,
+                                          'us_b1': relay_rows['b1']['us'], 'tops_b1': relay_rows['b1']['tops'],
+                                          'what': '(conv(x s8, w s8) + bias) * 11 in s32, 1x1 1024->2048 at 16x16, L2 flushed'}
+    del wr, pwr
+
     # a residual block chained in layout (u8 NCHW16c in, u8 NCHW16c out, no repack between the layers; the
     # reference's graph flow, apps/cpu/relay/result.log:30-36): the first bottleneck of ResNet-50's stage 1 at
     # batch 256: 1x1 256->64, 3x3 64->64, 1x1 64->256 with the block's input added before the clamp (ReLU);
