@@ -444,6 +444,39 @@ def test_host_tensors_in_host_tensor_out(U, oracle):
     assert np.array_equal(got.numpy(), oracle.conv2d_u8s8(x, w, (1, 1), (1, 1)))
 
 
+def test_operator_reuses_its_prepared_launch_on_the_same_buffers(U, oracle):
+    """Calls that name their output buffer keep their prepared launch (unit_b200.ops._PLAN_CACHE): a repeated
+    call must read the buffers' current contents, and other buffers, epilogues or shapes get launches of their own."""
+    from unit_b200 import ops
+    rng = np.random.default_rng(31)
+    x = rng.integers(0, 256, (2, 4, 20, 20, 16), dtype=np.uint8)
+    w = rng.integers(-128, 128, (4, 4, 3, 3, 4, 16, 4), dtype=np.int8)
+    b = rng.integers(-2 ** 12, 2 ** 12, 64, dtype=np.int32)
+    xd, bd = dev(x), dev(b)
+    pw = U.pack_conv_weights_int8(dev(w), 1, 1)
+    o1 = torch.empty((2, 4, 20, 20, 16), dtype=torch.int32, device='cuda')
+    o2 = torch.empty_like(o1)
+    o8 = torch.empty((2, 4, 20, 20, 16), dtype=torch.uint8, device='cuda')
+    n0 = len(ops._PLAN_CACHE)
+    for _ in range(3):
+        assert U.conv2d_NCHWc_int8(xd, pw, padding=1, out=o1) is o1
+    assert len(ops._PLAN_CACHE) == n0 + 1
+    assert np.array_equal(o1.cpu().numpy(), oracle.conv2d_u8s8(x, w, (1, 1), (1, 1)))
+    x2 = rng.integers(0, 256, x.shape, dtype=np.uint8)
+    xd.copy_(dev(x2))                                   # same buffer, new contents
+    U.conv2d_NCHWc_int8(xd, pw, padding=1, out=o1)
+    assert len(ops._PLAN_CACHE) == n0 + 1
+    assert np.array_equal(o1.cpu().numpy(), oracle.conv2d_u8s8(x2, w, (1, 1), (1, 1)))
+    U.conv2d_NCHWc_int8(xd, pw, padding=1, out=o2)      # another output buffer
+    U.conv2d_NCHWc_int8(xd, pw, padding=1, bias=bd, out_dtype='uint8', out=o8)   # another epilogue
+    assert len(ops._PLAN_CACHE) == n0 + 3
+    assert np.array_equal(o2.cpu().numpy(), o1.cpu().numpy())
+    assert np.array_equal(o8.cpu().numpy(), oracle.conv2d_i8_ex(x2, w, (1, 1), (1, 1), bias=b, requant_shift=8))
+    with pytest.raises(ValueError):                       # a wrong output shape is still refused
+        U.conv2d_NCHWc_int8(xd, pw, padding=1, out=torch.empty((2, 4, 19, 20, 16), dtype=torch.int32, device='cuda'))
+    U.device_status()
+
+
 def test_batch_split_equals_whole_batch(U):
     """The multi-GPU partition: concatenating per-slice results equals the whole-batch result."""
     from unit_b200 import resnet50 as R

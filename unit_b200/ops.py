@@ -276,7 +276,8 @@ class ConvPlan:
         return self.out
 
 
-_PLAN_CACHE: dict = {}
+_PLAN_CACHE: dict = {}      # prepared launches of conv2d_NCHWc_int8 calls that named their output buffer
+_PLAN_CACHE_MAX = 512
 
 
 def _conv_int8_prepare(data, kernel, stride, padding, dilation, out_layout, out_dtype, bias, requant_shift, mul,
@@ -358,14 +359,39 @@ def conv2d_NCHWc_int8(data: torch.Tensor, kernel, stride: IntPair = 1, padding: 
     ``layout`` is accepted for signature compatibility; the channel block is
     read from ``data``'s last dimension as the reference's compute does.
     """
+    # Repeated calls on the same device buffers (the caller passes ``out``) reuse the prepared launch:
+    # the checks, the tile selection and the tensor-map encoding are done once per distinct call.
+    key = None
+    if out is not None and data.is_cuda and isinstance(kernel, PackedWeights):
+        from . import tile_table
+        key = (data.data_ptr(), tuple(data.shape), data.dtype, kernel.buf.data_ptr(), kernel.key, stride, padding, dilation,
+               out_layout, out_dtype, None if bias is None else (bias.data_ptr(), bias.dtype, bias.numel()), requant_shift, mul,
+               None if residual is None else (residual.data_ptr(), tuple(residual.shape), residual.dtype),
+               out.data_ptr(), tuple(out.shape), out.dtype, out.is_contiguous(), _stream(), tile_table.version())
+        hit = _PLAN_CACHE.get(key)
+        if hit is not None:
+            rc = hit[1](hit[2], key[-2])
+            if rc:
+                check(rc, 'unit_conv2d_run')
+            return out
     L, d, tensors, epi, out_t, ws, ws_bytes, host, n = _conv_int8_prepare(
         data, kernel, stride, padding, dilation, out_layout, out_dtype, bias, requant_shift, mul, residual, out)
     if n == 0:
         return out_t.cpu() if (host and out is None) else out_t
     x, pw = tensors[0], tensors[1]
     with torch.cuda.device(x.device):
-        check(L.unit_conv2d_int8_nchwc(ctypes.byref(d), _ptr(x), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _ptr(ws),
-                                       ws_bytes, _stream()), 'unit_conv2d_int8_nchwc')
+        if key is not None and tensors[2] is bias and tensors[3] is residual:
+            plan = _CPlan()
+            check(L.unit_conv2d_plan_int8(ctypes.byref(d), _ptr(x), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _ptr(ws),
+                                          ws_bytes, ctypes.byref(plan)), 'unit_conv2d_plan_int8')
+            if len(_PLAN_CACHE) >= _PLAN_CACHE_MAX:
+                _PLAN_CACHE.pop(next(iter(_PLAN_CACHE)))
+            # (the entry holds no tensor: like the call itself it is valid for as long as the caller's buffers are)
+            _PLAN_CACHE[key] = (plan, L.unit_conv2d_run, ctypes.byref(plan))
+            check(L.unit_conv2d_run(ctypes.byref(plan), _stream()), 'unit_conv2d_run')
+        else:
+            check(L.unit_conv2d_int8_nchwc(ctypes.byref(d), _ptr(x), _ptr(pw.buf), ctypes.byref(epi), _ptr(out_t), _ptr(ws),
+                                           ws_bytes, _stream()), 'unit_conv2d_int8_nchwc')
     return out_t.cpu() if (host and out is None) else out_t
 
 
