@@ -823,6 +823,35 @@ def run_side_config(args):
         out = torch.empty((4096, 4096), dtype=torch.float32, device=dev)
         fn = lambda: U.gemm_f16f32(a, pw, out=out)
         ops, unit, peak, what = 2.0 * 4096 ** 3, 'TFLOP/s', peaks['bf16_burst'], 'fp16 GEMM 4096^3 (fp32 accumulate)'
+    elif args.config == 'resblock':
+        # the chained residual block of `configs.residual_block_chained_b256`, three launches per call
+        nb, hw = 256, 56
+        gen = torch.Generator(device=dev).manual_seed(77)
+        xb = torch.randint(0, 256, (nb, 16, hw, hw, 16), dtype=torch.uint8, device=dev, generator=gen)
+        ws = [(torch.randn(shape, device=dev, generator=gen) * 12).round_().clamp_(-128, 127).to(torch.int8)
+              for shape in ((4, 16, 1, 1, 4, 16, 4), (4, 4, 3, 3, 4, 16, 4), (16, 4, 1, 1, 4, 16, 4))]
+        bs = [torch.randint(-2 ** 12, 2 ** 12, (c,), dtype=torch.int32, device=dev, generator=gen) for c in (64, 64, 256)]
+        pws = [U.pack_conv_weights_int8(w_, 1, pad_) for w_, pad_ in zip(ws, (0, 1, 0))]
+        y1 = torch.empty((nb, 4, hw, hw, 16), dtype=torch.uint8, device=dev)
+        y2, y3 = torch.empty_like(y1), torch.empty_like(xb)
+        block = [U.conv2d_NCHWc_int8_plan(xb, pws[0], bias=bs[0], out_dtype='uint8', out=y1),
+                 U.conv2d_NCHWc_int8_plan(y1, pws[1], padding=1, bias=bs[1], out_dtype='uint8', out=y2),
+                 U.conv2d_NCHWc_int8_plan(y2, pws[2], bias=bs[2], out_dtype='uint8', residual=xb, out=y3)]
+        fn = lambda: [pl.run() for pl in block]
+        ops, unit, peak = 2.0 * nb * hw * hw * (256 * 64 + 64 * 64 * 9 + 64 * 256), 'TOPS', 2.0 * peaks['bf16_burst']
+        what = 'residual block chained in layout: 1x1 256->64, 3x3 64->64, 1x1 64->256 + residual + ReLU @56^2, N = 256'
+    elif args.config == 'relay':
+        # the signed fused graph operator of `configs.relay_flow_s8_1x1_1024_2048` at batch 256
+        gen = torch.Generator(device=dev).manual_seed(78)
+        w = torch.randint(-128, 128, (128, 64, 1, 1, 4, 16, 4), dtype=torch.int8, device=dev, generator=gen)
+        br = torch.randint(-2 ** 14, 2 ** 14, (2048,), dtype=torch.int32, device=dev, generator=gen)
+        pw = U.pack_conv_weights_int8(w, 1, 0)
+        x = torch.randint(-128, 128, (256, 64, 16, 16, 16), dtype=torch.int8, device=dev, generator=gen)
+        out = torch.empty((256, 128, 16, 16, 16), dtype=torch.int32, device=dev)
+        plr = U.conv2d_NCHWc_int8_plan(x, pw, bias=br, mul=11, out=out)
+        fn = plr.run
+        ops, unit, peak = 2.0 * 256 * 256 * 2048 * 1024, 'TOPS', 2.0 * peaks['bf16_burst']
+        what = '(conv(x s8, w s8) + bias) * 11 in s32, 1x1 1024->2048 @16^2, N = 256'
     else:
         x = torch.randn((256, 16, 14, 14, 16), dtype=torch.float16, device=dev)
         w = torch.randn((16, 16, 3, 3, 16, 16), dtype=torch.float16, device=dev) * 0.05
@@ -858,7 +887,7 @@ def run_side_config(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--config', default=None, choices=['gemm', 'fp16gemm', 'fp16conv', 'peak', 'layout'],
+    ap.add_argument('--config', default=None, choices=['gemm', 'fp16gemm', 'fp16conv', 'peak', 'layout', 'resblock', 'relay'],
                     help='time one of the other configurations alone instead of the conv sweep (single GPU)')
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=10)

@@ -1516,34 +1516,45 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         long long o = obase + (long long)g_begin * gstride;
         uint32_t taddr = t_row + (uint32_t)g_begin * 16u;
         int left = g_stop - g_begin;
+        // (residual epilogue: the residual values of a group are read one group ahead, like its accumulators)
+        uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
         if (left > 0) {
           tmem_ld16(taddr, va);
+          if constexpr (EPI == EPI_RES_NCHWC) {
+            if (mvalid) ra = *reinterpret_cast<const uint4 *>(p.residual + o);
+          }
           tmem_ld_wait();
         }
         while (left > 0) {
-          if (left > 1) tmem_ld16(taddr + 16u, vb);
+          if (left > 1) {
+            tmem_ld16(taddr + 16u, vb);
+            if constexpr (EPI == EPI_RES_NCHWC) {
+              if (mvalid) rb = *reinterpret_cast<const uint4 *>(p.residual + o + gstride);
+            }
+          }
           if constexpr (EPI == EPI_REQ_NCHWC) {
             const uint4 w = pack16_shift8(va);
             if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = w;
           } else if constexpr (EPI == EPI_RES_NCHWC) {
-            if (mvalid)
-              *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) =
-                  pack16_shift8_res(va, *reinterpret_cast<const uint4 *>(p.residual + o));
+            if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o) = pack16_shift8_res(va, ra);
           } else if constexpr (kRegroup) {
             store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, va, o_k, ok_k, o - obase);
           } else {
             if (mvalid) finish_group16<EPI>(p, va, o);
           }
           tmem_ld_wait();
-          if (left > 2) tmem_ld16(taddr + 32u, va);
+          if (left > 2) {
+            tmem_ld16(taddr + 32u, va);
+            if constexpr (EPI == EPI_RES_NCHWC) {
+              if (mvalid) ra = *reinterpret_cast<const uint4 *>(p.residual + o + 2 * gstride);
+            }
+          }
           if (left > 1) {
             if constexpr (EPI == EPI_REQ_NCHWC) {
               const uint4 w = pack16_shift8(vb);
               if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) = w;
             } else if constexpr (EPI == EPI_RES_NCHWC) {
-              if (mvalid)
-                *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) =
-                    pack16_shift8_res(vb, *reinterpret_cast<const uint4 *>(p.residual + o + gstride));
+              if (mvalid) *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.out) + o + gstride) = pack16_shift8_res(vb, rb);
             } else if constexpr (kRegroup) {
               store_group16_regrouped(reinterpret_cast<uint32_t *>(p.out), xs, lane, vb, o_k, ok_k, o - obase + gstride);
             } else {
