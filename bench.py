@@ -567,8 +567,11 @@ def run_unit(args):
             if n_branches > 1:
                 # the step's convolutions are independent of one another (own buffers each): deal them to
                 # parallel branches of the graph, so that one kernel's launch, prologue and tail overlap
-                # another's main loop
-                lanes = [instances[k::n_branches] for k in range(n_branches)]
+                # another's main loop.  Contiguous runs of the sweep per branch: the early layers' full
+                # grids then run beside the late layers' under-filled ones (measured against dealing the
+                # layers alternately: -1.5 % at batch 256, -4 % at batch 32, -5 % at batch 64)
+                per = (len(instances) + n_branches - 1) // n_branches
+                lanes = [instances[k * per:(k + 1) * per] for k in range(n_branches)]
                 branches = [(lambda ls=ls: [i[5].run() for i in ls]) for ls in lanes]
             graph, launches_per_step = capture_graph(torch, U, step, warm=args.warmup, branches=branches)
         except Exception as exc:  # keep measuring, say how
